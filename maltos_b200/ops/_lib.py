@@ -1,0 +1,120 @@
+"""ctypes binding to ``libmaltos_b200.so`` (the sm_100a kernel library).
+
+The library is built in-tree by :mod:`maltos_b200.build`. On a machine with a CUDA device the ops in
+this package refuse to run without it (no silent eager fallback); on CPU-only machines the library is
+never loaded and the ops use their PyTorch fp32 restatements, which are also the oracles of the GPU tests.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "libmaltos_b200.so"
+_lib = None
+_lock = threading.Lock()
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+c_double = ctypes.c_double
+
+
+class KernelLibraryError(RuntimeError):
+    """Raised when the kernel library is missing, fails to load, or a launcher reports an error."""
+
+
+class DeviceStatusError(RuntimeError):
+    """Raised when a kernel left an error code in the per-device status word (bounded wait ran out...)."""
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the kernel library. Raises :class:`KernelLibraryError` if it is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not _LIB_PATH.exists():
+            if os.environ.get("MALTOS_B200_AUTOBUILD", "1") == "1":
+                try:
+                    from maltos_b200 import build as _build
+
+                    _build.build()
+                except Exception as exc:  # pragma: no cover - depends on toolchain
+                    raise KernelLibraryError(
+                        f"{_LIB_PATH} is missing and building it failed: {exc}. "
+                        "Run `python -m maltos_b200.build` on a machine with nvcc."
+                    ) from exc
+            else:
+                raise KernelLibraryError(f"{_LIB_PATH} is missing; run `python -m maltos_b200.build`")
+        try:
+            handle = ctypes.CDLL(str(_LIB_PATH))
+        except OSError as exc:
+            raise KernelLibraryError(f"cannot load {_LIB_PATH}: {exc}") from exc
+        handle.mb_last_error.restype = ctypes.c_char_p
+        handle.mb_launch_count.restype = ctypes.c_ulonglong
+        _lib = handle
+    return _lib
+
+
+def use_kernels(*tensors: torch.Tensor) -> bool:
+    """True when the tensors live on a CUDA device (so the sm_100a kernels are the path to run)."""
+    return any(t is not None and t.is_cuda for t in tensors)
+
+
+def stream_ptr() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().mb_last_error().decode(errors="replace")
+        raise KernelLibraryError(f"{what} failed (code {rc}): {msg}")
+
+
+def launch_count() -> int:
+    """Number of kernels launched by this library in this process so far (0 if it was never loaded)."""
+    if _lib is None:
+        return 0
+    return int(_lib.mb_launch_count())
+
+
+def fetch_status(raise_on_error: bool = True) -> tuple[int, int, int, int]:
+    """Synchronise the current stream, read and clear the device status word.
+
+    Kernels never trap or spin forever: a wait that runs out of time sets a bit here and the kernel
+    returns. ``(code, block, detail, _)``; ``code`` 0 means no error since the last fetch.
+    """
+    out = (ctypes.c_int * 4)()
+    check(lib().mb_status_fetch_and_clear(out, stream_ptr()), "mb_status_fetch_and_clear")
+    vals = tuple(int(v) for v in out)
+    if raise_on_error and vals[0] != 0:
+        names = []
+        if vals[0] & 1:
+            names.append("mbarrier wait timed out")
+        if vals[0] & 2:
+            names.append("peer flag wait timed out")
+        if vals[0] & 4:
+            names.append("index out of bounds")
+        raise DeviceStatusError(f"kernel status {vals[0]} ({', '.join(names)}); block {vals[1]}, detail {vals[2]}")
+    return vals  # type: ignore[return-value]
