@@ -1,0 +1,86 @@
+"""Attention core in ``[B, S, heads, D]`` layout with native GQA (no ``repeat_interleave`` of K/V, unlike the
+reference's ``models/llama.py:145-148``) and one general mask rule that covers dense causal, packed documents and
+context-parallel blocks:
+
+    key j is visible to query i  <=>  k_pos[j] <= q_pos[i]  and  k_seq[j] == q_seq[i]  and  k_seq[j] != PAD
+
+Positions / sequence ids default to ``arange`` / one document. On CUDA bf16 the tcgen05 flash kernels in
+``csrc/flash_attn.cu`` run (forward returns the log-sum-exp so that ring attention can merge blocks); elsewhere an
+fp32 eager restatement is used, which is also the oracle of the kernel tests.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from maltos_b200.utils.constants import PAD_SEQUENCE_ID
+
+from . import _lib
+
+
+def build_visibility_mask(q_positions, k_positions, q_sequence_ids=None, k_sequence_ids=None) -> torch.Tensor:
+    """Boolean ``[B, Sq, Sk]`` mask of the rule above."""
+    mask = k_positions.unsqueeze(1) <= q_positions.unsqueeze(2)
+    if q_sequence_ids is not None and k_sequence_ids is not None:
+        same = q_sequence_ids.unsqueeze(2) == k_sequence_ids.unsqueeze(1)
+        mask = mask & same & (k_sequence_ids != PAD_SEQUENCE_ID).unsqueeze(1)
+    return mask
+
+
+def attention_reference(q, k, v, *, q_positions=None, k_positions=None, q_sequence_ids=None, k_sequence_ids=None,
+                        causal: bool = True, scale: float | None = None, return_lse: bool = False):
+    """fp32 eager attention. q ``[B,Sq,hq,D]``, k/v ``[B,Sk,hkv,D]`` -> ``[B,Sq,hq,D]`` (and ``lse [B,hq,Sq]``)."""
+    B, Sq, hq, D = q.shape
+    Sk, hkv = k.shape[1], k.shape[2]
+    g = hq // hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3).reshape(B, hkv, g, Sq, D)
+    kf = k.float().permute(0, 2, 1, 3).unsqueeze(2)
+    vf = v.float().permute(0, 2, 1, 3).unsqueeze(2)
+    scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale  # [B,hkv,g,Sq,Sk]
+    if q_positions is None and causal:
+        q_positions = torch.arange(Sk - Sq, Sk, device=q.device).unsqueeze(0).expand(B, Sq)
+        k_positions = torch.arange(Sk, device=q.device).unsqueeze(0).expand(B, Sk)
+    if q_positions is not None:
+        mask = build_visibility_mask(q_positions, k_positions, q_sequence_ids, k_sequence_ids)
+        scores = scores.masked_fill(~mask.view(B, 1, 1, Sq, Sk), float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    probs = torch.exp(scores - lse.unsqueeze(-1))
+    probs = torch.nan_to_num(probs, nan=0.0)  # rows with no visible key
+    out = torch.matmul(probs, vf).reshape(B, hq, Sq, D).permute(0, 2, 1, 3).to(q.dtype)
+    if return_lse:
+        return out, lse.reshape(B, hq, Sq)
+    return out
+
+
+def _kernel_eligible(q, k, v) -> bool:
+    return (_lib.use_kernels(q) and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+            and q.shape[-1] in (64, 128))
+
+
+def attention(q, k, v, *, q_positions=None, k_positions=None, q_sequence_ids=None, k_sequence_ids=None,
+              causal: bool = True, scale: float | None = None, return_lse: bool = False):
+    """General masked attention (see module docstring). Differentiable."""
+    if _kernel_eligible(q, k, v):
+        from .flash_attn import flash_attention
+
+        return flash_attention(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
+                               k_sequence_ids=k_sequence_ids, causal=causal, scale=scale, return_lse=return_lse)
+    return attention_reference(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
+                               k_sequence_ids=k_sequence_ids, causal=causal, scale=scale, return_lse=return_lse)
+
+
+def causal_attention(q, k, v, *, position_ids=None, sequence_ids=None, scale: float | None = None):
+    """Self-attention over one local sequence: causal, and document-local when ``sequence_ids`` is given."""
+    if sequence_ids is None:
+        return attention(q, k, v, causal=True, scale=scale)
+    B, S = q.shape[:2]
+    pos = position_ids
+    if pos is None:
+        pos = torch.arange(S, device=q.device).unsqueeze(0).expand(B, S)
+    # inside a packed row, positions restart per document; visibility needs an order that is monotone in the row,
+    # so the row index is used for causality and the document id for the block structure
+    order = torch.arange(S, device=q.device).unsqueeze(0).expand(B, S)
+    return attention(q, k, v, q_positions=order, k_positions=order, q_sequence_ids=sequence_ids, k_sequence_ids=sequence_ids,
+                     causal=True, scale=scale)

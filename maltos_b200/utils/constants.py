@@ -1,0 +1,20 @@
+"""Batch-dictionary keys and sentinel values shared by loaders, models and plugins
+(same names and values as the reference's ``utils/constants.py:3-29``; they are part of the batch contract)."""
+from __future__ import annotations
+
+IGNORE_INDEX = -100      # label value that does not contribute to the loss
+PAD_SEQUENCE_ID = -1     # sequence id of padding tokens in packed batches
+
+INPUT_IDS_KEY = "input_ids"
+LABELS_KEY = "labels"
+POSITION_IDS_KEY = "position_ids"
+SEQUENCE_IDS_KEY = "sequence_ids"
+POSITION_OFFSET_KEY = "position_offset"
+LOSS_WEIGHT_KEY = "loss_weight"
+HIDDEN_STATES_KEY = "hidden_states"
+
+MODEL_BATCH_KEYS = (
+    INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY,
+    POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY,
+)
+SFT_BATCH_KEYS = (INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY)
