@@ -1,0 +1,457 @@
+#!/usr/bin/env python
+"""Headline benchmark: LLaMA-3-8B bf16 training throughput (tokens/s) on N B200 GPUs of one node.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...            # the unmodified reference from baseline/_ref
+
+Config (the one the baseline names): 32 layers, d_model 4096, 32 query / 8 KV heads (head_dim 128), SwiGLU FFN 14336,
+RMSNorm eps 1e-5, RoPE theta 500000, vocab 128256, seq_len 8192, global batch 32 sequences per optimizer step,
+activation checkpointing per layer, fused AdamW with fp32 master weights, TP = N (+ sequence parallel), so the job is
+strong-scaled (the same 262144 tokens per step at every N). Synthetic uniform token ids, random-init weights.
+
+One "step" = one optimizer step = 32 / micro_batch micro-steps of forward + backward, then clip-free AdamW.
+Timing: W untimed warm-up steps, then K steps between CUDA events on the launching stream (barrier + synchronize on
+both sides), max over ranks. A second K-step region measures the same metric end to end through the public API
+(`RuntimeCore.run_step` / `step_optimizer`) with every micro-batch copied from pinned host memory and the step loss
+read back to the host. SM clocks and throttle reasons are sampled through NVML during the timed region.
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+
+MODEL = dict(layers=32, hidden=4096, heads=32, kv_heads=8, ffn=14336, vocab=128256, seq_len=8192, eps=1e-5,
+             rope_theta=500000.0)
+SMALL = dict(layers=2, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=1024, seq_len=256, eps=1e-5, rope_theta=500000.0)
+GLOBAL_BATCH = 32
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--micro-batch", type=int, default=1, help="sequences per micro-step (global batch stays 32)")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    ap.add_argument("--small", action="store_true", help="tiny model/sequence: plumbing check only, NOT a benchmark number")
+    ap.add_argument("--device", default=None, help="override device (cpu allowed only with --small)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
+    return ap.parse_args(argv)
+
+
+# ---------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every 200 ms."""
+
+    _REASONS = {
+        0x0000000000000004: "sw_power_cap",
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+        0x0000000000000080: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._ok = True
+        except Exception:
+            self._ok = False
+
+    def _loop(self) -> None:
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in self._REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self) -> None:
+        if self._ok:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ---------------------------------------------------------------------------------------------- common
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+def init_distributed(world: int, device):
+    import torch
+    import torch.distributed as dist
+
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        backend = "nccl" if device.type == "cuda" else "gloo"
+        kwargs = {"device_id": device} if device.type == "cuda" else {}
+        dist.init_process_group(backend=backend, **kwargs)
+    return dist
+
+
+def max_over_ranks(value: float, device) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized():
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync(device) -> None:
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        if device.type == "cuda":
+            dist.barrier(device_ids=[device.index])
+        else:
+            dist.barrier()
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+
+
+class HostBatches:
+    """Deterministic uniform token batches in pinned host memory (one fresh tensor pair per micro-step)."""
+
+    def __init__(self, micro_batch: int, seq_len: int, vocab: int, seed: int, pin: bool, pool: int = 4) -> None:
+        import torch
+
+        g = torch.Generator().manual_seed(seed)
+        self.items = []
+        for _ in range(pool):
+            toks = torch.randint(0, vocab, (micro_batch, seq_len + 1), generator=g, dtype=torch.long)
+            ids, labels = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
+            if pin:
+                ids, labels = ids.pin_memory(), labels.pin_memory()
+            self.items.append({"input_ids": ids, "labels": labels})
+        self.i = 0
+        self.bytes_per_batch = sum(t.numel() * t.element_size() for t in self.items[0].values())
+
+    def next_batch(self, cp_rank=None):
+        item = self.items[self.i % len(self.items)]
+        self.i += 1
+        return item
+
+
+def emit(payload: dict) -> None:
+    print(json.dumps(payload), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------- this framework
+def run_ours(args) -> None:
+    import torch
+
+    rank, local, world = dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs a torchrun launch with {args.gpus} ranks (WORLD_SIZE is {world})")
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE={world}")
+    use_cuda = torch.cuda.is_available() and (args.device or "cuda") != "cpu"
+    if not use_cuda and not args.small:
+        raise SystemExit("the benchmark needs a CUDA device (use --small --device cpu for a plumbing check)")
+    device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    init_distributed(world, device)
+
+    sys.path.insert(0, str(ROOT))
+    import maltos_b200  # noqa: F401  (installs the short package names)
+    from maltos_b200.models import ActivationCheckpointConfig, LlamaConfig, LlamaForCausalLM, LlamaForCausalLMTpSp
+    from maltos_b200.models.common import init_normal_
+    from maltos_b200.ops import _lib
+    from maltos_b200.runtime import MeshConfig, RuntimeCore
+    from maltos_b200.runtime.optim import FusedAdamW
+
+    m = SMALL if args.small else MODEL
+    tp = world
+    cfg = LlamaConfig(vocab_size=m["vocab"], hidden_size=m["hidden"], intermediate_size=m["ffn"],
+                      num_hidden_layers=m["layers"], num_attention_heads=m["heads"], num_key_value_heads=m["kv_heads"],
+                      max_position_embeddings=m["seq_len"], rms_norm_eps=m["eps"], rope_theta=m["rope_theta"],
+                      activation_checkpointing=ActivationCheckpointConfig(enabled=True))
+    dtype = torch.bfloat16 if use_cuda else torch.float32
+    torch.manual_seed(0)
+    plugins = []
+    if tp > 1:
+        from maltos_b200.runtime.plugins.tp_sp import TpSpPlugin
+
+        plugins.append(TpSpPlugin())
+        model_cls = LlamaForCausalLMTpSp
+    else:
+        model_cls = LlamaForCausalLM
+    # Parameters are created directly in the runtime dtype on the target device (no fp32 host copy of 8B weights);
+    # under TP every rank draws the same full tensors from the same seed and keeps only its shard.
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        with torch.device(device):
+            model = model_cls(cfg)
+            init_normal_(model, 0.02)
+    finally:
+        torch.set_default_dtype(prev)
+
+    micro = args.micro_batch
+    if args.global_batch % micro:
+        raise SystemExit("--micro-batch must divide the global batch")
+    accum = args.global_batch // micro
+    runtime = RuntimeCore(model=model, mesh=MeshConfig(tp=tp), device=device, dtype=dtype if use_cuda else None,
+                          grad_accum_steps=accum, plugins=plugins,
+                          optimizer_factory=lambda params: FusedAdamW(params, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1))
+    runtime.setup()
+    runtime.model.train()
+
+    seq = m["seq_len"]
+    tokens_per_step = args.global_batch * seq
+    host = HostBatches(micro, seq, m["vocab"], seed=0, pin=use_cuda)
+    dev_batches = [{k: v.to(device) for k, v in item.items()} for item in host.items]
+
+    def one_step(source, read_loss: bool):
+        for i in range(accum):
+            batch = source.next_batch() if hasattr(source, "next_batch") else source[i % len(source)]
+            loss, should = runtime.run_step(batch)
+        assert should, "accumulation window did not close"
+        runtime.step_optimizer()
+        if read_loss:
+            return float(runtime.collect_metrics()["loss"])
+        return None
+
+    for _ in range(args.warmup):
+        one_step(dev_batches, read_loss=False)
+    barrier_sync(device)
+
+    sampler = ClockSampler(device.index if use_cuda else 0)
+    sampler.start()
+    launches0 = _lib.launch_count()
+    if use_cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_step(dev_batches, read_loss=False)
+    if use_cuda:
+        e1.record()
+        torch.cuda.synchronize(device)
+        local_ms = e0.elapsed_time(e1)
+    else:
+        local_ms = (time.perf_counter() - t0) * 1e3
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop()
+    barrier_sync(device)
+    total_ms = max_over_ranks(local_ms, device)
+    ms_per_step = total_ms / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+
+    e2e = None
+    if not args.no_e2e:
+        barrier_sync(device)
+        t0 = time.perf_counter()
+        last_loss = None
+        for _ in range(args.steps):
+            last_loss = one_step(host, read_loss=True)   # pinned host -> device every micro-step, loss -> host every step
+        if use_cuda:
+            torch.cuda.synchronize(device)
+        e2e_s = max_over_ranks(time.perf_counter() - t0, device) / args.steps
+        e2e = {"value": tokens_per_step / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": host.bytes_per_batch * accum,
+               "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "loss": last_loss}
+
+    status = _lib.fetch_status(raise_on_error=False) if use_cuda else (0, 0, 0, 0)
+    peak_gib = torch.cuda.max_memory_allocated(device) / 2**30 if use_cuda else 0.0
+    if rank == 0:
+        emit({
+            "metric": "LLaMA-8B train tokens/sec (max over ranks)" if not args.small else "SMALL plumbing check (not a benchmark)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16" if use_cuda else "fp32", "data": "synthetic uniform token ids, random-init weights",
+            "impl": "ours",
+            "config": {"model": "llama3-8b" if not args.small else "small", "layers": m["layers"], "hidden": m["hidden"],
+                       "ffn": m["ffn"], "heads": m["heads"], "kv_heads": m["kv_heads"], "vocab": m["vocab"],
+                       "global_batch": args.global_batch, "seq_len": seq, "micro_batch": micro, "grad_accum": accum,
+                       "parallelism": f"tp{tp}+sp" if tp > 1 else "single-gpu", "activation_checkpointing": "per layer",
+                       "optimizer": "fused AdamW, fp32 master weights",
+                       "l2_policy": "working set (16 GB of bf16 weights + activations per micro-step) is far larger than the 126 MB L2; no explicit flush",
+                       "baseline_note": "no published number exists for this config; the same-box reference arm is the bar"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "kernel_status": list(status),
+            "peak_mem_gib": round(peak_gib, 1),
+        })
+    runtime.close()
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------- reference arm
+def run_reference(args) -> None:
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "runtime" / "core.py").exists():
+        emit({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install of the reference into it was not done)"})
+        return
+    sys.path.insert(0, str(ref_root))
+    rank, local, world = dist_env()
+    try:
+        import torch
+
+        if world != args.gpus:
+            raise RuntimeError(f"--gpus {args.gpus} does not match WORLD_SIZE={world}")
+        use_cuda = torch.cuda.is_available() and (args.device or "cuda") != "cpu"
+        if not use_cuda and not args.small:
+            raise RuntimeError("no CUDA device")
+        device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+        if use_cuda:
+            torch.cuda.set_device(device)
+        init_distributed(world, device)
+
+        import train.cli as ref_cli      # the reference's own CLI builders (stock code path)
+        import train.flags as ref_flags
+
+        m = SMALL if args.small else MODEL
+        tp = world
+        micro = args.micro_batch
+        accum = args.global_batch // micro
+        argv = ["--model", "llama", "--dim", str(m["hidden"]), "--n-heads", str(m["heads"]), "--n-kv-heads", str(m["kv_heads"]),
+                "--hidden-size", str(m["ffn"]), "--n-layers", str(m["layers"]), "--vocab-size", str(m["vocab"]),
+                "--seq-len", str(m["seq_len"]), "--eps", str(m["eps"]), "--micro-batch-size", str(micro),
+                "--grad-accum-steps", str(accum), "--dp-size", "1", "--tp-size", str(tp), "--zero-stage", "0",
+                "--precision", "bf16" if use_cuda else "fp32", "--activation-checkpointing", "--fused-adamw",
+                "--lr", "3e-4", "--weight-decay", "0.1", "--adam-beta1", "0.9", "--adam-beta2", "0.95", "--seed", "0",
+                "--attention-backend", "flash_attn" if use_cuda else "sdpa_auto", "--disable-metrics"]
+        if tp > 1:
+            argv.append("--use-sp")
+        if not use_cuda:
+            argv.remove("--fused-adamw")
+        ref_args = ref_flags.parse_args_from(argv, require_data=False)
+        torch.manual_seed(0)
+        model = ref_cli._build_model(ref_args)
+        core = ref_cli._build_runtime(ref_args, model, device)
+        core.setup()
+        core.model.train()
+
+        seq = m["seq_len"]
+        tokens_per_step = args.global_batch * seq
+        host = HostBatches(micro, seq, m["vocab"], seed=0, pin=use_cuda)
+        dev_batches = [{k: v.to(device) for k, v in item.items()} for item in host.items]
+
+        def one_step(source, read_loss):
+            for i in range(accum):
+                batch = source.next_batch() if hasattr(source, "next_batch") else source[i % len(source)]
+                loss, should = core.run_step(batch)
+            core.step_optimizer()
+            return float(loss.detach().float().item()) if read_loss else None
+
+        for _ in range(args.warmup):
+            one_step(dev_batches, False)
+        barrier_sync(device)
+        sampler = ClockSampler(device.index if use_cuda else 0)
+        sampler.start()
+        if use_cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            one_step(dev_batches, False)
+        if use_cuda:
+            e1.record()
+            torch.cuda.synchronize(device)
+            local_ms = e0.elapsed_time(e1)
+        else:
+            local_ms = (time.perf_counter() - t0) * 1e3
+        clocks = sampler.stop()
+        barrier_sync(device)
+        ms_per_step = max_over_ranks(local_ms, device) / args.steps
+        e2e = None
+        if not args.no_e2e:
+            barrier_sync(device)
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                last = one_step(host, True)
+            if use_cuda:
+                torch.cuda.synchronize(device)
+            e2e_s = max_over_ranks(time.perf_counter() - t0, device) / args.steps
+            e2e = {"value": tokens_per_step / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": host.bytes_per_batch * accum,
+                   "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "loss": last}
+        if rank == 0:
+            emit({"metric": "LLaMA-8B train tokens/sec (max over ranks)" if not args.small else "SMALL plumbing check (not a benchmark)",
+                  "value": tokens_per_step / (ms_per_step / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                  "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+                  "vs_baseline": None, "dtype": "bf16" if use_cuda else "fp32",
+                  "data": "synthetic uniform token ids, reference default init", "impl": "reference",
+                  "config": {"model": "llama3-8b" if not args.small else "small", "global_batch": args.global_batch,
+                             "seq_len": seq, "micro_batch": micro, "grad_accum": accum,
+                             "parallelism": f"tp{tp}+sp" if tp > 1 else "single-gpu", "attention_backend": ref_args.attention_backend,
+                             "zero_stage": 0, "note": "reference CLI rejects ZeRO-1 with dp=1 and has no rope_theta flag"},
+                  "clocks": clocks, "e2e": e2e, "gpu_launches": 0})
+        core.close()
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    except BaseException as exc:  # noqa: BLE001 - the arm must always answer with one JSON line
+        if isinstance(exc, KeyboardInterrupt):
+            raise
+        if rank == 0:
+            reason = f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300]
+            emit({"impl": "reference", "unavailable": reason})
+        try:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -12,6 +12,8 @@ namespace mb {
 int* status_ptr();
 // Every launcher calls this once per kernel launch; exposed through mb_launch_count().
 void count_launch(int n = 1);
+// Makes the device's primary context current on the calling thread (first call per thread only).
+void bind_context();
 // Number of SMs of the current device (cached).
 int sm_count();
 

@@ -20,6 +20,16 @@ void set_last_error(const char* msg) {
   std::snprintf(g_last_error, sizeof(g_last_error), "%s", msg ? msg : "");
 }
 
+void bind_context() {
+  // Launchers may be entered from a thread that has made no runtime call yet (autograd worker threads): the
+  // driver-level tensor-map encoder needs the primary context current on the calling thread.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 void count_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
 int* status_ptr() {
@@ -72,6 +82,7 @@ static CUtensorMapDataType dtype_of(int elem_bytes) {
 
 bool encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
                     uint32_t box0, uint32_t box1, int elem_bytes, bool swizzle128) {
+  bind_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_last_error("cuTensorMapEncodeTiled entry point not available");
@@ -99,6 +110,7 @@ bool encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t 
 bool encode_tmap_3d(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
                     uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
                     int elem_bytes, bool swizzle128) {
+  bind_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_last_error("cuTensorMapEncodeTiled entry point not available");
