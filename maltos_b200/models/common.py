@@ -82,11 +82,34 @@ def run_layer(layer: nn.Module, x: torch.Tensor, *, use_checkpoint: bool, **kwar
     return layer(x, **kwargs)
 
 
+def _local_sequence_slice(t: torch.Tensor, group, local_len: int) -> torch.Tensor:
+    import torch.distributed as dist
+
+    rank = dist.get_rank(group)
+    return t.narrow(1, rank * local_len, local_len)
+
+
+def lm_logits(hidden: torch.Tensor, lm_head: nn.Module) -> torch.Tensor:
+    """Logits for inference. A sequence-parallel head first all-gathers the hidden states along the sequence."""
+    group = getattr(lm_head, "sp_loss_group", None)
+    if group is not None:
+        from maltos_b200.runtime.layers.functional import all_gather
+
+        hidden = all_gather(hidden, group, 1)
+    return lm_head(hidden)
+
+
 def lm_loss(hidden: torch.Tensor, lm_head: nn.Module, labels: torch.Tensor, loss_weight=None) -> torch.Tensor:
-    """Mean next-token CE of ``lm_head(hidden)`` vs already-shifted ``labels`` (fused linear+CE when the head is a
-    plain bias-free linear whose input is the full local sequence)."""
+    """Mean next-token CE of ``lm_head(hidden)`` vs already-shifted ``labels``.
+
+    Plain bias-free heads use the fused linear+CE op (no ``[tokens, vocab]`` logits kept). When the TP+SP plugin
+    marked the head sequence-parallel (``sp_loss_group``), ``hidden`` is this rank's ``[B, S/T, H]`` slice: the
+    matching label slice is scored locally and the sum / target count are reduced over the group."""
+    group = getattr(lm_head, "sp_loss_group", None)
+    if group is not None and labels.shape[1] != hidden.shape[1]:
+        labels = _local_sequence_slice(labels, group, hidden.shape[1])
     if isinstance(lm_head, nn.Linear) and lm_head.bias is None and not lm_head._forward_pre_hooks and not lm_head._forward_hooks:
-        loss = linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), lm_head.weight, labels.reshape(-1))
+        loss = linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), lm_head.weight, labels.reshape(-1), group=group)
     else:
         loss = causal_cross_entropy(lm_head(hidden), labels)
     if loss_weight is not None:

@@ -21,7 +21,7 @@ from maltos_b200.parallel.specs import (ContextParallelSpec, PipelineParallelSpe
                                         TpSpShardRule)
 
 from .activation_checkpointing import ActivationCheckpointConfig
-from .common import ParsedBatch, lm_loss, project_group, project_out, run_layer
+from .common import ParsedBatch, lm_logits, lm_loss, project_group, project_out, run_layer
 
 
 @dataclass(frozen=True)
@@ -166,6 +166,8 @@ class LlamaDecoderLayer(nn.Module):
 
 
 class LlamaForCausalLM(nn.Module):
+    handles_sequence_parallel_loss = True
+
     def __init__(self, config: LlamaConfig) -> None:
         super().__init__()
         self.config = config
@@ -194,7 +196,7 @@ class LlamaForCausalLM(nn.Module):
             return x
         h = self.norm(x)
         if b.labels is None:
-            return self.lm_head(h)
+            return lm_logits(h, self.lm_head)
         if b.input_ids is not None and b.labels.shape != b.input_ids.shape:
             raise ValueError(f"labels shape must match input_ids shape, got {b.labels.shape} vs {b.input_ids.shape}")
         return lm_loss(h, self.lm_head, b.labels, b.loss_weight)

@@ -13,7 +13,7 @@ from maltos_b200.parallel.specs import (ContextParallelSpec, ExpertParallelSpec,
                                         TpSpShardAxis, TpSpShardRule)
 from maltos_b200.runtime.types import LossOutput, PipelineOutput
 
-from .common import ParsedBatch, lm_loss
+from .common import ParsedBatch, lm_logits, lm_loss
 from .tiny_transformer import MLP, CausalSelfAttention, RmsNorm, RoPE, tiny_tp_rules
 
 
@@ -111,6 +111,8 @@ def _metric(t: torch.Tensor):
 
 
 class TinyMoETransformer(nn.Module):
+    handles_sequence_parallel_loss = True
+
     def __init__(self, dim, n_heads, n_kv_heads, hidden_size, eps, n_layers, vocab_size, max_seq_len, num_experts,
                  moe_aux_loss_coef: float = 0.0, attention_backend: str = "eager", top_k: int = 1,
                  capacity_factor: float | None = None, apply_rope: bool = False):
@@ -157,7 +159,7 @@ class TinyMoETransformer(nn.Module):
             return PipelineOutput(activation=x, auxiliary_loss=aux_loss) if want_aux else x
         h = self.norm(x)
         if b.labels is None:
-            return self.lm_head(h)
+            return lm_logits(h, self.lm_head)
         if b.input_ids is not None and b.labels.shape != b.input_ids.shape:
             raise ValueError(f"labels shape must match input_ids shape, got {b.labels.shape} vs {b.input_ids.shape}")
         ce = lm_loss(h, self.lm_head, b.labels, b.loss_weight)

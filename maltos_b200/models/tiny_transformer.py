@@ -16,7 +16,7 @@ from maltos_b200.ops.swiglu import swiglu, swiglu_packed
 from maltos_b200.parallel.specs import (ContextParallelSpec, PipelineParallelSpec, TpSpParallelSpec, TpSpShardAxis,
                                         TpSpShardRule)
 
-from .common import ParsedBatch, lm_loss, project_group, project_out
+from .common import ParsedBatch, lm_logits, lm_loss, project_group, project_out
 
 
 class _LocalCausalAttentionCore(nn.Module):
@@ -121,6 +121,8 @@ class RoPE(nn.Module):
 
 
 class TinyTransformer(nn.Module):
+    handles_sequence_parallel_loss = True
+
     def __init__(self, dim, n_heads, n_kv_heads, hidden_size, eps, n_layers, vocab_size, max_seq_len,
                  attention_backend: str = "eager", apply_rope: bool = False):
         super().__init__()
@@ -152,7 +154,7 @@ class TinyTransformer(nn.Module):
             return x
         h = self.norm(x)
         if b.labels is None:
-            return self.lm_head(h)
+            return lm_logits(h, self.lm_head)
         if b.input_ids is not None and b.labels.shape != b.input_ids.shape:
             raise ValueError(f"labels shape must match input_ids shape, got {b.labels.shape} vs {b.input_ids.shape}")
         return lm_loss(h, self.lm_head, b.labels, b.loss_weight)

@@ -59,12 +59,13 @@ def cross_entropy_mean(logits: torch.Tensor, labels: torch.Tensor, ignore_index:
 
 class _LinearCrossEntropy(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens):
+    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens, group):
         N, H = h.shape
         V = weight.shape[0]
         need_dh = ctx.needs_input_grad[0]
         need_dw = ctx.needs_input_grad[1]
-        inv = (1.0 / (labels != ignore_index).sum().clamp_min(1).to(torch.float32)).reshape(1)
+        count = _global_count(labels, ignore_index, group)
+        inv = (1.0 / count.clamp_min(1).to(torch.float32)).reshape(1)
         loss_rows = torch.empty(N, device=h.device, dtype=torch.float32)
         dh = torch.empty_like(h) if need_dh else None
         dw = torch.zeros_like(weight) if need_dw else None
@@ -81,7 +82,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
             if need_dw:
                 gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)   # dlogits^T[V,n] @ h[n,H]
         ctx.save_for_backward(dh, dw)
-        return loss_rows.sum() * inv.squeeze(0)
+        return _sum_over_group(loss_rows.sum() * inv.squeeze(0), group)
 
     @staticmethod
     def backward(ctx, dloss):
@@ -91,14 +92,53 @@ class _LinearCrossEntropy(torch.autograd.Function):
             dh = dh * g.to(dh.dtype)
         if dw is not None:
             dw = dw * g.to(dw.dtype)
-        return dh, dw, None, None, None
+        return dh, dw, None, None, None, None
+
+
+def _global_count(labels: torch.Tensor, ignore_index: int, group) -> torch.Tensor:
+    count = (labels != ignore_index).sum()
+    if group is not None:
+        import torch.distributed as dist
+
+        count = count.to(torch.float32 if labels.is_cuda else torch.float64)
+        dist.all_reduce(count, op=dist.ReduceOp.SUM, group=group)
+    return count
+
+
+def _sum_over_group(value: torch.Tensor, group) -> torch.Tensor:
+    if group is None:
+        return value
+    import torch.distributed as dist
+
+    out = value.detach().clone()
+    dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+    return out
+
+
+class _GroupSum(torch.autograd.Function):
+    """Forward: sum of the per-rank scalars over the group. Backward: identity (each rank differentiates its term)."""
+
+    @staticmethod
+    def forward(ctx, value, group):
+        return _sum_over_group(value, group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
 
 
 def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
-                         chunk_tokens: int = DEFAULT_CHUNK_TOKENS) -> torch.Tensor:
-    """Mean CE of ``h @ weight.T`` against ``labels`` without materialising all logits. ``h [N,H]``, ``weight [V,H]``."""
+                         chunk_tokens: int = DEFAULT_CHUNK_TOKENS, group=None) -> torch.Tensor:
+    """Mean CE of ``h @ weight.T`` against ``labels`` without materialising all logits. ``h [N,H]``, ``weight [V,H]``.
+
+    With ``group`` the tokens are split over the ranks of the group (sequence-parallel head): the mean is taken over
+    the targets of all ranks and the returned scalar is the same on every rank."""
     h2 = h.reshape(-1, h.shape[-1])
     lab = labels.reshape(-1)
     if _lib.use_kernels(h2, weight) and h2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
-        return _LinearCrossEntropy.apply(h2.contiguous(), weight, lab.contiguous().to(torch.long), ignore_index, chunk_tokens)
-    return cross_entropy_mean(F.linear(h2, weight), lab, ignore_index)
+        return _LinearCrossEntropy.apply(h2.contiguous(), weight, lab.contiguous().to(torch.long), ignore_index, chunk_tokens, group)
+    if group is None:
+        return cross_entropy_mean(F.linear(h2, weight), lab, ignore_index)
+    total = F.cross_entropy(F.linear(h2, weight).float(), lab, ignore_index=ignore_index, reduction="sum")
+    count = _global_count(lab, ignore_index, group).clamp_min(1)
+    return _GroupSum.apply(total / count.to(total.dtype), group)
