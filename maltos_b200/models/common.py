@@ -69,10 +69,16 @@ def project_group(x: torch.Tensor, modules: Sequence[nn.Module]) -> tuple[torch.
     return grouped_linear(x, weights)
 
 
+class Linear(nn.Linear):
+    """``nn.Linear`` (same parameters, same checkpoint names) whose forward is the tcgen05 GEMM on CUDA bf16."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return linear(x, self.weight, self.bias)
+
+
 def project_out(x: torch.Tensor, module: nn.Module) -> torch.Tensor:
-    """Output projection: plain linear, or the row-parallel module with its communication."""
-    if isinstance(module, nn.Linear):
-        return linear(x, module.weight, module.bias)
+    """Output projection through the module's own forward (plain, or row-parallel with its communication), so that
+    hooks other plugins attach to it (ZeRO-3 gathers, SP gathers) run."""
     return module(x)
 
 

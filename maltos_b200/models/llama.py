@@ -21,7 +21,7 @@ from maltos_b200.parallel.specs import (ContextParallelSpec, PipelineParallelSpe
                                         TpSpShardRule)
 
 from .activation_checkpointing import ActivationCheckpointConfig
-from .common import ParsedBatch, lm_logits, lm_loss, project_group, project_out, run_layer
+from .common import Linear, ParsedBatch, lm_logits, lm_loss, project_group, project_out, run_layer
 
 
 @dataclass(frozen=True)
@@ -103,10 +103,10 @@ class LlamaAttention(nn.Module):
             raise ValueError("num_attention_heads must be divisible by num_key_value_heads")
         self.head_dim = config.hidden_size // config.num_attention_heads
         self.rotary_emb = LlamaRotaryEmbedding(self.head_dim, config.max_position_embeddings, config.rope_theta)
-        self.q_proj = nn.Linear(config.hidden_size, self.num_heads * self.head_dim, bias=False)
-        self.k_proj = nn.Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=False)
-        self.v_proj = nn.Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=False)
-        self.o_proj = nn.Linear(config.hidden_size, config.hidden_size, bias=False)
+        self.q_proj = Linear(config.hidden_size, self.num_heads * self.head_dim, bias=False)
+        self.k_proj = Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=False)
+        self.v_proj = Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=False)
+        self.o_proj = Linear(config.hidden_size, config.hidden_size, bias=False)
         self.attn_core = _LlamaAttentionCore(config.attention_backend)
 
     def parameter_fusion_groups(self):
@@ -132,9 +132,9 @@ class LlamaMLP(nn.Module):
 
     def __init__(self, config) -> None:
         super().__init__()
-        self.gate_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
-        self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
-        self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
+        self.gate_proj = Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.up_proj = Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.down_proj = Linear(config.intermediate_size, config.hidden_size, bias=False)
 
     def parameter_fusion_groups(self):
         return [[self.gate_proj.weight, self.up_proj.weight]]
@@ -174,7 +174,7 @@ class LlamaForCausalLM(nn.Module):
         self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size)
         self.layers = nn.ModuleList([LlamaDecoderLayer(config) for _ in range(config.num_hidden_layers)])
         self.norm = LlamaRMSNorm(config.hidden_size, config.rms_norm_eps)
-        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.lm_head = Linear(config.hidden_size, config.vocab_size, bias=False)
         if config.tie_word_embeddings:
             self.lm_head.weight = self.embed_tokens.weight
 

@@ -14,7 +14,7 @@ from maltos_b200.parallel.specs import (ContextParallelSpec, PipelineParallelSpe
 from maltos_b200.runtime.layers.distributed_rmsnorm import DistributedRMSNorm
 
 from .activation_checkpointing import ActivationCheckpointConfig
-from .common import ParsedBatch, lm_logits, lm_loss, project_group, project_out, run_layer
+from .common import Linear, ParsedBatch, lm_logits, lm_loss, project_group, project_out, run_layer
 from .llama import LlamaMLP, LlamaRMSNorm, LlamaRotaryEmbedding, _LlamaAttentionCore
 
 
@@ -63,10 +63,10 @@ class OlmoAttention(nn.Module):
         self.head_dim = config.hidden_size // config.num_attention_heads
         self.rotary_emb = OlmoRotaryEmbedding(self.head_dim, config.max_position_embeddings, config.rope_theta)
         b = config.attention_bias
-        self.q_proj = nn.Linear(config.hidden_size, self.num_heads * self.head_dim, bias=b)
-        self.k_proj = nn.Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=b)
-        self.v_proj = nn.Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=b)
-        self.o_proj = nn.Linear(config.hidden_size, config.hidden_size, bias=b)
+        self.q_proj = Linear(config.hidden_size, self.num_heads * self.head_dim, bias=b)
+        self.k_proj = Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=b)
+        self.v_proj = Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=b)
+        self.o_proj = Linear(config.hidden_size, config.hidden_size, bias=b)
         self.q_norm = DistributedRMSNorm(self.num_heads * self.head_dim, config.rms_norm_eps)
         self.k_norm = DistributedRMSNorm(self.num_kv_heads * self.head_dim, config.rms_norm_eps)
         self.attn_core = _LlamaAttentionCore(config.attention_backend)
@@ -119,7 +119,7 @@ class OlmoForCausalLM(nn.Module):
         self.rotary_emb = OlmoRotaryEmbedding(head_dim, config.max_position_embeddings, config.rope_theta)
         self.layers = nn.ModuleList([OlmoDecoderLayer(config) for _ in range(config.num_hidden_layers)])
         self.norm = OlmoRMSNorm(config.hidden_size, config.rms_norm_eps)
-        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.lm_head = Linear(config.hidden_size, config.vocab_size, bias=False)
         if config.tie_word_embeddings:
             self.lm_head.weight = self.embed_tokens.weight
 

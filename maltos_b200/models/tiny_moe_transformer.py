@@ -13,7 +13,7 @@ from maltos_b200.parallel.specs import (ContextParallelSpec, ExpertParallelSpec,
                                         TpSpShardAxis, TpSpShardRule)
 from maltos_b200.runtime.types import LossOutput, PipelineOutput
 
-from .common import ParsedBatch, lm_logits, lm_loss
+from .common import Linear, ParsedBatch, lm_logits, lm_loss
 from .tiny_transformer import MLP, CausalSelfAttention, RmsNorm, RoPE, tiny_tp_rules
 
 
@@ -52,7 +52,7 @@ class TopKMoE(nn.Module):
         self._dim, self._hidden_size, self._num_experts = dim, hidden_size, num_experts
         self.top_k = top_k
         self.capacity_factor = capacity_factor
-        self.router = nn.Linear(dim, num_experts, bias=False)
+        self.router = Linear(dim, num_experts, bias=False)
         self.experts = nn.ModuleList([MLP(dim, hidden_size) for _ in range(num_experts)])
 
     @property
@@ -127,7 +127,7 @@ class TinyMoETransformer(nn.Module):
             for _ in range(n_layers)
         ])
         self.norm = RmsNorm(dim, eps)
-        self.lm_head = nn.Linear(dim, vocab_size, bias=False)
+        self.lm_head = Linear(dim, vocab_size, bias=False)
         self.moe_aux_loss_coef = float(moe_aux_loss_coef)
         self._total_moe_layers = n_layers
 

@@ -16,7 +16,7 @@ from maltos_b200.ops.swiglu import swiglu, swiglu_packed
 from maltos_b200.parallel.specs import (ContextParallelSpec, PipelineParallelSpec, TpSpParallelSpec, TpSpShardAxis,
                                         TpSpShardRule)
 
-from .common import ParsedBatch, lm_logits, lm_loss, project_group, project_out
+from .common import Linear, ParsedBatch, lm_logits, lm_loss, project_group, project_out
 
 
 class _LocalCausalAttentionCore(nn.Module):
@@ -40,10 +40,10 @@ class CausalSelfAttention(nn.Module):
         self.n_heads = n_heads
         self.n_kv_heads = n_kv_heads or n_heads
         self.apply_rope = apply_rope
-        self.q_proj = nn.Linear(dim, dim, bias=False)
-        self.k_proj = nn.Linear(dim, self.head_dim * self.n_kv_heads, bias=False)
-        self.v_proj = nn.Linear(dim, self.head_dim * self.n_kv_heads, bias=False)
-        self.o_proj = nn.Linear(dim, dim, bias=False)
+        self.q_proj = Linear(dim, dim, bias=False)
+        self.k_proj = Linear(dim, self.head_dim * self.n_kv_heads, bias=False)
+        self.v_proj = Linear(dim, self.head_dim * self.n_kv_heads, bias=False)
+        self.o_proj = Linear(dim, dim, bias=False)
         self.attn_core = _LocalCausalAttentionCore(attention_backend)
 
     def parameter_fusion_groups(self):
@@ -69,9 +69,9 @@ class MLP(nn.Module):
 
     def __init__(self, dim, hidden_size):
         super().__init__()
-        self.gate = nn.Linear(dim, hidden_size, bias=False)
-        self.up = nn.Linear(dim, hidden_size, bias=False)
-        self.down = nn.Linear(hidden_size, dim, bias=False)
+        self.gate = Linear(dim, hidden_size, bias=False)
+        self.up = Linear(dim, hidden_size, bias=False)
+        self.down = Linear(hidden_size, dim, bias=False)
 
     def parameter_fusion_groups(self):
         return [[self.gate.weight, self.up.weight]]
@@ -133,7 +133,7 @@ class TinyTransformer(nn.Module):
             for _ in range(n_layers)
         ])
         self.norm = RmsNorm(dim, eps)
-        self.lm_head = nn.Linear(dim, vocab_size, bias=False)
+        self.lm_head = Linear(dim, vocab_size, bias=False)
 
     def _embed(self, b: ParsedBatch) -> torch.Tensor:
         if b.hidden_states is not None:

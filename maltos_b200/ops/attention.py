@@ -84,3 +84,59 @@ def causal_attention(q, k, v, *, position_ids=None, sequence_ids=None, scale: fl
     order = torch.arange(S, device=q.device).unsqueeze(0).expand(B, S)
     return attention(q, k, v, q_positions=order, k_positions=order, q_sequence_ids=sequence_ids, k_sequence_ids=sequence_ids,
                      causal=True, scale=scale)
+
+
+# ------------------------------------------------------------------------------------------------ block primitives
+def attention_block_forward(q, k, v, *, q_positions, k_positions, q_sequence_ids=None, k_sequence_ids=None, scale=None):
+    """One (query block, key block) attention WITHOUT autograd: returns ``(out, lse)`` with ``lse = -inf`` and
+    ``out = 0`` for rows that see no key. Building block of ring attention; merged with :func:`merge_attention_blocks`."""
+    with torch.no_grad():
+        if _kernel_eligible(q, k, v):
+            from .flash_attn import flash_block_forward
+
+            res = flash_block_forward(q, k, v, q_positions, k_positions, q_sequence_ids, k_sequence_ids, scale)
+            if res is not None:
+                return res
+        out, lse = attention_reference(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
+                                       k_sequence_ids=k_sequence_ids, scale=scale, return_lse=True)
+        return out, lse
+
+
+def merge_attention_blocks(out_a, lse_a, out_b, lse_b):
+    """Combine two partial softmax results over disjoint key sets. ``out [B,S,h,D]`` fp32, ``lse [B,h,S]`` fp32."""
+    lse = torch.logaddexp(lse_a, lse_b)
+    wa = torch.exp(lse_a - lse).nan_to_num(0.0).permute(0, 2, 1).unsqueeze(-1)
+    wb = torch.exp(lse_b - lse).nan_to_num(0.0).permute(0, 2, 1).unsqueeze(-1)
+    return out_a * wa + out_b * wb, lse
+
+
+def attention_block_backward(q, k, v, out, lse, dout, *, q_positions, k_positions, q_sequence_ids=None, k_sequence_ids=None,
+                             scale=None):
+    """Gradients of one block given the GLOBAL output and log-sum-exp of the query rows (flash-attention backward
+    formulation): ``P = exp(S - lse)``, ``dS = P * (dO V^T - rowsum(dO * O))``. Returns fp32 ``(dq, dk, dv)``."""
+    with torch.no_grad():
+        if _kernel_eligible(q, k, v):
+            from .flash_attn import flash_block_backward
+
+            res = flash_block_backward(q, k, v, out, lse, dout, q_positions, k_positions, q_sequence_ids, k_sequence_ids, scale)
+            if res is not None:
+                return res
+        B, Sq, hq, D = q.shape
+        Sk, hkv = k.shape[1], k.shape[2]
+        g = hq // hkv
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+        qf = q.float().permute(0, 2, 1, 3).reshape(B, hkv, g, Sq, D)
+        kf = k.float().permute(0, 2, 1, 3).unsqueeze(2)
+        vf = v.float().permute(0, 2, 1, 3).unsqueeze(2)
+        of = out.float().permute(0, 2, 1, 3).reshape(B, hkv, g, Sq, D)
+        dof = dout.float().permute(0, 2, 1, 3).reshape(B, hkv, g, Sq, D)
+        scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        mask = build_visibility_mask(q_positions, k_positions, q_sequence_ids, k_sequence_ids).view(B, 1, 1, Sq, Sk)
+        p = torch.exp(scores - lse.float().reshape(B, hkv, g, Sq, 1)).masked_fill(~mask, 0.0).nan_to_num(0.0)
+        dv = torch.matmul(p.transpose(-1, -2), dof).sum(2)
+        dp = torch.matmul(dof, vf.transpose(-1, -2))
+        delta = (dof * of).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dq = torch.matmul(ds, kf).reshape(B, hq, Sq, D).permute(0, 2, 1, 3)
+        dk = torch.matmul(ds.transpose(-1, -2), qf).sum(2).permute(0, 2, 1, 3)
+        return dq.contiguous(), dk.contiguous(), dv.permute(0, 2, 1, 3).contiguous()

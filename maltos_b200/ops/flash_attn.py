@@ -27,3 +27,12 @@ def flash_attention(q, k, v, *, q_positions=None, k_positions=None, q_sequence_i
         return attention_reference(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
                                    k_sequence_ids=k_sequence_ids, causal=causal, scale=scale, return_lse=return_lse)
     raise NotImplementedError
+
+
+def flash_block_forward(q, k, v, q_positions, k_positions, q_sequence_ids, k_sequence_ids, scale):
+    """Kernel block forward returning ``(out fp32, lse)``; None when the kernel does not cover the case."""
+    return None
+
+
+def flash_block_backward(q, k, v, out, lse, dout, q_positions, k_positions, q_sequence_ids, k_sequence_ids, scale):
+    return None

@@ -418,7 +418,7 @@ class RuntimeCore:
         if not torch.is_tensor(raw):
             return
         running, n = md.get("loss_sum_for_metrics"), md.get("loss_count_for_metrics")
-        fresh = self.state.step_context.accum_start or not torch.is_tensor(running) or not isinstance(n, int)
+        fresh = self.state.step_context.microbatch_idx == 0 or not torch.is_tensor(running) or not isinstance(n, int)
         if fresh:  # new window (also after a mid-accumulation resume, where telemetry is not restored)
             md["loss_sum_for_metrics"], md["loss_count_for_metrics"] = raw.clone(), 1
         else:

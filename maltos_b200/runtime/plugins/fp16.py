@@ -1,0 +1,51 @@
+"""fp16 loss scaling: active only when the runtime dtype is float16 on CUDA. Scales the loss at PRE_BACKWARD through a
+``torch.amp.GradScaler`` kept in ``runtime.state.scaler`` (the core steps through it), checkpoints the scaler state
+(reference ``runtime/plugins/fp16.py:10-74``)."""
+from __future__ import annotations
+
+import torch
+
+from maltos_b200.runtime.plugin import PluginId, RuntimePlugin
+from maltos_b200.runtime.types import RuntimePhase, SetupPhase
+
+
+class Fp16Plugin(RuntimePlugin):
+    def __init__(self, init_scale: float = 2.0 ** 16, growth_interval: int = 2000) -> None:
+        super().__init__(id=PluginId.FP16, name="fp16")
+        self.init_scale = init_scale
+        self.growth_interval = growth_interval
+        self.scaler = None
+
+    @property
+    def active(self) -> bool:
+        rt = self.runtime
+        return rt is not None and rt.dtype == torch.float16 and torch.device(rt.device).type == "cuda"
+
+    def on_setup_phase(self, phase: SetupPhase, model):
+        if phase is SetupPhase.FINALIZE and self.active:
+            self.scaler = torch.amp.GradScaler("cuda", init_scale=self.init_scale, growth_interval=self.growth_interval)
+            self.runtime.state.scaler = self.scaler
+        return model
+
+    def on_step_phase(self, phase: RuntimePhase) -> None:
+        if phase is RuntimePhase.PRE_BACKWARD and self.scaler is not None:
+            st = self.runtime.state
+            if st.loss is not None:
+                st.metadata["raw_loss_for_metrics"] = st.loss.detach().float()
+                st.loss = self.scaler.scale(st.loss)
+
+    def export_plugin_state(self):
+        return {"scaler": self.scaler.state_dict()} if self.scaler is not None else {}
+
+    def import_plugin_state(self, state) -> None:
+        if self.scaler is not None and isinstance(state.get("scaler"), dict):
+            self.scaler.load_state_dict(state["scaler"])
+
+    def collect_metrics(self):
+        rt = self.runtime
+        out = {"dtype": str(rt.dtype).replace("torch.", "") if rt.dtype is not None else "float32"}
+        if self.scaler is not None:
+            md = rt.state.metadata
+            out["loss_scale"] = md.get("loss_scale")
+            out["overflow"] = bool(md.get("overflow", False))
+        return out

@@ -1,0 +1,359 @@
+"""ZeRO stage 3: parameters, gradients and optimizer state sharded; full parameters exist only around their use.
+
+Buckets (this order is part of the checkpoint format, reference ``runtime/plugins/zero3.py:181-240``):
+  1. parameter groups announced by other plugins through ``param_materialization_groups()`` (q/k/v and gate/up of the
+     TP+SP plugin, fused scopes), in plugin order;
+  2. every module of a ``wrap_cls`` type in ``named_modules()`` order with its direct, not yet covered parameters.
+Each bucket is a flat padded buffer whose ``1/N`` slice is this rank's ``local_param`` (what the optimizer updates and
+what ``zero3_bucket_{i}`` stores in a checkpoint).
+
+Execution: a forward-pre hook of the bucket's module all-gathers the slices into a pooled buffer and binds the
+parameters to views of it, the forward hook releases them; a backward-pre hook gathers again for the backward pass;
+when the last gradient of the bucket has been produced the flat gradient is reduce-scattered (AVG x correction) and
+added to the slice gradient, and the full parameters are released. Gradients accumulate on the slices, so the
+reduce-scatter runs every micro-step. Recompute under activation checkpointing re-enters the same hooks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from maltos_b200.runtime.buffer_allocator import BufferPolicy, acquire_buffer, release_buffer
+from maltos_b200.runtime.mesh import MeshAxis
+from maltos_b200.runtime.plugin import ParamMaterializationGroupProvider, PluginId
+from maltos_b200.runtime.types import ParamRole, RuntimePhase, SetupPhase
+from maltos_b200.state.state import ModelStateMeta
+from maltos_b200.utils.distributed import all_gather_single, reduce_scatter_single
+from maltos_b200.utils.profiling import span
+
+from .zero_common import GroupContext, ZeroPluginBase, padded_len
+
+
+@dataclass
+class ShardedBucket:
+    index: int
+    module: nn.Module
+    params: list[nn.Parameter]
+    role: ParamRole
+    group_context: GroupContext
+    param_shapes: list[tuple[int, ...]]
+    param_numels: list[int]
+    offsets: list[int]
+    total: int
+    padded: int
+    local_param: nn.Parameter = None
+    logical_names: list[str] = field(default_factory=list)
+    full_handle: object = None      # pooled buffer holding the gathered parameters while materialized
+    grad_flat: torch.Tensor | None = None
+    grad_handle: object = None
+    grads_pending: int = 0
+    users: int = 0                  # nested materialisations (recompute inside backward)
+    hook_module: nn.Module = None   # module whose forward/backward brackets the use of these parameters
+
+    @property
+    def shard_numel(self) -> int:
+        return self.padded // self.group_context.world_size
+
+    @property
+    def materialized(self) -> bool:
+        return self.full_handle is not None
+
+
+class Zero3Plugin(ZeroPluginBase):
+    def __init__(self, wrap_cls: set[type] | None = None, bucket_mb_size: int = 25) -> None:
+        super().__init__(id=PluginId.ZERO3, name="zero3", owns_optimizer=True, owns_model_state=True, bucket_mb_size=bucket_mb_size,
+                         runs_after={PluginId.TP, PluginId.TP_SP, PluginId.PP, PluginId.EP, PluginId.CP, PluginId.COMPILE})
+        self.wrap_cls = set(wrap_cls) if wrap_cls is not None else {nn.Linear}
+        self._by_param: dict[int, ShardedBucket] = {}
+        self._placeholder: dict[int, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ setup
+    def bind(self, runtime) -> None:
+        super().bind(runtime)
+        self.dp_group = runtime.get_group(MeshAxis.DP)
+        if self.dp_group is not None:
+            self.world_size, self.rank = dist.get_world_size(self.dp_group), dist.get_rank(self.dp_group)
+
+    def on_setup_phase(self, phase: SetupPhase, model: nn.Module) -> nn.Module:
+        if phase is SetupPhase.MATERIALIZE:
+            self._materialize(model)
+        elif phase is SetupPhase.FINALIZE:
+            self._register_hooks(model)
+        return model
+
+    def _wrap_types(self) -> tuple[type, ...]:
+        types = set(self.wrap_cls)
+        for t in list(types):
+            types |= set(self.runtime.get_module_replacements(t))
+        return tuple(types)
+
+    def _collect_groups(self, model: nn.Module) -> list[tuple[nn.Module, list[nn.Parameter]]]:
+        covered: set[int] = set()
+        groups: list[tuple[nn.Module, list[nn.Parameter]]] = []
+
+        def add(module, params):
+            fresh = [p for p in params if p.requires_grad and id(p) not in covered]
+            if fresh:
+                covered.update(id(p) for p in fresh)
+                groups.append((module, fresh))
+
+        for plugin in self.runtime.plugins:
+            if plugin is not self and isinstance(plugin, ParamMaterializationGroupProvider):
+                for module, params in plugin.param_materialization_groups():
+                    add(module, list(params))
+        wrap = self._wrap_types()
+        for _, module in model.named_modules():
+            if isinstance(module, wrap):
+                add(module, list(module.parameters(recurse=False)))
+        missing = [n for n, p in model.named_parameters() if p.requires_grad and id(p) not in covered]
+        if missing:
+            raise ValueError(f"Zero3Plugin: parameters not covered by wrap_cls / materialization groups: {missing[:8]}")
+        return groups
+
+    def _materialize(self, model: nn.Module) -> None:
+        rt = self.runtime
+        device = torch.device(rt.device)
+        dtype = rt.dtype
+        # this plugin owns the model state: the core did not move the model. Buffers (RoPE tables...) move here.
+        for mod in model.modules():
+            for name, buf in list(mod._buffers.items()):
+                if buf is not None:
+                    mod._buffers[name] = buf.to(device)
+        names = {id(p): n for n, p in model.named_parameters()}
+        self.buckets = []
+        self._by_param.clear()
+        for module, params in self._collect_groups(model):
+            role = rt.get_param_role(params[0])
+            gc = self._group_context_for_role(role)
+            numels = [p.numel() for p in params]
+            total = sum(numels)
+            padded = padded_len(total, max(gc.world_size, 1))
+            offsets, at = [], 0
+            for n in numels:
+                offsets.append(at)
+                at += n
+            b = ShardedBucket(index=len(self.buckets), module=module, params=params, role=role, group_context=gc,
+                              param_shapes=[tuple(p.shape) for p in params], param_numels=numels, offsets=offsets, total=total,
+                              padded=padded, logical_names=[names[id(p)] for p in params])
+            want = dtype if (dtype is not None and params[0].is_floating_point()) else params[0].dtype
+            flat = torch.zeros(padded, dtype=want, device=device)
+            with torch.no_grad():
+                for p, off, n in zip(params, offsets, numels):
+                    flat[off:off + n].copy_(p.data.reshape(-1))
+            lo = gc.rank * b.shard_numel
+            b.local_param = nn.Parameter(flat[lo:lo + b.shard_numel].clone())
+            for p in params:
+                self._by_param[id(p)] = b
+                ph = torch.empty(0, dtype=want, device=device)
+                self._placeholder[id(p)] = ph
+                p.data = ph
+            del flat
+            self.buckets.append(b)
+        self.optimizer = rt.create_optimizer([b.local_param for b in self.buckets])
+        self.scheduler = rt.create_scheduler(self.optimizer)
+
+    # ------------------------------------------------------------------ gather / release
+    def _gather(self, b: ShardedBucket) -> None:
+        b.users += 1
+        if b.materialized:
+            return
+        gc = b.group_context
+        lp = b.local_param
+        b.full_handle = acquire_buffer(shape=(b.padded,), dtype=lp.dtype, device=lp.device, policy=BufferPolicy.CACHEABLE)
+        full = b.full_handle.tensor
+        with torch.no_grad():
+            if gc.group is None or gc.world_size == 1:
+                full.copy_(lp.data)
+            else:
+                all_gather_single(full, lp.data.contiguous(), group=gc.group)
+        for p, off, n, shape in zip(b.params, b.offsets, b.param_numels, b.param_shapes):
+            p.data = full[off:off + n].view(shape)
+
+    def _release(self, b: ShardedBucket, *, force: bool = False) -> None:
+        b.users = 0 if force else max(b.users - 1, 0)
+        if b.users > 0 or not b.materialized:
+            return
+        for p in b.params:
+            p.data = self._placeholder[id(p)]
+        release_buffer(b.full_handle)
+        b.full_handle = None
+
+    def materialize_model(self) -> None:
+        """Gather every bucket (tests / export). Pair with :meth:`reshard_model`."""
+        for b in self.buckets:
+            self._gather(b)
+
+    def reshard_model(self) -> None:
+        for b in self.buckets:
+            self._release(b, force=True)
+
+    # ------------------------------------------------------------------ hooks
+    def _register_hooks(self, model: nn.Module) -> None:
+        # Projection groups (q/k/v, gate/up) are consumed by their parent block in one fused op, not through the
+        # member modules' own forward: their buckets are bracketed by the parent's forward / backward instead.
+        group_owner: dict[int, nn.Module] = {}
+        for m in model.modules():
+            groups = getattr(m, "parameter_fusion_groups", None)
+            if callable(groups):
+                for params in groups():
+                    for p in params:
+                        group_owner[id(p)] = m
+        for b in self.buckets:
+            owners = {id(group_owner.get(id(p))) for p in b.params}
+            first = group_owner.get(id(b.params[0]))
+            b.hook_module = first if (first is not None and len(owners) == 1) else b.module
+            b.hook_module.register_forward_pre_hook(self._pre_forward(b), prepend=True)
+            b.hook_module.register_forward_hook(self._post_forward(b), always_call=True)
+            b.hook_module.register_full_backward_pre_hook(self._pre_backward(b))
+            for p in b.params:
+                p.register_post_accumulate_grad_hook(self._grad_ready(b))
+
+    def _pre_forward(self, b: ShardedBucket):
+        def hook(module, args):
+            with span("maltos::zero3.materialize.forward"):
+                self._gather(b)
+
+        return hook
+
+    def _post_forward(self, b: ShardedBucket):
+        def hook(module, args, output):
+            self._release(b)
+
+        return hook
+
+    def _pre_backward(self, b: ShardedBucket):
+        def hook(module, grad_output):
+            with span("maltos::zero3.materialize.backward"):
+                if not b.materialized:
+                    self._gather(b)
+                if b.grads_pending <= 0:
+                    b.grads_pending = sum(1 for p in b.params if p.requires_grad)
+
+        return hook
+
+    def _grad_ready(self, b: ShardedBucket):
+        def hook(param: nn.Parameter) -> None:
+            if b.grad_flat is None:
+                lp = b.local_param
+                b.grad_handle = acquire_buffer(shape=(b.padded,), dtype=lp.dtype, device=lp.device, policy=BufferPolicy.TEMPORARY)
+                b.grad_flat = b.grad_handle.tensor
+                b.grad_flat.zero_()
+            i = next(k for k, p in enumerate(b.params) if p is param)
+            off, n = b.offsets[i], b.param_numels[i]
+            b.grad_flat[off:off + n].add_(param.grad.reshape(-1).to(b.grad_flat.dtype))
+            param.grad = None
+            if b.grads_pending <= 0:   # backward entered without the module-level hook (e.g. inputs need no grad)
+                b.grads_pending = sum(1 for p in b.params if p.requires_grad)
+            b.grads_pending -= 1
+            if b.grads_pending == 0:
+                self._reduce(b)
+                self._release(b, force=True)
+
+        return hook
+
+    def _reduce(self, b: ShardedBucket) -> None:
+        gc = b.group_context
+        lp = b.local_param
+        flat = b.grad_flat
+        if gc.group is None or gc.world_size == 1:
+            if gc.correction != 1.0:
+                flat.mul_(gc.correction)
+            piece = flat[: b.shard_numel]
+        else:
+            if gc.correction != 1.0:
+                flat.mul_(gc.correction)
+            piece = torch.empty(b.shard_numel, dtype=flat.dtype, device=flat.device)
+            reduce_scatter_single(piece, flat, op=dist.ReduceOp.AVG, group=gc.group)
+        if lp.grad is None:
+            lp.grad = piece.detach().clone()
+        else:
+            lp.grad.add_(piece)
+        release_buffer(b.grad_handle)
+        b.grad_flat, b.grad_handle = None, None
+
+    def on_step_phase(self, phase: RuntimePhase) -> None:
+        if phase is RuntimePhase.POST_BACKWARD:
+            with span("maltos::zero3.grad_sync.wait"):
+                for b in self.buckets:
+                    if b.grad_flat is not None:      # some parameter produced no gradient: reduce what arrived
+                        b.grads_pending = 0
+                        self._reduce(b)
+                    if b.materialized:
+                        self._release(b, force=True)
+        elif phase is RuntimePhase.PRE_STEP:
+            self._maybe_clip_local_shards()
+        elif phase is RuntimePhase.POST_LOAD:
+            sync = getattr(self.optimizer, "sync_master_params_from_model", None)
+            if callable(sync):
+                sync()
+
+    # ------------------------------------------------------------------ clipping
+    def _bucket_local_sq(self, b: ShardedBucket) -> torch.Tensor:
+        g = b.local_param.grad
+        out = torch.zeros((), dtype=torch.float64, device=b.local_param.device)
+        if g is None:
+            return out
+        lo = b.group_context.rank * b.shard_numel
+        hi = lo + b.shard_numel
+        sm = self.runtime.state_manager
+        for name, off, n in zip(b.logical_names, b.offsets, b.param_numels):
+            s, e = max(off, lo), min(off + n, hi)
+            if s < e:
+                factor = self._replica_factor(name)
+                out.add_(g[s - lo:e - lo].detach().double().pow(2).sum() / float(factor))
+        del sm
+        return out
+
+    def _replica_factor(self, name: str) -> int:
+        entry = self.runtime.state_manager.params.get(name)
+        if entry is None:
+            return 1
+        return self.runtime.grad_norm_replica_factor(entry.param)
+
+    # ------------------------------------------------------------------ metadata & model state
+    def annotate_param_metadata(self) -> None:
+        return
+
+    def export_model_state(self, state_manager):
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        tensors: dict[str, torch.Tensor] = {}
+        metas: list[ModelStateMeta] = []
+        for b in self.buckets:
+            key = f"zero3_bucket_{b.index}"
+            tensors[key] = b.local_param.detach().cpu().clone()
+            metas.append(ModelStateMeta(state_key=key, logical_names=list(b.logical_names), logical_shapes=[tuple(s) for s in b.param_shapes],
+                                        physical_shape=(b.shard_numel,), dtype=str(b.local_param.dtype), source_rank=rank))
+        for name, entry in state_manager.buffers.items():
+            tensors[name] = entry.tensor.detach().cpu().clone()
+            meta = entry.meta
+            metas.append(ModelStateMeta(meta.state_key, list(meta.logical_names), list(meta.logical_shapes), tuple(meta.physical_shape), meta.dtype, rank))
+        return tensors, metas
+
+    def import_model_state(self, state_manager, model_state) -> None:
+        by_key = {f"zero3_bucket_{b.index}": b for b in self.buckets}
+        for key, value in model_state.items():
+            if key in by_key:
+                lp = by_key[key].local_param
+                if value.numel() != lp.numel():
+                    raise ValueError(f"{key}: shard size mismatch checkpoint={value.numel()} runtime={lp.numel()}")
+                lp.data.copy_(value.to(device=lp.device, dtype=lp.dtype).reshape(-1))
+            elif key in state_manager.buffers:
+                dst = state_manager.buffers[key].tensor
+                dst.copy_(value.to(device=dst.device, dtype=dst.dtype))
+            else:
+                raise KeyError(f"model state not found: {key}")
+
+    def export_plugin_state(self):
+        if self.runtime.state.step_context.microbatch_idx == 0:
+            return {}
+        return {"bucket_local_grads": [None if b.local_param.grad is None else b.local_param.grad.detach().cpu().clone() for b in self.buckets]}
+
+    def import_plugin_state(self, state) -> None:
+        grads = state.get("bucket_local_grads")
+        if isinstance(grads, list):
+            for b, g in zip(self.buckets, grads):
+                if g is not None:
+                    b.local_param.grad = g.to(device=b.local_param.device, dtype=b.local_param.dtype)

@@ -111,6 +111,8 @@ class PipelineStepRunner:
             st.pending_sends.clear()
         loss = self.broadcast_loss(runtime=runtime, total_loss=totals["loss"], total_auxiliary_loss=totals["aux"], batch=pieces[0])
         runtime.state.loss = loss
+        # the metric of this micro-step is the mean loss over its pipeline micro-batches, on every stage
+        runtime.state.metadata["raw_loss_for_metrics"] = loss.detach().float()
         return loss
 
     @property
