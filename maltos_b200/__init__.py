@@ -79,7 +79,9 @@ def install_aliases(force: bool = False) -> list[str]:
         _finder.enabled.add(name)
         installed.append(name)
     if _finder not in sys.meta_path:
-        sys.meta_path.append(_finder)
+        # In front of the path finder: `runtime.types` must resolve to the SAME module object as
+        # `maltos_b200.runtime.types`, not to a second copy loaded from the aliased package's __path__.
+        sys.meta_path.insert(0, _finder)
     return installed
 
 

@@ -26,10 +26,10 @@ class MetricPlugin(RuntimePlugin):
             self._t0 = None
             dev = torch.device(self.runtime.device)
             if self.include_cuda_memory and dev.type == "cuda":
-                gib = 1024.0 ** 3
-                self._pending["memory/allocated_gib"] = torch.cuda.memory_allocated(dev) / gib
-                self._pending["memory/reserved_gib"] = torch.cuda.memory_reserved(dev) / gib
-                self._pending["memory/max_allocated_gib"] = torch.cuda.max_memory_allocated(dev) / gib
+                self._pending["memory/allocated_gb"] = torch.cuda.memory_allocated(dev) / 1e9
+                self._pending["memory/reserved_gb"] = torch.cuda.memory_reserved(dev) / 1e9
+                self._pending["memory/max_allocated_gb"] = torch.cuda.max_memory_allocated(dev) / 1e9
+                self._pending["memory/max_reserved_gb"] = torch.cuda.max_memory_reserved(dev) / 1e9
 
     def collect_metrics(self):
         out, self._pending = self._pending, {}

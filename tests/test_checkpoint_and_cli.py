@@ -1,0 +1,120 @@
+"""Checkpoint format: cross-loading with the unmodified reference in both directions, manifest validation errors,
+resume == continuous training. Reference checks are skipped when ``baseline/_ref`` is not installed."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+REF = ROOT / "baseline" / "_ref"
+
+FLAGS = ("--model llama --dim 64 --n-heads 4 --n-kv-heads 2 --hidden-size 128 --n-layers 2 --vocab-size 256 --seq-len 32 "
+         "--micro-batch-size 2 --grad-accum-steps 2 --log-every 1 --checkpoint-every 2 --grad-clip 1.0").split()
+
+
+@pytest.fixture(scope="module")
+def shards(tmp_path_factory):
+    d = tmp_path_factory.mktemp("tokens")
+    rng = np.random.default_rng(0)
+    for i in range(2):
+        rng.integers(0, 256, size=5000, dtype=np.uint32).tofile(d / f"tokens_{i:05d}.bin")
+    return d
+
+
+def _run(cmd, cwd, env_extra=None):
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    env.update(env_extra or {})
+    out = subprocess.run(cmd, cwd=cwd, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    return [l for l in out.stdout.splitlines() if l.startswith("[step")]
+
+
+def _ours(shards, ckpt, steps, resume=None):
+    cmd = [sys.executable, "-m", "maltos_b200.tools.train", "--data", str(shards), *FLAGS, "--max-steps", str(steps), "--checkpoint-dir", str(ckpt)]
+    if resume:
+        cmd += ["--resume-from", str(resume)]
+    return _run(cmd, ROOT)
+
+
+def _reference(shards, ckpt, steps, resume=None):
+    cmd = [sys.executable, "tools/train.py", "--data", str(shards), *FLAGS, "--max-steps", str(steps), "--checkpoint-dir", str(ckpt)]
+    if resume:
+        cmd += ["--resume-from", str(resume)]
+    return _run(cmd, REF, {"PYTHONPATH": str(REF)})
+
+
+def _losses(lines):
+    return [l.split("loss ")[1].split(" ")[0] for l in lines]
+
+
+def test_resume_equals_continuous(shards, tmp_path):
+    full = _losses(_ours(shards, tmp_path / "a", 4))
+    _ours(shards, tmp_path / "b", 2)
+    tail = _losses(_ours(shards, tmp_path / "b", 4, resume=tmp_path / "b" / "step_00000002"))
+    assert tail == full[2:]
+
+
+@pytest.mark.skipif(not (REF / "runtime" / "core.py").exists(), reason="reference not installed under baseline/_ref")
+def test_cross_load_with_reference(shards, tmp_path):
+    ours_first = _losses(_ours(shards, tmp_path / "ours", 2))
+    ref_continue = _losses(_reference(shards, tmp_path / "ours", 4, resume=tmp_path / "ours" / "step_00000002"))
+    ref_first = _losses(_reference(shards, tmp_path / "ref", 2))
+    ours_continue = _losses(_ours(shards, tmp_path / "ref", 4, resume=tmp_path / "ref" / "step_00000002"))
+    assert ours_first == ref_first
+    assert ref_continue == ours_continue
+    m_ours = json.loads((tmp_path / "ours" / "step_00000002" / "manifest.json").read_text())
+    m_ref = json.loads((tmp_path / "ref" / "step_00000002" / "manifest.json").read_text())
+    assert m_ours == m_ref
+    assert (tmp_path / "ours" / "runtime_spec.json").read_bytes() == (tmp_path / "ref" / "runtime_spec.json").read_bytes()
+
+
+def _tiny_runtime():
+    import maltos_b200  # noqa: F401
+    from maltos_b200.models import TinyModel
+    from maltos_b200.runtime import RuntimeCore
+
+    torch.manual_seed(0)
+    rt = RuntimeCore(model=TinyModel(), optimizer_factory=lambda p: torch.optim.AdamW(p, lr=1e-2))
+    rt.setup()
+    return rt
+
+
+def test_manifest_validation_errors(tmp_path):
+    from maltos_b200.state import load_sharded_checkpoint, save_sharded_checkpoint
+
+    rt = _tiny_runtime()
+    rt.run_step(torch.randn(4, 32))
+    rt.step_optimizer()
+    ckpt = tmp_path / "step_00000001"
+    save_sharded_checkpoint(rt.state_manager, ckpt)
+    with pytest.raises(FileExistsError):
+        save_sharded_checkpoint(rt.state_manager, ckpt)
+    good = json.loads((ckpt / "manifest.json").read_text())
+
+    def corrupt(mutate, match):
+        bad = json.loads(json.dumps(good))
+        mutate(bad)
+        (ckpt / "manifest.json").write_text(json.dumps(bad))
+        with pytest.raises(ValueError, match=match):
+            load_sharded_checkpoint(_tiny_runtime().state_manager, ckpt)
+
+    corrupt(lambda m: m.pop("artifacts"), "missing artifacts")
+    corrupt(lambda m: m.update(world_size=2), "world_size mismatch")
+    corrupt(lambda m: m.update(version=7), "unsupported checkpoint manifest version")
+    corrupt(lambda m: m["artifacts"].append(dict(m["artifacts"][0])), "duplicate artifact")
+    corrupt(lambda m: m["ranks"][0]["entries"][0].update(source_rank=5), "source rank out of range")
+    corrupt(lambda m: m.update(optimizer_source_ranks=[3]), "optimizer source rank out of range")
+    corrupt(lambda m: m.update(artifacts=[a for a in m["artifacts"] if a["kind"] != "trainer"]), "missing trainer artifact")
+    (ckpt / "manifest.json").write_text(json.dumps(good))
+    fresh = _tiny_runtime()
+    load_sharded_checkpoint(fresh.state_manager, ckpt)
+    for (n, a), (_, b) in zip(rt.model.named_parameters(), fresh.model.named_parameters()):
+        assert torch.equal(a, b), n
+    assert fresh.state.step_context.step == 1
+    with pytest.raises(RuntimeError, match="insufficient free space"):
+        save_sharded_checkpoint(rt.state_manager, tmp_path / "step_00000002", min_free_gb=1e9)
