@@ -45,6 +45,7 @@ def parse_args(argv=None):
     ap.add_argument("--small", action="store_true", help="tiny model/sequence: plumbing check only, NOT a benchmark number")
     ap.add_argument("--device", default=None, help="override device (cpu allowed only with --small)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
+    ap.add_argument("--layers", type=int, default=None, help="debugging only: fewer layers (the JSON line is then marked invalid)")
     return ap.parse_args(argv)
 
 
@@ -207,7 +208,9 @@ def run_ours(args) -> None:
     from maltos_b200.runtime import MeshConfig, RuntimeCore
     from maltos_b200.runtime.optim import FusedAdamW
 
-    m = SMALL if args.small else MODEL
+    m = dict(SMALL if args.small else MODEL)
+    if args.layers is not None:
+        m["layers"] = args.layers
     tp = world
     cfg = LlamaConfig(vocab_size=m["vocab"], hidden_size=m["hidden"], intermediate_size=m["ffn"],
                       num_hidden_layers=m["layers"], num_attention_heads=m["heads"], num_key_value_heads=m["kv_heads"],
@@ -302,7 +305,7 @@ def run_ours(args) -> None:
     peak_gib = torch.cuda.max_memory_allocated(device) / 2**30 if use_cuda else 0.0
     if rank == 0:
         emit({
-            "metric": "LLaMA-8B train tokens/sec (max over ranks)" if not args.small else "SMALL plumbing check (not a benchmark)",
+            "metric": "LLaMA-8B train tokens/sec (max over ranks)" if not (args.small or args.layers) else "REDUCED MODEL plumbing check (not a benchmark)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16" if use_cuda else "fp32", "data": "synthetic uniform token ids, random-init weights",
