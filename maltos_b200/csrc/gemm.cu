@@ -37,6 +37,96 @@ struct GemmArgs {
   int* status;
 };
 
+// Sequence-parallel all-gather fused into the GEMM (A operand = rows gathered from all ranks of the TP group).
+// The first `push_ctas` blocks of the grid copy this rank's rows into every peer's gathered buffer over NVLink and
+// publish a per-source flag; the GEMM blocks start with this rank's own rows and visit the other sources in ring
+// order, waiting (bounded) for a source's flag only when they reach its rows. Signal-pad words (uint32):
+//   [buf*8 + src]        arrived : rows of `src` are complete in my gathered buffer `buf`      (written by src)
+//   [16 + buf*8 + rank]  consumed: `rank` has finished reading ITS gathered buffer `buf`       (written by rank)
+//   [32]                 finished GEMM blocks of the running call (local)   [40 + dst] finished push blocks (local)
+constexpr int kMaxPeers = 8;
+struct GatherArgs {
+  int enabled;
+  int push_ctas;
+  int rank, world;
+  int batches;            // B
+  int rows_per_chunk;     // S / T rows of one rank per batch
+  const __nv_bfloat16* x_local;   // [B * rows_per_chunk, K] (row stride x_ld)
+  long long x_ld;
+  unsigned seq;           // sequence number of this call (1, 2, ...); buffer = seq & 1
+  long long buf_elems;    // elements of one gathered buffer (B * S * K)
+  unsigned long long gathered[kMaxPeers];   // base address of every rank's gathered buffers, as mapped here
+  unsigned long long pads[kMaxPeers];       // base address of every rank's signal pad, as mapped here
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// Wait until *flag has reached `want` (sequence numbers, wrap-safe). Bounded: false after the deadline.
+__device__ __forceinline__ bool wait_flag_reached(const unsigned* flag, unsigned want, volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  while (true) {
+    if (static_cast<int>(ld_acquire_sys(flag) - want) >= 0) return true;
+    if (abort_flag && *abort_flag) return false;
+    if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
+    __nanosleep(200);
+  }
+}
+
+// Body of a push block: copies x_local into slot `rank` of every rank's gathered buffer, local copy first.
+__device__ void gather_push_role(const GatherArgs& g, int K, int* status) {
+  __shared__ int s_ok;
+  const int buf = static_cast<int>(g.seq & 1u);
+  const long long vec_per_row = K >> 3;
+  const long long rows_local = static_cast<long long>(g.batches) * g.rows_per_chunk;
+  const long long total_vec = rows_local * vec_per_row;
+  const long long s_rows = static_cast<long long>(g.rows_per_chunk) * g.world;   // rows of one batch in the gathered buffer
+  unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
+  for (int step = 0; step < g.world; ++step) {
+    const int dst = (g.rank + step) % g.world;
+    if (threadIdx.x == 0) {
+      // the destination must have finished the call that last used this buffer (two calls ago)
+      bool ok = step == 0 ? true : wait_flag_reached(my_pad + 16 + buf * 8 + dst, g.seq - 2u, nullptr);
+      if (step == 0) ok = wait_flag_reached(my_pad + 16 + buf * 8 + g.rank, g.seq - 2u, nullptr);
+      if (!ok) {
+        atomicOr(&status[0], MB_ERR_PEER_TIMEOUT);
+        status[2] = dst;
+      }
+      s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(g.gathered[dst]) + static_cast<long long>(buf) * g.buf_elems;
+    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total_vec;
+         v += static_cast<long long>(g.push_ctas) * blockDim.x) {
+      const long long row = v / vec_per_row, c = v - row * vec_per_row;
+      const long long b = row / g.rows_per_chunk, i = row - b * g.rows_per_chunk;
+      const uint4 val = *reinterpret_cast<const uint4*>(g.x_local + row * g.x_ld + c * 8);
+      const long long drow = b * s_rows + static_cast<long long>(g.rank) * g.rows_per_chunk + i;
+      *reinterpret_cast<uint4*>(out + drow * K + c * 8) = val;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned done = atomicAdd(my_pad + 40 + dst, 1u);
+      if (done == static_cast<unsigned>(g.push_ctas - 1)) {   // last push block for this destination publishes the flag
+        atomicExch(my_pad + 40 + dst, 0u);
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<unsigned*>(g.pads[dst]) + buf * 8 + g.rank, g.seq);
+      }
+    }
+    __syncthreads();
+  }
+}
+
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
   const int per_group = kGroupM * tiles_n;
   const int group = tile / per_group;
@@ -49,7 +139,15 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p,
+                 const __grid_constant__ GatherArgs g) {
+  if (g.enabled && static_cast<int>(blockIdx.x) < g.push_ctas) {
+    gather_push_role(g, p.K, p.status);   // push blocks never touch TMEM or the smem pipeline
+    return;
+  }
+  const int first_cta = g.enabled ? g.push_ctas : 0;
+  const int cta = static_cast<int>(blockIdx.x) - first_cta;
+  const int n_ctas = static_cast<int>(gridDim.x) - first_cta;
   constexpr int A_BYTES = kBM * kBK * 2;
   constexpr int B_BYTES = BN * kBK * 2;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -98,9 +196,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int s_rows = g.enabled ? g.rows_per_chunk * g.world : 1;
+      const int m_rot = g.enabled ? (g.rank * g.rows_per_chunk) / kBM : 0;
+      const int gbuf = static_cast<int>(g.seq & 1u);
+      const unsigned* my_pad = g.enabled ? reinterpret_cast<const unsigned*>(g.pads[g.rank]) : nullptr;
+      for (int tile = cta; ok && tile < total_tiles; tile += n_ctas) {
         int m_blk, n_blk;
         tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
+        if (g.enabled) {
+          // own rows first, then the other sources in ring order; wait for a source only when its rows are needed
+          m_blk = (m_blk + m_rot) % p.tiles_m;
+          const int row_lo = m_blk * kBM, row_hi = min(row_lo + kBM, p.M) - 1;
+          const int src_lo = (row_lo % s_rows) / g.rows_per_chunk, src_hi = (row_hi % s_rows) / g.rows_per_chunk;
+          bool ready = wait_flag_reached(my_pad + gbuf * 8 + src_lo, g.seq, abort_flag);
+          if (ready && src_hi != src_lo) ready = wait_flag_reached(my_pad + gbuf * 8 + src_hi, g.seq, abort_flag);
+          if (!ready) {
+            *abort_flag = 1;
+            atomicOr(&p.status[0], MB_ERR_PEER_TIMEOUT);
+            p.status[2] = src_lo;
+            ok = false;
+            break;
+          }
+          fence_proxy_async_global();   // peers' generic-proxy stores -> this thread's TMA (async proxy) reads
+        }
         const int m0 = m_blk * kBM, n0 = n_blk * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
@@ -143,7 +261,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = cta; ok && tile < total_tiles; tile += n_ctas) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -181,9 +299,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const int m_rot_e = g.enabled ? (g.rank * g.rows_per_chunk) / kBM : 0;
+    for (int tile = cta; tile < total_tiles; tile += n_ctas) {
       int m_blk, n_blk;
       tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
+      if (g.enabled) m_blk = (m_blk + m_rot_e) % p.tiles_m;
       bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -274,10 +394,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (g.enabled && threadIdx.x == 0 && !*abort_flag) {
+    // the last GEMM block to finish tells every rank that this rank's gathered buffer may be overwritten
+    unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
+    const unsigned done = atomicAdd(my_pad + 32, 1u);
+    if (done == static_cast<unsigned>(n_ctas - 1)) {
+      atomicExch(my_pad + 32, 0u);
+      __threadfence_system();
+      const int gbuf = static_cast<int>(g.seq & 1u);
+      for (int r = 0; r < g.world; ++r) st_release_sys(reinterpret_cast<unsigned*>(g.pads[r]) + 16 + gbuf * 8 + g.rank, g.seq);
+    }
+  }
 }
 
 template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& args, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& args, cudaStream_t stream,
+                       const GatherArgs* gather = nullptr) {
   constexpr size_t smem = 1024 + STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 256;
   static bool configured[64] = {false};
   int dev = 0;
@@ -289,8 +421,16 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   }
   args.tiles_n = (args.N + BN - 1) / BN;
   const int total = args.tiles_m * args.tiles_n;
-  const int grid = total < sm_count() ? total : sm_count();
-  gemm_bf16_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, args);
+  GatherArgs g;
+  if (gather) {
+    g = *gather;
+  } else {
+    g.enabled = 0;
+    g.push_ctas = 0;
+  }
+  int grid = total < sm_count() ? total : sm_count();
+  if (g.enabled) grid += g.push_ctas;   // push blocks are small and share SMs with the GEMM blocks
+  gemm_bf16_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, args, g);
   count_launch();
   MB_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -363,4 +503,64 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   if (!ok) return -4;
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream);
   return launch_gemm<128, 6>(tmA, tmB, args, stream);
+}
+
+// Sequence-parallel all-gather fused into a column-parallel GEMM:
+//   C[B*S, N] = gather_over_ranks(x_local)[B*S, K] @ W[N, K]^T
+// x_local is this rank's [B * rows_per_chunk, K] slice (row stride x_ld). `gathered` / `pads` hold, for every rank of
+// the group, the address at which that rank's double-buffered gathered buffer / signal pad is mapped in this process.
+// `seq` is the call's sequence number (same on every rank, starting at 1, +1 per call on this context).
+MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int rows_per_chunk, const void* W,
+                           long long ldb, void* C, long long ldc, int N, int K, int rank, int world, unsigned seq,
+                           const unsigned long long* gathered, const unsigned long long* pads, long long buf_elems,
+                           int push_ctas, cudaStream_t stream) {
+  using namespace mb;
+  if (world < 2 || world > kMaxPeers) {
+    set_last_error("mb_ag_gemm_bf16: group size must be in [2, 8]");
+    return -1;
+  }
+  if ((K & 7) || (x_ld & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(x_local) & 15) ||
+      (reinterpret_cast<uintptr_t>(W) & 15)) {
+    set_last_error("mb_ag_gemm_bf16: operands must be 16-byte aligned with K and leading dimensions multiple of 8");
+    return -2;
+  }
+  const long long M = static_cast<long long>(batches) * rows_per_chunk * world;
+  if (M * K > buf_elems) {
+    set_last_error("mb_ag_gemm_bf16: gathered buffer too small");
+    return -3;
+  }
+  int* status = status_ptr();
+  if (!status) return -4;
+  GemmArgs args;
+  args.C = C;
+  args.bias = nullptr;
+  args.ldc = ldc;
+  args.M = static_cast<int>(M), args.N = N, args.K = K;
+  args.a_mn = 0, args.b_mn = 0;
+  args.out_fp32 = 0, args.accumulate = 0;
+  args.tiles_m = (args.M + kBM - 1) / kBM;
+  args.k_blocks = (K + kBK - 1) / kBK;
+  args.status = status;
+  args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
+  args.b_lbo = 16u, args.b_sbo = 1024u, args.b_kstep = 32u;
+  GatherArgs g;
+  g.enabled = 1;
+  g.push_ctas = push_ctas > 0 ? push_ctas : 16;
+  g.rank = rank, g.world = world;
+  g.batches = batches, g.rows_per_chunk = rows_per_chunk;
+  g.x_local = static_cast<const __nv_bfloat16*>(x_local);
+  g.x_ld = x_ld;
+  g.seq = seq;
+  g.buf_elems = buf_elems;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    g.gathered[r] = r < world ? gathered[r] : 0ull;
+    g.pads[r] = r < world ? pads[r] : 0ull;
+  }
+  const __nv_bfloat16* a_base = reinterpret_cast<const __nv_bfloat16*>(gathered[rank]) + static_cast<long long>(seq & 1u) * buf_elems;
+  const int bn = (N <= 128 || static_cast<long long>(args.tiles_m) * ((N + 255) / 256) < sm_count()) ? 128 : 256;
+  CUtensorMap tmA, tmB;
+  if (!encode_tmap_2d(&tmA, a_base, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM, 2, true)) return -5;
+  if (!encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true)) return -5;
+  if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream, &g);
+  return launch_gemm<128, 6>(tmA, tmB, args, stream, &g);
 }

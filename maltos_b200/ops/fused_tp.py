@@ -1,0 +1,143 @@
+"""Tensor/sequence-parallel linear ops with the collective inside the GEMM kernel (``csrc/gemm.cu``).
+
+``all_gather_grouped_linear``: the SP all-gather of ``x [B, S/T, H]`` and the q/k/v (gate/up) projection are ONE launch:
+push blocks of the kernel store this rank's rows into every peer's gathered buffer over NVLink (plain P2P stores into
+CUDA-IPC mapped memory, per-source flags), while the tcgen05 GEMM blocks start on the rows that are already local and
+reach a peer's rows only after its flag arrived - the transfer hides behind the math tile by tile. Buffers are
+double-buffered by call parity and a "consumed" flag keeps a fast rank from overwriting a buffer a slow rank still reads.
+
+Backward (and the GEMM -> reduce-scatter of row-parallel layers) currently use NCCL collectives around the tcgen05 GEMMs.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .gemm import gemm
+from .grouped import _fused_view, _memory_order
+
+PUSH_CTAS = 16
+
+
+def _nccl_all_gather_rows(x2: torch.Tensor, ctx, B: int, rows: int) -> torch.Tensor:
+    """[B*rows, K] local slices -> [B*rows*T, K] in batch-major, rank-minor order."""
+    T = ctx.world
+    K = x2.shape[1]
+    out = torch.empty((T, B * rows, K), dtype=x2.dtype, device=x2.device)
+    dist.all_gather_into_tensor(out.view(T * B * rows, K), x2.contiguous(), group=ctx.group)
+    if B == 1:
+        return out.view(T * rows, K)
+    return out.view(T, B, rows, K).permute(1, 0, 2, 3).reshape(B * T * rows, K)
+
+
+def _nccl_reduce_scatter_rows(y_full: torch.Tensor, ctx, B: int, rows: int) -> torch.Tensor:
+    """[B*T*rows, K] (batch-major) -> sum over ranks of this rank's [B*rows, K] slice."""
+    T = ctx.world
+    K = y_full.shape[1]
+    src = y_full if B == 1 else y_full.view(B, T, rows, K).permute(1, 0, 2, 3).reshape(T * B * rows, K)
+    out = torch.empty((B * rows, K), dtype=y_full.dtype, device=y_full.device)
+    dist.reduce_scatter_tensor(out, src.contiguous(), op=dist.ReduceOp.SUM, group=ctx.group)
+    return out
+
+
+class _AllGatherGroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, symm, *weights):
+        B, rows, K = x_local.shape
+        T = symm.world
+        order = _memory_order(weights)
+        fused = _fused_view(weights, order) if order is not None else torch.cat([w for w in weights], dim=0)
+        layout = order if order is not None else list(range(len(weights)))
+        N = fused.shape[0]
+        x2 = x_local.reshape(B * rows, K)
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        M = B * rows * T
+        buf_elems = M * K
+        buf = symm.ensure_buffer("sp_gather", 2 * buf_elems * 2)
+        seq = symm.next_seq()
+        out = torch.empty((M, N), dtype=x_local.dtype, device=x_local.device)
+        gathered = (ctypes.c_ulonglong * 8)(*(buf.peer_ptrs + [0] * (8 - T)))
+        pads = (ctypes.c_ulonglong * 8)(*(symm.pad.peer_ptrs + [0] * (8 - T)))
+        rc = _lib.lib().mb_ag_gemm_bf16(
+            _lib.ptr(x2), _lib.c_ll(x2.stride(0)), _lib.c_int(B), _lib.c_int(rows), _lib.ptr(fused), _lib.c_ll(fused.stride(0)),
+            _lib.ptr(out), _lib.c_ll(out.stride(0)), _lib.c_int(N), _lib.c_int(K), _lib.c_int(symm.rank), _lib.c_int(T),
+            ctypes.c_uint(seq & 0xFFFFFFFF), gathered, pads, _lib.c_ll(buf_elems), _lib.c_int(PUSH_CTAS), _lib.stream_ptr())
+        _lib.check(rc, "mb_ag_gemm_bf16")
+        ctx.save_for_backward(x2, *weights)
+        ctx.symm, ctx.layout, ctx.fused_ok = symm, layout, order is not None
+        ctx.dims = (B, rows, K, N)
+        return out.view(B, rows * T, N)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, *weights = ctx.saved_tensors
+        B, rows, K, N = ctx.dims
+        symm = ctx.symm
+        d2 = dout.reshape(-1, N)
+        if d2.stride(1) != 1 or d2.stride(0) % 8:
+            d2 = d2.contiguous()
+        fused = _fused_view(weights, ctx.layout) if ctx.fused_ok else torch.cat(list(weights), dim=0)
+        dx_local = None
+        dws = [None] * len(weights)
+        if ctx.needs_input_grad[0]:
+            dx_full = gemm(d2, fused, b_mn=True)                       # [B*S, K]
+            dx_local = _nccl_reduce_scatter_rows(dx_full, symm, B, rows).view(B, rows, K)
+        if any(ctx.needs_input_grad[2:]):
+            x_full = _nccl_all_gather_rows(x2, symm, B, rows)          # re-gathered, as the forward buffer is recycled
+            dwf = gemm(d2, x_full, a_mn=True, b_mn=True)               # [N, K]
+            at = 0
+            for i in ctx.layout:
+                n = weights[i].shape[0]
+                dws[i] = dwf[at:at + n]
+                at += n
+        return (dx_local, None, *dws)
+
+
+def all_gather_grouped_linear(x_local: torch.Tensor, weights, symm, *, seq_dim: int = 1):
+    """``x_local [B, S/T, H]`` -> ``(packed [B, S, sum(out_i)], column offsets)``; see module docstring."""
+    if seq_dim != 1 or x_local.dim() != 3:
+        raise ValueError("all_gather_grouped_linear expects [batch, sequence/T, hidden] with the sequence on dim 1")
+    weights = list(weights)
+    order = _memory_order(weights)
+    layout = order if order is not None else list(range(len(weights)))
+    offs = [0] * len(weights)
+    at = 0
+    for i in layout:
+        offs[i] = at
+        at += weights[i].shape[0]
+    return _AllGatherGroupedLinear.apply(x_local, symm, *weights), offs
+
+
+class _LinearReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, symm):
+        B, S, Kin = x.shape
+        T = symm.world
+        rows = S // T
+        x2 = x.reshape(B * S, Kin)
+        y_full = gemm(x2, weight)                                       # partial sums [B*S, H]
+        y = _nccl_reduce_scatter_rows(y_full, symm, B, rows)
+        ctx.save_for_backward(x2, weight)
+        ctx.symm, ctx.dims = symm, (B, S, rows, Kin)
+        return y.view(B, rows, weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        B, S, rows, Kin = ctx.dims
+        H = weight.shape[0]
+        dy_full = _nccl_all_gather_rows(dy.reshape(B * rows, H), ctx.symm, B, rows)   # [B*S, H]
+        dx = gemm(dy_full, weight, b_mn=True).view(B, S, Kin) if ctx.needs_input_grad[0] else None
+        dw = gemm(dy_full, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, symm, *, seq_dim: int = 1) -> torch.Tensor:
+    """Row-parallel ``x [B, S, in/T] @ W^T`` followed by reduce-scatter along the sequence -> ``[B, S/T, out]``."""
+    if seq_dim != 1 or x.dim() != 3:
+        raise ValueError("linear_reduce_scatter expects [batch, sequence, in/T] with the sequence on dim 1")
+    return _LinearReduceScatter.apply(x, weight, symm)

@@ -1,0 +1,88 @@
+"""Fused all-gather -> GEMM over NVLink peer memory against NCCL all-gather + fp32 matmul, on 2 GPUs."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.dist_utils import free_port
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _worker(rank, world, port, queue):
+    import io
+    import traceback
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import maltos_b200  # noqa: F401
+        from maltos_b200.ops import _lib, comm
+        from maltos_b200.ops.fused_tp import all_gather_grouped_linear
+        from maltos_b200.ops.grouped import fuse_parameters
+
+        group = dist.new_group(list(range(world)))
+        ctx = comm.context_for(group)
+        assert ctx is not None, comm.disabled_reason(group)
+        results = []
+        torch.manual_seed(7)   # same weights everywhere
+        for (B, rows, K, outs) in [(1, 256, 256, (256, 128, 128)), (2, 192, 512, (384, 384)), (1, 1024, 1024, (1024, 256, 256)),
+                                   (1, 256, 256, (256, 128, 128))]:
+            ws = [torch.nn.Parameter((torch.randn(n, K, device="cuda") * 0.05).bfloat16()) for n in outs]
+            fuse_parameters(ws)
+            g = torch.Generator(device="cuda").manual_seed(100 + rank)
+            for rep in range(3):          # several calls: both buffer parities and the consumed handshake
+                x = torch.randn(B, rows, K, device="cuda", generator=g).bfloat16().requires_grad_()
+                y, offs = all_gather_grouped_linear(x, ws, ctx)
+                full = torch.empty(world, B, rows, K, device="cuda", dtype=torch.bfloat16)
+                dist.all_gather_into_tensor(full.view(-1, K), x.detach().reshape(-1, K).contiguous(), group=group)
+                xf = full.permute(1, 0, 2, 3).reshape(B, world * rows, K).float()
+                ref = torch.cat([xf @ w.detach().float().t() for w in ws], dim=-1)
+                err = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+                dy = torch.randn_like(y)
+                y.backward(dy)
+                dyf = dy.float()
+                dx_full = dyf @ torch.cat([w.detach().float() for w in ws], 0)
+                dist.all_reduce(dx_full, group=group)
+                dx_ref = dx_full.view(B, world, rows, K)[:, rank]
+                gerr = ((x.grad.float() - dx_ref).abs().max() / dx_ref.abs().max()).item()
+                results.append((B, rows, K, rep, err, gerr))
+                for w in ws:
+                    w.grad = None
+        status = _lib.fetch_status(raise_on_error=False)
+        queue.put((rank, "ok", (results, status)))
+        ctx.close()
+    except BaseException:  # noqa: BLE001
+        queue.put((rank, "error", traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_fused_all_gather_gemm_two_gpus():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = {}
+    try:
+        for _ in range(world):
+            rank, status, payload = q.get(timeout=240)
+            assert status == "ok", payload
+            out[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    for rank, (results, status) in out.items():
+        assert status[0] == 0, f"rank {rank} kernel status {status}"
+        for B, rows, K, rep, err, gerr in results:
+            assert err < 1e-2, (rank, B, rows, K, rep, err)
+            assert gerr < 2e-2, (rank, B, rows, K, rep, gerr)
