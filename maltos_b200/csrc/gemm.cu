@@ -21,6 +21,7 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kEpiWarps = 4;
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr int kMaxPushThreads = 128;  // extra warps per block that copy rows to peers in the fused all-gather launch
 constexpr int kGroupM = 8;  // tiles of one N column are visited for 8 consecutive M blocks (L2 reuse of B)
 
 struct GemmArgs {
@@ -38,7 +39,7 @@ struct GemmArgs {
 };
 
 // Sequence-parallel all-gather fused into the GEMM (A operand = rows gathered from all ranks of the TP group).
-// The first `push_ctas` blocks of the grid copy this rank's rows into every peer's gathered buffer over NVLink and
+// `push_ctas` extra warps of every block copy this rank's rows into every peer's gathered buffer over NVLink and
 // publish a per-source flag; the GEMM blocks start with this rank's own rows and visit the other sources in ring
 // order, waiting (bounded) for a source's flag only when they reach its rows. Signal-pad words (uint32):
 //   [buf*8 + src]        arrived : rows of `src` are complete in my gathered buffer `buf`      (written by src)
@@ -47,7 +48,7 @@ struct GemmArgs {
 constexpr int kMaxPeers = 8;
 struct GatherArgs {
   int enabled;
-  int push_ctas;
+  int push_ctas;          // push warps per block
   int rank, world;
   int batches;            // B
   int rows_per_chunk;     // S / T rows of one rank per batch
@@ -82,17 +83,19 @@ __device__ __forceinline__ bool wait_flag_reached(const unsigned* flag, unsigned
 }
 
 // Body of a push block: copies x_local into slot `rank` of every rank's gathered buffer, local copy first.
-__device__ void gather_push_role(const GatherArgs& g, int K, int* status) {
+__device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_ctas) {
   __shared__ int s_ok;
+  const int tid = static_cast<int>(threadIdx.x) - kGemmThreads;          // push warps sit behind the GEMM warps
+  const int nthr = static_cast<int>(blockDim.x) - kGemmThreads;
+  auto push_sync = [nthr]() { asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory"); };
   const int buf = static_cast<int>(g.seq & 1u);
   const long long vec_per_row = K >> 3;
   const long long rows_local = static_cast<long long>(g.batches) * g.rows_per_chunk;
-  const long long total_vec = rows_local * vec_per_row;
   const long long s_rows = static_cast<long long>(g.rows_per_chunk) * g.world;   // rows of one batch in the gathered buffer
   unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
   for (int step = 0; step < g.world; ++step) {
     const int dst = (g.rank + step) % g.world;
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
       // the destination must have finished the call that last used this buffer (two calls ago)
       bool ok = step == 0 ? true : wait_flag_reached(my_pad + 16 + buf * 8 + dst, g.seq - 2u, nullptr);
       if (step == 0) ok = wait_flag_reached(my_pad + 16 + buf * 8 + g.rank, g.seq - 2u, nullptr);
@@ -102,28 +105,49 @@ __device__ void gather_push_role(const GatherArgs& g, int K, int* status) {
       }
       s_ok = ok ? 1 : 0;
     }
-    __syncthreads();
+    push_sync();
     if (!s_ok) return;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(g.gathered[dst]) + static_cast<long long>(buf) * g.buf_elems;
-    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total_vec;
-         v += static_cast<long long>(g.push_ctas) * blockDim.x) {
-      const long long row = v / vec_per_row, c = v - row * vec_per_row;
-      const long long b = row / g.rows_per_chunk, i = row - b * g.rows_per_chunk;
-      const uint4 val = *reinterpret_cast<const uint4*>(g.x_local + row * g.x_ld + c * 8);
-      const long long drow = b * s_rows + static_cast<long long>(g.rank) * g.rows_per_chunk + i;
-      *reinterpret_cast<uint4*>(out + drow * K + c * 8) = val;
+    // Row-wise copy, 4 rows per pass: every thread keeps several independent 16-byte loads in flight before the
+    // (posted) NVLink stores - a dependent load->store chain per thread would make the copy latency-bound.
+    constexpr int kRows = 4;
+    const int vpr = static_cast<int>(vec_per_row);
+    for (long long r0 = static_cast<long long>(blockIdx.x) * kRows; r0 < rows_local; r0 += static_cast<long long>(n_ctas) * kRows) {
+      for (int c0 = tid; c0 < vpr; c0 += nthr * 2) {
+        uint4 vals[kRows][2];
+        const int c1 = c0 + nthr;
+#pragma unroll
+        for (int rr = 0; rr < kRows; ++rr) {
+          const long long row = r0 + rr;
+          if (row < rows_local) {
+            const __nv_bfloat16* src = g.x_local + row * g.x_ld;
+            vals[rr][0] = *reinterpret_cast<const uint4*>(src + c0 * 8);
+            if (c1 < vpr) vals[rr][1] = *reinterpret_cast<const uint4*>(src + c1 * 8);
+          }
+        }
+#pragma unroll
+        for (int rr = 0; rr < kRows; ++rr) {
+          const long long row = r0 + rr;
+          if (row < rows_local) {
+            const long long b = row / g.rows_per_chunk, i = row - b * g.rows_per_chunk;
+            __nv_bfloat16* drow = out + (b * s_rows + static_cast<long long>(g.rank) * g.rows_per_chunk + i) * K;
+            *reinterpret_cast<uint4*>(drow + c0 * 8) = vals[rr][0];
+            if (c1 < vpr) *reinterpret_cast<uint4*>(drow + c1 * 8) = vals[rr][1];
+          }
+        }
+      }
     }
     __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    push_sync();
+    if (tid == 0) {
       const unsigned done = atomicAdd(my_pad + 40 + dst, 1u);
-      if (done == static_cast<unsigned>(g.push_ctas - 1)) {   // last push block for this destination publishes the flag
+      if (done == static_cast<unsigned>(n_ctas - 1)) {   // last block to finish this destination publishes the flag
         atomicExch(my_pad + 40 + dst, 0u);
         __threadfence_system();
         st_release_sys(reinterpret_cast<unsigned*>(g.pads[dst]) + buf * 8 + g.rank, g.seq);
       }
     }
-    __syncthreads();
+    push_sync();
   }
 }
 
@@ -138,16 +162,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads + kMaxPushThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p,
                  const __grid_constant__ GatherArgs g) {
-  if (g.enabled && static_cast<int>(blockIdx.x) < g.push_ctas) {
-    gather_push_role(g, p.K, p.status);   // push blocks never touch TMEM or the smem pipeline
-    return;
-  }
-  const int first_cta = g.enabled ? g.push_ctas : 0;
-  const int cta = static_cast<int>(blockIdx.x) - first_cta;
-  const int n_ctas = static_cast<int>(gridDim.x) - first_cta;
+  const int cta = static_cast<int>(blockIdx.x);
+  const int n_ctas = static_cast<int>(gridDim.x);
   constexpr int A_BYTES = kBM * kBK * 2;
   constexpr int B_BYTES = BN * kBK * 2;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -292,6 +311,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     __syncwarp();
+  } else if (warp >= 2 + kEpiWarps) {
+    // ------------------------------------------------------------ all-gather push (fused launches only)
+    // Every block carries push warps, so the copy is spread over all SMs and no block of the persistent GEMM is
+    // delayed behind a copy-only block.
+    gather_push_role(g, p.K, p.status, n_ctas);
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may touch
@@ -428,9 +452,9 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
     g.enabled = 0;
     g.push_ctas = 0;
   }
-  int grid = total < sm_count() ? total : sm_count();
-  if (g.enabled) grid += g.push_ctas;   // push blocks are small and share SMs with the GEMM blocks
-  gemm_bf16_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, args, g);
+  const int grid = total < sm_count() ? total : sm_count();
+  const int threads = g.enabled ? kGemmThreads + 32 * g.push_ctas : kGemmThreads;
+  gemm_bf16_kernel<BN, STAGES><<<grid, threads, smem, stream>>>(tmA, tmB, args, g);
   count_launch();
   MB_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -545,7 +569,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.b_lbo = 16u, args.b_sbo = 1024u, args.b_kstep = 32u;
   GatherArgs g;
   g.enabled = 1;
-  g.push_ctas = push_ctas > 0 ? push_ctas : 16;
+  g.push_ctas = (push_ctas > 0 && push_ctas * 32 <= kMaxPushThreads) ? push_ctas : kMaxPushThreads / 32;
   g.rank = rank, g.world = world;
   g.batches = batches, g.rows_per_chunk = rows_per_chunk;
   g.x_local = static_cast<const __nv_bfloat16*>(x_local);

@@ -1,7 +1,7 @@
 """Tensor/sequence-parallel linear ops with the collective inside the GEMM kernel (``csrc/gemm.cu``).
 
 ``all_gather_grouped_linear``: the SP all-gather of ``x [B, S/T, H]`` and the q/k/v (gate/up) projection are ONE launch:
-push blocks of the kernel store this rank's rows into every peer's gathered buffer over NVLink (plain P2P stores into
+push warps in every block of the kernel store this rank's rows into every peer's gathered buffer over NVLink (plain P2P stores into
 CUDA-IPC mapped memory, per-source flags), while the tcgen05 GEMM blocks start on the rows that are already local and
 reach a peer's rows only after its flag arrived - the transfer hides behind the math tile by tile. Buffers are
 double-buffered by call parity and a "consumed" flag keeps a fast rank from overwriting a buffer a slow rank still reads.
@@ -19,7 +19,7 @@ from . import _lib
 from .gemm import gemm
 from .grouped import _fused_view, _memory_order
 
-PUSH_CTAS = 16
+PUSH_CTAS = 4   # push warps per block
 
 
 def _nccl_all_gather_rows(x2: torch.Tensor, ctx, B: int, rows: int) -> torch.Tensor:
