@@ -443,3 +443,49 @@ MB_API int mb_swiglu_bwd(const void* dout, long long dout_stride, const void* ga
   MB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// RMSNorm backward whose partial-sum scratch is a file-scope device array instead of a caller-provided buffer, for
+// hosts that must not allocate device memory around the call (see rmsnorm_bwd_static.h for limits and sharing rules).
+#include "rmsnorm_bwd_static.h"
+
+namespace mb {
+static __device__ __align__(256) float g_rmsnorm_static_scratch[MB_RMSNORM_STATIC_MAX_BLOCKS * MB_RMSNORM_STATIC_MAX_H];
+}
+
+MB_API int mb_rmsnorm_bwd_static(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,
+                                 void* dx, void* dw_bf16, float* dw_f32, int accumulate_dw, long long rows, int H,
+                                 cudaStream_t stream) {
+  using namespace mb;
+  if (H <= 0 || H % 8 != 0) {
+    set_last_error("mb_rmsnorm_bwd_static: hidden size must be a positive multiple of 8");
+    return -1;
+  }
+  if (rows <= 0) return 0;
+  const int blocks = mb_rmsnorm_bwd_blocks(rows);
+  if (H > MB_RMSNORM_STATIC_MAX_H || blocks > MB_RMSNORM_STATIC_MAX_BLOCKS) {
+    set_last_error("mb_rmsnorm_bwd_static: problem exceeds the static scratch (H <= 8192, at most 304 row blocks)");
+    return -2;
+  }
+  // Per-device address of the scratch array, resolved on the first call on that device.
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  MB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_last_error("mb_rmsnorm_bwd_static: device index out of range");
+    return -3;
+  }
+  float* scratch = scratch_of_device[dev];
+  if (!scratch) {
+    MB_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_rmsnorm_static_scratch));
+    scratch_of_device[dev] = scratch;
+  }
+  rmsnorm_bwd_kernel<<<blocks, kNormThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(w),
+      rstd, static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), scratch, rows, H);
+  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, blocks, H, static_cast<__nv_bfloat16*>(dw_bf16),
+                                                              dw_f32, accumulate_dw);
+  count_launch(2);
+  MB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
