@@ -36,6 +36,8 @@ struct GemmArgs {
   // UMMA shared-memory descriptor geometry in bytes (see make_smem_desc_sw128).
   unsigned a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
   int* status;
+  int group_m;        // M blocks per rasterisation group (CTA-pair kernel)
+  long long* trace;   // debug: per-CTA cycle counters {mma total, wait full, wait tempty, producer wait empty} or nullptr
 };
 
 // Sequence-parallel all-gather fused into the GEMM (A operand = rows gathered from all ranks of the TP group).
@@ -151,7 +153,8 @@ __device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_
   }
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk, int group_m = kGroupM) {
+  const int kGroupM = group_m;
   const int per_group = kGroupM * tiles_n;
   const int group = tile / per_group;
   const int first_m = group * kGroupM;
@@ -159,6 +162,63 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   const int in_group = tile - group * per_group;
   m_blk = first_m + in_group % gsz;
   n_blk = in_group / gsz;
+}
+
+// Epilogue of one accumulator chunk: 32 consecutive fp32 columns of one output row (+bias, optional accumulate)
+// written as bf16 or fp32 with 16-byte stores where the alignment allows.
+__device__ __forceinline__ void epilogue_store32(const GemmArgs& p, int row, int col0, const uint32_t (&r)[32], bool vec_ok) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  if (p.bias) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+  }
+  if (p.out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        if (p.accumulate) {
+          const float4 old = *reinterpret_cast<const float4*>(dst + i);
+          o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+        }
+        *reinterpret_cast<float4*>(dst + i) = o;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        if (p.accumulate) {
+          const uint4 old = *reinterpret_cast<const uint4*>(dst + i);
+          const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(ob[j]);
+            v[i + 2 * j] += f.x;
+            v[i + 2 * j + 1] += f.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(v[i], v[i + 1]);
+        o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+        o.z = pack_bf16x2(v[i + 4], v[i + 5]);
+        o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+        *reinterpret_cast<uint4*>(dst + i) = o;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+        const float o = p.accumulate ? v[i] + __bfloat162float(dst[i]) : v[i];
+        dst[i] = __float2bfloat16(o);
+      }
+    }
+  }
 }
 
 template <int BN, int STAGES>
@@ -340,60 +400,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = n_blk * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.bias) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
-          }
-          if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-            if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                if (p.accumulate) {
-                  const float4 old = *reinterpret_cast<const float4*>(dst + i);
-                  o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(dst + i) = o;
-              }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-            if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                if (p.accumulate) {
-                  const uint4 old = *reinterpret_cast<const uint4*>(dst + i);
-                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 f = __bfloat1622float2(ob[j]);
-                    v[i + 2 * j] += f.x;
-                    v[i + 2 * j + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[i], v[i + 1]);
-                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
-                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
-                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                *reinterpret_cast<uint4*>(dst + i) = o;
-              }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-                const float o = p.accumulate ? v[i] + __bfloat162float(dst[i]) : v[i];
-                dst[i] = __float2bfloat16(o);
-              }
-            }
-          }
-        }
+        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, r, vec_ok);
       }
       tc_fence_before();
       __syncwarp();
@@ -431,6 +438,296 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------------------------------------- CTA-pair kernel
+// 256x256 output tiles computed by a cluster of two CTAs with ONE tcgen05.mma.cta_group::2 stream: CTA r of the pair
+// stages rows [128 r, 128 r + 128) of the A tile and rows [128 r, 128 r + 128) of the B tile (its half of N) in its
+// own shared memory, the even CTA issues M=256 x N=256 UMMAs that read both CTAs' shared memory, and each CTA's TMEM
+// receives its 128 output rows. Per CTA and k-block that is 32 KB of shared-memory operand traffic for 8.4 MFLOP,
+// half the bytes per FLOP of the single-CTA 128x256 tile, which is what lifts the kernel off the shared-memory
+// bandwidth limit. Barriers: full[s] lives in the leader and counts the TMA bytes of both CTAs; empty[s] and
+// tfull[a] exist in both CTAs and are signalled by one commit addressed to both; tempty[a] lives in the leader and
+// collects the epilogue warps of both CTAs.
+constexpr int kPairStages = 6;
+constexpr int kPairTile = 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads + kMaxPushThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p,
+                      const __grid_constant__ GatherArgs g) {
+  constexpr int STAGES = kPairStages;
+  constexpr int A_BYTES = 128 * kBK * 2;
+  constexpr int B_BYTES = 128 * kBK * 2;
+  constexpr uint32_t TMEM_COLS = 512;   // two 256-column fp32 accumulators
+  const uint32_t cta_rank = cluster_cta_rank();
+  const bool leader = cta_rank == 0;
+  const int pair = static_cast<int>(blockIdx.x) >> 1;
+  const int n_pairs = static_cast<int>(gridDim.x) >> 1;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n;   // in 256x256 tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 2 * kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);   // the whole TMEM of this SM: both CTAs of the pair get base column 0
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();   // barriers of both CTAs are initialised before any remote arrive / TMA completion targets them
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tmem_base != 0 && threadIdx.x == 0) {   // the pair's UMMA needs the same TMEM address in both CTAs
+    *abort_flag = 1;
+    atomicOr(&p.status[0], MB_ERR_BAD_INDEX);
+  }
+  __syncthreads();
+
+  const int m_rot = g.enabled ? (g.rank * g.rows_per_chunk) / kPairTile : 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
+    if (lane == 0 && !*abort_flag) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const int s_rows = g.enabled ? g.rows_per_chunk * g.world : 1;
+      const int gbuf = static_cast<int>(g.seq & 1u);
+      const unsigned* my_pad = g.enabled ? reinterpret_cast<const unsigned*>(g.pads[g.rank]) : nullptr;
+      uint32_t full_addr[STAGES];
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) full_addr[s] = mapa_u32(&full_bar[s], 0);
+      long long t_empty = 0;
+      for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+        int m_blk, n_blk;
+        tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
+        if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;
+        const int m0 = m_blk * kPairTile + static_cast<int>(cta_rank) * 128;
+        const int n0 = n_blk * kPairTile + static_cast<int>(cta_rank) * 128;
+        if (g.enabled && m0 < p.M) {
+          const int row_hi = min(m0 + 128, p.M) - 1;
+          const int src_lo = (m0 % s_rows) / g.rows_per_chunk, src_hi = (row_hi % s_rows) / g.rows_per_chunk;
+          bool ready = wait_flag_reached(my_pad + gbuf * 8 + src_lo, g.seq, abort_flag);
+          if (ready && src_hi != src_lo) ready = wait_flag_reached(my_pad + gbuf * 8 + src_hi, g.seq, abort_flag);
+          if (!ready) {
+            *abort_flag = 1;
+            atomicOr(&p.status[0], MB_ERR_PEER_TIMEOUT);
+            p.status[2] = src_lo;
+            break;
+          }
+          fence_proxy_async_global();
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          const long long t0 = clock64();
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          t_empty += clock64() - t0;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * (A_BYTES + B_BYTES));
+          const int k0 = kb * kBK;
+          uint8_t* a_dst = sA + stage * A_BYTES;
+          uint8_t* b_dst = sB + stage * B_BYTES;
+          if (!p.a_mn) {
+            tma_load_2d_pair(a_dst, &tmA, full_addr[stage], k0, m0);
+          } else {
+            tma_load_2d_pair(a_dst, &tmA, full_addr[stage], m0, k0);
+            tma_load_2d_pair(a_dst + 8192, &tmA, full_addr[stage], m0 + 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(b_dst, &tmB, full_addr[stage], k0, n0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmB, full_addr[stage], n0, k0);
+            tma_load_2d_pair(b_dst + 8192, &tmB, full_addr[stage], n0 + 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (p.trace) p.trace[4 * blockIdx.x + 3] = t_empty;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0 && !*abort_flag) {
+      const uint32_t idesc = make_idesc_bf16(kPairTile, kPairTile, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_lbo, b_lbo = p.b_lbo, a_kstep = p.a_kstep, b_kstep = p.b_kstep;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      long long t_full = 0, t_tempty = 0;
+      const long long t_begin = clock64();
+      for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+        long long t0 = clock64();
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) break;
+        t_tempty += clock64() - t0;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairTile);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          t0 = clock64();
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          t_full += clock64() - t0;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + kk * a_kstep, a_lbo, p.a_sbo);
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + kk * b_kstep, b_lbo, p.b_sbo);
+            umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);   // both CTAs may refill this stage
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull_bar[acc], 3);       // accumulator complete in both CTAs' TMEM
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+      if (p.trace) {
+        long long* t = p.trace + 4 * blockIdx.x;
+        t[0] = clock64() - t_begin, t[1] = t_full, t[2] = t_tempty;
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 2 + kEpiWarps) {
+    gather_push_role(g, p.K, p.status, static_cast<int>(gridDim.x));
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
+                                   : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const uint32_t tempty_leader[2] = {mapa_u32(&tempty_bar[0], 0), mapa_u32(&tempty_bar[1], 0)};
+    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+      int m_blk, n_blk;
+      tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
+      if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;
+      bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_blk * kPairTile + static_cast<int>(cta_rank) * 128 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kPairTile) + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kPairTile / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * kPairTile + c * 32;
+        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, r, vec_ok);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  // Neither CTA may leave while the other can still read its shared memory (UMMA operands) or signal its barriers.
+  cluster_arrive();
+  cluster_wait();
+  if (*abort_flag) {
+    __nanosleep(50000);
+    if (threadIdx.x == 0) {
+      atomicOr(&p.status[0], MB_ERR_MBAR_TIMEOUT);
+      p.status[1] = static_cast<int>(blockIdx.x);
+    }
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (g.enabled && threadIdx.x == 0 && !*abort_flag) {
+    unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
+    const unsigned done = atomicAdd(my_pad + 32, 1u);
+    if (done == gridDim.x - 1) {
+      atomicExch(my_pad + 32, 0u);
+      __threadfence_system();
+      const int gbuf = static_cast<int>(g.seq & 1u);
+      for (int r = 0; r < g.world; ++r) st_release_sys(reinterpret_cast<unsigned*>(g.pads[r]) + 16 + gbuf * 8 + g.rank, g.seq);
+    }
+  }
+}
+
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& args, cudaStream_t stream,
+                            const GatherArgs* gather = nullptr) {
+  constexpr size_t smem = 1024 + kPairStages * (2 * 128 * kBK * 2) + 256;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    MB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+    configured[dev & 63] = true;
+  }
+  args.tiles_m = (args.M + kPairTile - 1) / kPairTile;
+  args.tiles_n = (args.N + kPairTile - 1) / kPairTile;
+  const int total = args.tiles_m * args.tiles_n;
+  GatherArgs g;
+  if (gather) {
+    g = *gather;
+  } else {
+    g.enabled = 0;
+    g.push_ctas = 0;
+  }
+  const int max_pairs = sm_count() / 2;
+  const int grid = 2 * (total < max_pairs ? total : max_pairs);
+  const int threads = g.enabled ? kGemmThreads + 32 * g.push_ctas : kGemmThreads;
+  gemm_bf16_pair_kernel<<<grid, threads, smem, stream>>>(tmA, tmB, args, g);
+  count_launch();
+  MB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// True when the 256x256 CTA-pair kernel is the better choice. Measured on B200 against the single-CTA 128x256 kernel:
+// the pair wins by 5-15 % for weight gradients (both operands MN-major) and for long reductions (K >= 8192), and is
+// level or slightly behind elsewhere; it needs enough tiles to fill every pair of SMs.
+static bool prefer_pair_kernel(int M, int N, int K, int a_mn) {
+  const long long tiles = static_cast<long long>((M + kPairTile - 1) / kPairTile) * ((N + kPairTile - 1) / kPairTile);
+  if (tiles < 2 * (sm_count() / 2)) return false;
+  return a_mn || K >= 8192;
+}
+
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& args, cudaStream_t stream,
                        const GatherArgs* gather = nullptr) {
@@ -462,8 +759,19 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
 
 // Debug override of the descriptor geometry {lbo, sbo, kstep} per operand; negative = built-in value.
 static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
+static long long* g_trace = nullptr;
+static int g_pair_group_m = 8;
 
 }  // namespace mb
+
+// Debug: device buffer of 4 int64 per CTA that the CTA-pair kernel fills with cycle counters (nullptr = off).
+MB_API void mb_gemm_set_trace(long long* buf) { mb::g_trace = buf; }
+
+// Tuning knob of the CTA-pair kernel: M blocks per rasterisation group. (An L2 prefetch stream ahead of the
+// shared-memory ring was tried and removed: the extra L2 requests cost a third of the throughput.)
+MB_API void mb_gemm_set_tuning(int group_m) {
+  if (group_m > 0) mb::g_pair_group_m = group_m;
+}
 
 MB_API void mb_gemm_debug_descriptor(int a_lbo, int a_sbo, int a_kstep, int b_lbo, int b_sbo, int b_kstep) {
   int v[6] = {a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
@@ -472,7 +780,7 @@ MB_API void mb_gemm_debug_descriptor(int a_lbo, int a_sbo, int a_kstep, int b_lb
 
 // C[M,N] (+)= op(A) op(B) (+bias). Leading dimensions are in elements; bf16 operands need them (and the base
 // addresses) to be multiples of 8 elements / 16 bytes because the operands are fetched with TMA.
-// block_n: 0 = choose, else 128 or 256.
+// block_n: 0 = choose; 128 or 256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel (256x256 tiles).
 MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn, long long ldb, void* C,
                         long long ldc, int M, int N, int K, int out_fp32, int accumulate, const void* bias,
                         int block_n, cudaStream_t stream) {
@@ -500,6 +808,8 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   args.tiles_m = (M + kBM - 1) / kBM;
   args.k_blocks = (K + kBK - 1) / kBK;
   args.status = status;
+  args.trace = g_trace;
+  args.group_m = g_pair_group_m;
   args.a_lbo = a_mn ? 8192u : 16u, args.a_sbo = 1024u, args.a_kstep = a_mn ? 2048u : 32u;
   args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;
   {
@@ -509,6 +819,8 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   }
 
   int bn = block_n;
+  const bool pair = block_n == 512 || (block_n == 0 && prefer_pair_kernel(M, N, K, a_mn));
+  if (pair) bn = 128;   // each CTA of a pair stages 128 rows of B
   if (bn != 128 && bn != 256) {
     const long long tiles256 = static_cast<long long>(args.tiles_m) * ((N + 255) / 256);
     bn = (N <= 128 || tiles256 < sm_count()) ? 128 : 256;
@@ -525,6 +837,7 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   else
     ok = encode_tmap_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBK, 2, true);
   if (!ok) return -4;
+  if (pair) return launch_gemm_pair(tmA, tmB, args, stream);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream);
   return launch_gemm<128, 6>(tmA, tmB, args, stream);
 }
@@ -565,6 +878,8 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.tiles_m = (args.M + kBM - 1) / kBM;
   args.k_blocks = (K + kBK - 1) / kBK;
   args.status = status;
+  args.trace = nullptr;
+  args.group_m = g_pair_group_m;
   args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
   args.b_lbo = 16u, args.b_sbo = 1024u, args.b_kstep = 32u;
   GatherArgs g;
@@ -581,10 +896,12 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
     g.pads[r] = r < world ? pads[r] : 0ull;
   }
   const __nv_bfloat16* a_base = reinterpret_cast<const __nv_bfloat16*>(gathered[rank]) + static_cast<long long>(seq & 1u) * buf_elems;
-  const int bn = (N <= 128 || static_cast<long long>(args.tiles_m) * ((N + 255) / 256) < sm_count()) ? 128 : 256;
+  const bool pair = prefer_pair_kernel(args.M, N, K, 0);
+  const int bn = pair ? 128 : ((N <= 128 || static_cast<long long>(args.tiles_m) * ((N + 255) / 256) < sm_count()) ? 128 : 256);
   CUtensorMap tmA, tmB;
   if (!encode_tmap_2d(&tmA, a_base, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM, 2, true)) return -5;
   if (!encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true)) return -5;
+  if (pair) return launch_gemm_pair(tmA, tmB, args, stream, &g);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream, &g);
   return launch_gemm<128, 6>(tmA, tmB, args, stream, &g);
 }
