@@ -203,3 +203,22 @@ def test_adamw_and_norm_kernels():
     for g, b in zip(gs, before):
         _close(g, b.float() * coef.item(), 1e-2)
     _lib.fetch_status()
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 8, 2), (128, 4, 4)])
+def test_causal_attention_matches_fp32_reference(D, Hq, Hkv):
+    from maltos_b200.ops.attention import attention_reference, causal_attention
+
+    torch.manual_seed(3)
+    B, S = 2, 384
+    q, k, v = (torch.randn(B, S, h, D, device=DEV).bfloat16().requires_grad_() for h in (Hq, Hkv, Hkv))
+    out = causal_attention(q, k, v)
+    do = torch.randn_like(out)
+    out.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qf, kf, vf, causal=True)
+    ref.backward(do.float())
+    _close(out, ref, 2e-2)
+    _close(q.grad, qf.grad, 3e-2)
+    _close(k.grad, kf.grad, 3e-2)
+    _close(v.grad, vf.grad, 3e-2)
