@@ -20,7 +20,9 @@ namespace mb {
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kEpiWarps = 4;
-constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr int kFirstPushWarp = 2 + kEpiWarps;
+constexpr int kGemmThreads = 32 * kFirstPushWarp;        // warp 0 TMA, 1 MMA, 2..5 epilogue
+constexpr int kWideThreads = kGemmThreads + 32 * kEpiWarps;   // 256x512 kernel: warps 6..9 are a second epilogue group
 constexpr int kMaxPushThreads = 128;  // extra warps per block that copy rows to peers in the fused all-gather launch
 constexpr int kGroupM = 8;  // tiles of one N column are visited for 8 consecutive M blocks (L2 reuse of B)
 
@@ -37,6 +39,8 @@ struct GemmArgs {
   unsigned a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
   int* status;
   int group_m;        // M blocks per rasterisation group (CTA-pair kernel)
+  int stages;         // debug: ring depth used by the CTA-pair kernel (0 = all)
+  int debug_mode;     // 0 normal; 1 = MMAs without waiting for data (producer idle); 2 = loads without MMAs (timing probes)
   long long* trace;   // debug: per-CTA cycle counters {mma total, wait full, wait tempty, producer wait empty} or nullptr
 };
 
@@ -85,10 +89,10 @@ __device__ __forceinline__ bool wait_flag_reached(const unsigned* flag, unsigned
 }
 
 // Body of a push block: copies x_local into slot `rank` of every rank's gathered buffer, local copy first.
-__device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_ctas) {
+__device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_ctas, int first_thread = kGemmThreads) {
   __shared__ int s_ok;
-  const int tid = static_cast<int>(threadIdx.x) - kGemmThreads;          // push warps sit behind the GEMM warps
-  const int nthr = static_cast<int>(blockDim.x) - kGemmThreads;
+  const int tid = static_cast<int>(threadIdx.x) - first_thread;          // push warps sit behind the GEMM warps
+  const int nthr = static_cast<int>(blockDim.x) - first_thread;
   auto push_sync = [nthr]() { asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory"); };
   const int buf = static_cast<int>(g.seq & 1u);
   const long long vec_per_row = K >> 3;
@@ -192,7 +196,18 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& p, int row, int
     }
   } else {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-    if (vec_ok && col0 + 32 <= p.N) {
+    if (vec_ok && !p.accumulate && col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+      // 64 contiguous bytes of one row as two 32-byte stores
+#pragma unroll
+      for (int i = 0; i < 32; i += 16) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + i),
+                     "r"(pack_bf16x2(v[i], v[i + 1])), "r"(pack_bf16x2(v[i + 2], v[i + 3])), "r"(pack_bf16x2(v[i + 4], v[i + 5])),
+                     "r"(pack_bf16x2(v[i + 6], v[i + 7])), "r"(pack_bf16x2(v[i + 8], v[i + 9])),
+                     "r"(pack_bf16x2(v[i + 10], v[i + 11])), "r"(pack_bf16x2(v[i + 12], v[i + 13])),
+                     "r"(pack_bf16x2(v[i + 14], v[i + 15]))
+                     : "memory");
+      }
+    } else if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
         if (p.accumulate) {
@@ -271,7 +286,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    constexpr bool is_a = true;
+    if (lane == 0 && p.debug_mode != 1) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -282,9 +298,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = cta; ok && tile < total_tiles; tile += n_ctas) {
         int m_blk, n_blk;
         tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
-        if (g.enabled) {
-          // own rows first, then the other sources in ring order; wait for a source only when its rows are needed
-          m_blk = (m_blk + m_rot) % p.tiles_m;
+        if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;   // own rows first, then the other sources in ring order
+        if (g.enabled && is_a) {
+          // wait for a source only when its rows are needed
           const int row_lo = m_blk * kBM, row_hi = min(row_lo + kBM, p.M) - 1;
           const int src_lo = (row_lo % s_rows) / g.rows_per_chunk, src_hi = (row_hi % s_rows) / g.rows_per_chunk;
           bool ready = wait_flag_reached(my_pad + gbuf * 8 + src_lo, g.seq, abort_flag);
@@ -304,21 +320,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&full_bar[stage], A_BYTES + B_BYTES);
           const int k0 = kb * kBK;
-          uint8_t* a_dst = sA + stage * A_BYTES;
-          uint8_t* b_dst = sB + stage * B_BYTES;
-          if (!p.a_mn) {
-            tma_load_2d(a_dst, &tmA, &full_bar[stage], k0, m0);
-          } else {
+          {
+            mbar_arrive_expect_tx(&full_bar[stage], A_BYTES + B_BYTES);
+            uint8_t* a_dst = sA + stage * A_BYTES;
+            if (!p.a_mn) {
+              tma_load_2d(a_dst, &tmA, &full_bar[stage], k0, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[stage], m0 + 64 * j, k0);
-          }
-          if (!p.b_mn) {
-            tma_load_2d(b_dst, &tmB, &full_bar[stage], k0, n0);
-          } else {
+              for (int j = 0; j < kBM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[stage], m0 + 64 * j, k0);
+            }
+            uint8_t* b_dst = sB + stage * B_BYTES;
+            if (!p.b_mn) {
+              tma_load_2d(b_dst, &tmB, &full_bar[stage], k0, n0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[stage], n0 + 64 * j, k0);
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[stage], n0 + 64 * j, k0);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -345,9 +363,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          if (p.debug_mode != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
             ok = false;
             break;
+          }
+          if (p.debug_mode == 2) {   // timing probe: consume the stage without math
+            mbar_arrive(&empty_bar[stage]);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
           }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
@@ -371,7 +397,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp >= 2 + kEpiWarps) {
+  } else if (warp >= kFirstPushWarp) {
     // ------------------------------------------------------------ all-gather push (fused launches only)
     // Every block carries push warps, so the copy is spread over all SMs and no block of the persistent GEMM is
     // delayed behind a copy-only block.
@@ -447,16 +473,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // bandwidth limit. Barriers: full[s] lives in the leader and counts the TMA bytes of both CTAs; empty[s] and
 // tfull[a] exist in both CTAs and are signalled by one commit addressed to both; tempty[a] lives in the leader and
 // collects the epilogue warps of both CTAs.
+static int g_debug_max_pairs = 0;   // debug cap on the number of CTA pairs (0 = all)
 constexpr int kPairStages = 6;
 constexpr int kPairTile = 256;
+constexpr int kWideStages = 4;   // 256x512 tiles: 48 KB per stage and CTA
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads + kMaxPushThreads, 1)
+template <bool WIDE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((WIDE ? kWideThreads : kGemmThreads) + kMaxPushThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p,
                       const __grid_constant__ GatherArgs g) {
-  constexpr int STAGES = kPairStages;
+  // WIDE: the tile is 256x512 - every k-step issues two N=256 UMMAs that share the A stage, each CTA stages 256 rows
+  // of B, and the single 512-column accumulator fills TMEM (the epilogue is then not overlapped with the next tile).
+  // Per FLOP this moves a third less data through shared memory (TMA writes + UMMA operand reads share its bandwidth,
+  // which is what limits the 256x256 and the single-CTA kernels).
+  constexpr int STAGES = WIDE ? kWideStages : kPairStages;
+  constexpr int B_ROWS = WIDE ? 256 : 128;          // rows of B staged per CTA
+  constexpr int TILE_N = 2 * B_ROWS;
+  constexpr int N_ACC = WIDE ? 1 : 2;               // accumulator buffers in TMEM
+  constexpr int EPI_WARPS = WIDE ? 2 * kEpiWarps : kEpiWarps;   // WIDE: two groups of four, each drains 256 columns
+  constexpr int FIRST_PUSH_THREAD = WIDE ? kWideThreads : kGemmThreads;
   constexpr int A_BYTES = 128 * kBK * 2;
-  constexpr int B_BYTES = 128 * kBK * 2;
-  constexpr uint32_t TMEM_COLS = 512;   // two 256-column fp32 accumulators
+  constexpr int B_BYTES = B_ROWS * kBK * 2;
+  constexpr uint32_t TMEM_COLS = 512;   // two 256-column fp32 accumulators, or one of 512 columns
   const uint32_t cta_rank = cluster_cta_rank();
   const bool leader = cta_rank == 0;
   const int pair = static_cast<int>(blockIdx.x) >> 1;
@@ -476,6 +514,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.tiles_m * p.tiles_n;   // in 256x256 tiles
+  const int n_stages = (p.stages > 0 && p.stages < STAGES) ? p.stages : STAGES;   // ring depth actually used (debug)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -484,7 +523,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 2 * kEpiWarps);
+      mbar_init(&tempty_bar[b], 2 * EPI_WARPS);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -511,7 +550,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
-    if (lane == 0 && !*abort_flag) {
+    constexpr bool is_a = true;
+    if (lane == 0 && !*abort_flag && p.debug_mode != 1) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -522,13 +562,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) full_addr[s] = mapa_u32(&full_bar[s], 0);
       long long t_empty = 0;
+      int n_issued = 0;
       for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
         int m_blk, n_blk;
         tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
         if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;
         const int m0 = m_blk * kPairTile + static_cast<int>(cta_rank) * 128;
-        const int n0 = n_blk * kPairTile + static_cast<int>(cta_rank) * 128;
-        if (g.enabled && m0 < p.M) {
+        const int n0 = n_blk * TILE_N + static_cast<int>(cta_rank) * B_ROWS;
+        if (is_a && g.enabled && m0 < p.M) {
           const int row_hi = min(m0 + 128, p.M) - 1;
           const int src_lo = (m0 % s_rows) / g.rows_per_chunk, src_hi = (row_hi % s_rows) / g.rows_per_chunk;
           bool ready = wait_flag_reached(my_pad + gbuf * 8 + src_lo, g.seq, abort_flag);
@@ -548,29 +589,33 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             break;
           }
           t_empty += clock64() - t0;
-          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * (A_BYTES + B_BYTES));
+          if (is_a && p.trace && n_issued < 64) p.trace[4 * gridDim.x + blockIdx.x * 256 + n_issued] = clock64();   // stage free seen / TMA issue
+          ++n_issued;
           const int k0 = kb * kBK;
-          uint8_t* a_dst = sA + stage * A_BYTES;
-          uint8_t* b_dst = sB + stage * B_BYTES;
-          if (!p.a_mn) {
-            tma_load_2d_pair(a_dst, &tmA, full_addr[stage], k0, m0);
-          } else {
-            tma_load_2d_pair(a_dst, &tmA, full_addr[stage], m0, k0);
-            tma_load_2d_pair(a_dst + 8192, &tmA, full_addr[stage], m0 + 64, k0);
+          {
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * (A_BYTES + B_BYTES));
+            uint8_t* a_dst = sA + stage * A_BYTES;
+            if (!p.a_mn) {
+              tma_load_2d_pair(a_dst, &tmA, full_addr[stage], k0, m0);
+            } else {
+              tma_load_2d_pair(a_dst, &tmA, full_addr[stage], m0, k0);
+              tma_load_2d_pair(a_dst + 8192, &tmA, full_addr[stage], m0 + 64, k0);
+            }
+            uint8_t* b_dst = sB + stage * B_BYTES;
+            if (!p.b_mn) {
+              tma_load_2d_pair(b_dst, &tmB, full_addr[stage], k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < B_ROWS / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, full_addr[stage], n0 + 64 * j, k0);
+            }
           }
-          if (!p.b_mn) {
-            tma_load_2d_pair(b_dst, &tmB, full_addr[stage], k0, n0);
-          } else {
-            tma_load_2d_pair(b_dst, &tmB, full_addr[stage], n0, k0);
-            tma_load_2d_pair(b_dst + 8192, &tmB, full_addr[stage], n0 + 64, k0);
-          }
-          if (++stage == STAGES) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1;
           }
         }
       }
-      if (p.trace) p.trace[4 * blockIdx.x + 3] = t_empty;
+      if (is_a && p.trace) p.trace[4 * blockIdx.x + 3] = t_empty;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -584,6 +629,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t acc_phase = 0;
       bool ok = true;
       long long t_full = 0, t_tempty = 0;
+      int n_seen = 0;
       const long long t_begin = clock64();
       for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
         long long t0 = clock64();
@@ -593,11 +639,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairTile);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           t0 = clock64();
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          if (p.debug_mode != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
           t_full += clock64() - t0;
+          if (p.trace && n_seen < 64) p.trace[4 * gridDim.x + blockIdx.x * 256 + 64 + n_seen] = clock64();      // data seen
+          ++n_seen;
+          if (p.debug_mode == 2) {   // consume the stage without math: release it in both CTAs
+            mbar_arrive(&empty_bar[stage]);
+            mbar_arrive_cluster(mapa_u32(&empty_bar[stage], 1));
+            if (++stage == n_stages) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * B_BYTES);
@@ -606,17 +663,23 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const uint64_t adesc = make_smem_desc_sw128(a_addr + kk * a_kstep, a_lbo, p.a_sbo);
             const uint64_t bdesc = make_smem_desc_sw128(b_addr + kk * b_kstep, b_lbo, p.b_sbo);
             umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            if (WIDE) {   // second half of the tile: rows 128..255 of this CTA's B stage, accumulator columns 256..511
+              const uint64_t bdesc2 = make_smem_desc_sw128(b_addr + 16384 + kk * b_kstep, b_lbo, p.b_sbo);
+              umma_bf16_ss_pair(d_tmem + 256, adesc, bdesc2, idesc, (kb | kk) != 0 ? 1u : 0u);
+            }
           }
           umma_commit_pair(&empty_bar[stage], 3);   // both CTAs may refill this stage
-          if (++stage == STAGES) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
         umma_commit_pair(&tfull_bar[acc], 3);       // accumulator complete in both CTAs' TMEM
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == N_ACC) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
       }
       if (p.trace) {
         long long* t = p.trace + 4 * blockIdx.x;
@@ -624,8 +687,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp >= 2 + kEpiWarps) {
-    gather_push_role(g, p.K, p.status, static_cast<int>(gridDim.x));
+  } else if (warp >= FIRST_PUSH_THREAD / 32) {
+    gather_push_role(g, p.K, p.status, static_cast<int>(gridDim.x), FIRST_PUSH_THREAD);
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     const int q = warp & 3;
@@ -644,19 +707,34 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = m_blk * kPairTile + static_cast<int>(cta_rank) * 128 + q * 32 + lane;
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kPairTile) + (static_cast<uint32_t>(q * 32) << 16);
+      // Two chunks of 32 columns are kept in flight: the TMEM load of the next chunk is issued before the current one
+      // is converted and stored. In the 256x512 kernel warps 2..5 drain columns 0..255 and warps 6..9 columns 256..511.
+      const int c_begin = (WIDE && warp >= kFirstPushWarp) ? 8 : 0;
+      const int c_end = WIDE ? c_begin + 8 : TILE_N / 32;
+      auto out_col = [&](int c) {
+        // accumulator columns -> output columns: each UMMA writes CTA 0's B rows first, then CTA 1's
+        return WIDE ? n_blk * TILE_N + ((c & 4) ? 256 : 0) + (c >> 3) * 128 + (c & 3) * 32 : n_blk * kPairTile + c * 32;
+      };
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32b_x32(t_row + c_begin * 32, ra);
 #pragma unroll 1
-      for (int c = 0; c < kPairTile / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
+      for (int c = c_begin; c < c_end; c += 2) {
         tmem_ld_wait();
-        const int col0 = n_blk * kPairTile + c * 32;
-        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, r, vec_ok);
+        tmem_ld_32x32b_x32(t_row + (c + 1) * 32, rb);
+        int col0 = out_col(c);
+        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, ra, vec_ok);
+        tmem_ld_wait();
+        if (c + 2 < c_end) tmem_ld_32x32b_x32(t_row + (c + 2) * 32, ra);
+        col0 = out_col(c + 1);
+        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, rb, vec_ok);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      if (++acc == N_ACC) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
     }
   }
 
@@ -689,19 +767,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
+template <bool WIDE>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& args, cudaStream_t stream,
                             const GatherArgs* gather = nullptr) {
-  constexpr size_t smem = 1024 + kPairStages * (2 * 128 * kBK * 2) + 256;
+  constexpr int stages = WIDE ? kWideStages : kPairStages;
+  constexpr int tile_n = WIDE ? 512 : 256;
+  constexpr size_t smem = 1024 + stages * ((128 + tile_n / 2) * kBK * 2) + 256;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    MB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    MB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
     configured[dev & 63] = true;
   }
   args.tiles_m = (args.M + kPairTile - 1) / kPairTile;
-  args.tiles_n = (args.N + kPairTile - 1) / kPairTile;
+  args.tiles_n = (args.N + tile_n - 1) / tile_n;
   const int total = args.tiles_m * args.tiles_n;
   GatherArgs g;
   if (gather) {
@@ -710,22 +791,36 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     g.enabled = 0;
     g.push_ctas = 0;
   }
-  const int max_pairs = sm_count() / 2;
+  const int max_pairs = g_debug_max_pairs > 0 ? g_debug_max_pairs : sm_count() / 2;
   const int grid = 2 * (total < max_pairs ? total : max_pairs);
-  const int threads = g.enabled ? kGemmThreads + 32 * g.push_ctas : kGemmThreads;
-  gemm_bf16_pair_kernel<<<grid, threads, smem, stream>>>(tmA, tmB, args, g);
+  const int base_threads = WIDE ? kWideThreads : kGemmThreads;
+  const int threads = g.enabled ? base_threads + 32 * g.push_ctas : base_threads;
+  gemm_bf16_pair_kernel<WIDE><<<grid, threads, smem, stream>>>(tmA, tmB, args, g);
   count_launch();
   MB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
-// True when the 256x256 CTA-pair kernel is the better choice. Measured on B200 against the single-CTA 128x256 kernel:
-// the pair wins by 5-15 % for weight gradients (both operands MN-major) and for long reductions (K >= 8192), and is
-// level or slightly behind elsewhere; it needs enough tiles to fill every pair of SMs.
-static bool prefer_pair_kernel(int M, int N, int K, int a_mn) {
-  const long long tiles = static_cast<long long>((M + kPairTile - 1) / kPairTile) * ((N + kPairTile - 1) / kPairTile);
-  if (tiles < 2 * (sm_count() / 2)) return false;
-  return a_mn || K >= 8192;
+// Kernel choice. Relative throughputs per SM measured on B200 at K = 4096 (fraction of the math-only rate of the
+// pipeline): 256x512 pair tiles ~0.9, 256x256 pair tiles and 128x256 single-CTA tiles ~0.7 (shared-memory bandwidth
+// bound: TMA writes and UMMA operand reads share it), 128x128 tiles ~0.4. The estimate is waves x tile area / rate;
+// wide tiles lose when the problem has too few of them to fill the 74 SM pairs.
+enum GemmKind { kKindSingle128 = 128, kKindSingle256 = 256, kKindPair = 512, kKindWide = 1024 };
+
+static GemmKind choose_gemm_kind(int M, int N) {
+  const int sms = sm_count(), pairs = sms / 2;
+  auto cost = [&](int tm, int tn, int slots, double rate_per_slot) {
+    const long long tiles = static_cast<long long>((M + tm - 1) / tm) * ((N + tn - 1) / tn);
+    const long long waves = (tiles + slots - 1) / slots;
+    return static_cast<double>(waves) * tm * tn / rate_per_slot;
+  };
+  GemmKind best = kKindSingle128;
+  double best_cost = cost(128, 128, sms, 0.4);
+  const double c256 = cost(128, 256, sms, 0.7);
+  if (c256 < best_cost) best = kKindSingle256, best_cost = c256;
+  const double cwide = cost(256, 512, pairs, 2 * 0.9);
+  if (cwide < best_cost) best = kKindWide, best_cost = cwide;
+  return best;
 }
 
 template <int BN, int STAGES>
@@ -761,6 +856,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
 static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
 static long long* g_trace = nullptr;
 static int g_pair_group_m = 8;
+static int g_debug_mode = 0;
+static int g_debug_stages = 0;
 
 }  // namespace mb
 
@@ -772,6 +869,11 @@ MB_API void mb_gemm_set_trace(long long* buf) { mb::g_trace = buf; }
 MB_API void mb_gemm_set_tuning(int group_m) {
   if (group_m > 0) mb::g_pair_group_m = group_m;
 }
+// Timing probes of the CTA-pair kernel (results are meaningless): 1 = math only, 2 = loads only, 0 = normal.
+MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
+MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
+// Debug: cap the number of CTA pairs of the pair kernel (0 = one pair per two SMs).
+MB_API void mb_gemm_set_debug_max_pairs(int pairs) { mb::g_debug_max_pairs = pairs; }
 
 MB_API void mb_gemm_debug_descriptor(int a_lbo, int a_sbo, int a_kstep, int b_lbo, int b_sbo, int b_kstep) {
   int v[6] = {a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
@@ -780,7 +882,8 @@ MB_API void mb_gemm_debug_descriptor(int a_lbo, int a_sbo, int a_kstep, int b_lb
 
 // C[M,N] (+)= op(A) op(B) (+bias). Leading dimensions are in elements; bf16 operands need them (and the base
 // addresses) to be multiples of 8 elements / 16 bytes because the operands are fetched with TMA.
-// block_n: 0 = choose; 128 or 256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel (256x256 tiles).
+// block_n: 0 = choose; 128 or 256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel (256x256 tiles);
+// 1024 = CTA-pair kernel with 256x512 tiles.
 MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn, long long ldb, void* C,
                         long long ldc, int M, int N, int K, int out_fp32, int accumulate, const void* bias,
                         int block_n, cudaStream_t stream) {
@@ -810,6 +913,8 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   args.status = status;
   args.trace = g_trace;
   args.group_m = g_pair_group_m;
+  args.debug_mode = g_debug_mode;
+  args.stages = g_debug_stages;
   args.a_lbo = a_mn ? 8192u : 16u, args.a_sbo = 1024u, args.a_kstep = a_mn ? 2048u : 32u;
   args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;
   {
@@ -818,13 +923,9 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
       if (g_desc_override[i] >= 0) *f[i] = static_cast<unsigned>(g_desc_override[i]);
   }
 
-  int bn = block_n;
-  const bool pair = block_n == 512 || (block_n == 0 && prefer_pair_kernel(M, N, K, a_mn));
-  if (pair) bn = 128;   // each CTA of a pair stages 128 rows of B
-  if (bn != 128 && bn != 256) {
-    const long long tiles256 = static_cast<long long>(args.tiles_m) * ((N + 255) / 256);
-    bn = (N <= 128 || tiles256 < sm_count()) ? 128 : 256;
-  }
+  const int kind = (block_n == 128 || block_n == 256 || block_n == 512 || block_n == 1024) ? block_n : choose_gemm_kind(M, N);
+  const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
+  const int bn = wide ? 256 : (pair ? 128 : kind);   // rows of B staged per CTA and k-block
   CUtensorMap tmA, tmB;
   bool ok;
   if (!a_mn)
@@ -837,7 +938,8 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   else
     ok = encode_tmap_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBK, 2, true);
   if (!ok) return -4;
-  if (pair) return launch_gemm_pair(tmA, tmB, args, stream);
+  if (wide) return launch_gemm_pair<true>(tmA, tmB, args, stream);
+  if (pair) return launch_gemm_pair<false>(tmA, tmB, args, stream);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream);
   return launch_gemm<128, 6>(tmA, tmB, args, stream);
 }
@@ -880,6 +982,8 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.status = status;
   args.trace = nullptr;
   args.group_m = g_pair_group_m;
+  args.debug_mode = g_debug_mode;
+  args.stages = g_debug_stages;
   args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
   args.b_lbo = 16u, args.b_sbo = 1024u, args.b_kstep = 32u;
   GatherArgs g;
@@ -896,12 +1000,14 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
     g.pads[r] = r < world ? pads[r] : 0ull;
   }
   const __nv_bfloat16* a_base = reinterpret_cast<const __nv_bfloat16*>(gathered[rank]) + static_cast<long long>(seq & 1u) * buf_elems;
-  const bool pair = prefer_pair_kernel(args.M, N, K, 0);
-  const int bn = pair ? 128 : ((N <= 128 || static_cast<long long>(args.tiles_m) * ((N + 255) / 256) < sm_count()) ? 128 : 256);
+  const int kind = choose_gemm_kind(args.M, N);
+  const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
+  const int bn = wide ? 256 : (pair ? 128 : kind);
   CUtensorMap tmA, tmB;
   if (!encode_tmap_2d(&tmA, a_base, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM, 2, true)) return -5;
   if (!encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true)) return -5;
-  if (pair) return launch_gemm_pair(tmA, tmB, args, stream, &g);
+  if (wide) return launch_gemm_pair<true>(tmA, tmB, args, stream, &g);
+  if (pair) return launch_gemm_pair<false>(tmA, tmB, args, stream, &g);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream, &g);
   return launch_gemm<128, 6>(tmA, tmB, args, stream, &g);
 }

@@ -27,7 +27,7 @@ def _rel_err(c, ref):
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (200, 328, 136), (4096, 1024, 512)])
-@pytest.mark.parametrize("block_n", [128, 256, 512])   # 512 = CTA-pair kernel (tcgen05 cta_group::2, 256x256 tiles)
+@pytest.mark.parametrize("block_n", [128, 256, 512, 1024])   # 512 / 1024 = CTA-pair kernels (cta_group::2), 256x256 / 256x512 tiles
 def test_gemm_layouts(a_mn, b_mn, shape, block_n):
     M, N, K = shape
     a, b = _mk(M, N, K, a_mn, b_mn)
@@ -41,14 +41,15 @@ def test_gemm_pair_kernel_many_tiles_per_pair():
     """More 256x256 tiles than SM pairs, several trips round the stage ring, ragged M/N/K edges, fp32 accumulate."""
     M, N, K = 4000, 5000, 1096
     a, b = _mk(M, N, K, False, False, seed=3)
-    c = gemm(a, b, block_n=512)
-    _lib.fetch_status()
     ref = _ref(a, b, False, False)
-    assert _rel_err(c, ref) < 1e-2
-    out = torch.ones((M, N), device="cuda", dtype=torch.float32)
-    gemm(a, b, out=out, accumulate=True, block_n=512)
-    _lib.fetch_status()
-    assert _rel_err(out, ref + 1.0) < 2e-3
+    for block_n in (512, 1024):
+        c = gemm(a, b, block_n=block_n)
+        _lib.fetch_status()
+        assert _rel_err(c, ref) < 1e-2
+        out = torch.ones((M, N), device="cuda", dtype=torch.float32)
+        gemm(a, b, out=out, accumulate=True, block_n=block_n)
+        _lib.fetch_status()
+        assert _rel_err(out, ref + 1.0) < 2e-3
 
 
 def test_gemm_fp32_accumulate_and_bias():
