@@ -51,8 +51,12 @@ class LlamaRMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size))
         self.eps = eps
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return rms_norm(x, self.weight, self.eps)
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
+        """``norm(x)``; with ``residual``: ``(norm(x + residual), x + residual)`` in one pass over the row. Going through
+        the module call (rather than reading ``weight`` from outside) keeps parameter-sharding hooks in the loop."""
+        if residual is None:
+            return rms_norm(x, self.weight, self.eps)
+        return add_rms_norm(x, residual, self.weight, self.eps)
 
 
 class LlamaRotaryEmbedding(nn.Module):
@@ -160,8 +164,7 @@ class LlamaDecoderLayer(nn.Module):
     def forward(self, x, position_offset: int = 0, position_ids=None, sequence_ids=None):
         a = self.self_attn(self.input_layernorm(x), position_offset=position_offset, position_ids=position_ids,
                            sequence_ids=sequence_ids)
-        n = self.post_attention_layernorm
-        y, x = add_rms_norm(a, x, n.weight, n.eps)   # x <- x + a ; y = norm(x), one pass
+        y, x = self.post_attention_layernorm(a, residual=x)   # x <- x + a ; y = norm(x), one pass
         return x + self.mlp(y)
 
 

@@ -1,0 +1,96 @@
+"""Logical (safetensors) checkpoints: file-format round trips and runtime <-> logical conversion across layouts."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import yaml
+
+from tests.dist_utils import free_port
+from maltos_b200.state.logical_checkpoint import (LogicalCheckpointTensorReader, iter_logical_checkpoint_tensors, load_logical_checkpoint,
+                                                  load_logical_tensor, save_logical_checkpoint)
+
+ROOT = Path(__file__).resolve().parents[1]
+MODEL = {"type": "llama", "hidden_size": 64, "num_heads": 4, "num_kv_heads": 2, "intermediate_size": 128, "num_layers": 2,
+         "vocab_size": 256}
+
+
+def test_logical_file_roundtrip_sharded_and_hf_prefix(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    tensors = {f"layers.{i}.w": torch.randn(16, 8, generator=g) for i in range(5)}
+    tensors["lm_head.weight"] = torch.randn(4, 8, generator=g).bfloat16()
+    save_logical_checkpoint(tmp_path / "a", tensors, max_shard_size_bytes=16 * 8 * 4 * 2)
+    index = json.loads((tmp_path / "a" / "model.safetensors.index.json").read_text())
+    assert index["metadata"]["format"] == "logical_model" and index["metadata"]["version"] == 1
+    assert len(set(index["weight_map"].values())) == 3 and all("-of-00003" in f for f in index["weight_map"].values())
+    back = load_logical_checkpoint(tmp_path / "a")
+    assert set(back) == set(tensors) and all(torch.equal(back[k], tensors[k]) for k in tensors)
+    assert torch.equal(load_logical_tensor(tmp_path / "a", "layers.3.w"), tensors["layers.3.w"])
+    assert dict(iter_logical_checkpoint_tensors(tmp_path / "a")).keys() == tensors.keys()
+    reader = LogicalCheckpointTensorReader(tmp_path / "a")
+    assert len(reader) == 6 and torch.equal(reader["lm_head.weight"], tensors["lm_head.weight"])
+    with pytest.raises(KeyError):
+        reader["nope"]
+    # an HF-style index: no format tag, names prefixed with "model." except lm_head.weight
+    from safetensors.torch import save_file
+
+    hf = tmp_path / "hf"
+    hf.mkdir()
+    save_file({"model.embed.weight": tensors["layers.0.w"], "lm_head.weight": tensors["lm_head.weight"]}, str(hf / "x.safetensors"))
+    (hf / "model.safetensors.index.json").write_text(json.dumps(
+        {"metadata": {"total_size": 1}, "weight_map": {"model.embed.weight": "x.safetensors", "lm_head.weight": "x.safetensors"}}))
+    hf_back = load_logical_checkpoint(hf)
+    assert set(hf_back) == {"embed.weight", "lm_head.weight"} and torch.equal(hf_back["embed.weight"], tensors["layers.0.w"])
+    with pytest.raises(ValueError):
+        load_logical_checkpoint(tmp_path / "missing")
+
+
+def _run(cmd, nproc=1):
+    env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=str(ROOT))
+    if nproc > 1:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+               "--master-port", str(free_port())] + cmd
+    else:
+        cmd = [sys.executable] + cmd
+    out = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=420)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    return out.stdout
+
+
+def _recipe(path, parallel):
+    cfg = {"seed": 1, "data": {"seq_len": 32, "micro_batch_size": 2}, "model": MODEL, "parallel": parallel,
+           "training": {"max_steps": 2, "grad_accum_steps": 1, "lr": 1e-3}}
+    path.write_text(yaml.safe_dump(cfg))
+    return path
+
+
+def test_runtime_logical_runtime_across_layouts(tmp_path):
+    data = tmp_path / "tokens"
+    data.mkdir()
+    np.random.default_rng(0).integers(0, 256, size=6000, dtype=np.uint32).tofile(data / "tokens_00000.bin")
+    # 1. train two steps as DP2 + ZeRO-3 and keep the runtime checkpoint
+    src = _recipe(tmp_path / "src.yaml", {"dp_size": 2, "zero_stage": 3})
+    _run(["-m", "maltos_b200.tools.train", "--config", str(src), "--data", str(data), "--checkpoint-dir", str(tmp_path / "rt_a"),
+          "--checkpoint-every", "2", "--log-every", "1"], nproc=2)
+    step_a = tmp_path / "rt_a" / "step_00000002"
+    assert (step_a / "manifest.json").is_file()
+    # 2. runtime -> logical (single process, recipe read from the runtime spec)
+    _run(["-m", "maltos_b200.tools.convert_checkpoint", "runtime-to-logical", "--checkpoint", str(step_a), "--output", str(tmp_path / "logical_a")])
+    logical_a = load_logical_checkpoint(tmp_path / "logical_a")
+    assert len(logical_a) > 10 and all(t.dtype == torch.float32 for t in logical_a.values())
+    # 3. logical -> runtime for a TP2 + SP layout, then back to logical: every tensor must survive bit for bit
+    dst = _recipe(tmp_path / "dst.yaml", {"tp_size": 2, "use_sp": True})
+    _run(["-m", "maltos_b200.tools.convert_checkpoint", "logical-to-runtime", "--config", str(dst), "--checkpoint", str(tmp_path / "logical_a"),
+          "--output", str(tmp_path / "rt_b")], nproc=2)
+    step_b = tmp_path / "rt_b" / "step_00000000"
+    manifest = json.loads((step_b / "manifest.json").read_text())
+    assert manifest["world_size"] == 2 and not [a for a in manifest["artifacts"] if a["kind"] == "optimizer"]
+    _run(["-m", "maltos_b200.tools.convert_checkpoint", "runtime-to-logical", "--checkpoint", str(step_b), "--output", str(tmp_path / "logical_b")])
+    logical_b = load_logical_checkpoint(tmp_path / "logical_b")
+    assert set(logical_a) == set(logical_b)
+    for name in logical_a:
+        assert torch.equal(logical_a[name], logical_b[name]), name
