@@ -361,7 +361,7 @@ def run_reference(args) -> None:
                 "--grad-accum-steps", str(accum), "--dp-size", "1", "--tp-size", str(tp), "--zero-stage", "0",
                 "--precision", "bf16" if use_cuda else "fp32", "--activation-checkpointing", "--fused-adamw",
                 "--lr", "3e-4", "--weight-decay", "0.1", "--adam-beta1", "0.9", "--adam-beta2", "0.95", "--seed", "0",
-                "--attention-backend", os.environ.get("BENCH_REF_ATTENTION", "flash_attn") if use_cuda else "sdpa_auto", "--disable-metrics"]
+                "--attention-backend", os.environ.get("BENCH_REF_ATTENTION", "sdpa_auto"), "--disable-metrics"]
         if tp > 1:
             argv.append("--use-sp")
         if not use_cuda:
