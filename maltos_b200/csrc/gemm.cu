@@ -26,6 +26,23 @@ constexpr int kWideThreads = kGemmThreads + 32 * kEpiWarps;   // 256x512 kernel:
 constexpr int kMaxPushThreads = 128;  // extra warps per block that copy rows to peers in the fused all-gather launch
 constexpr int kGroupM = 8;  // tiles of one N column are visited for 8 consecutive M blocks (L2 reuse of B)
 
+// Reduce-scatter fused into the GEMM epilogue (row-parallel layers; sequence-parallel output). Output row m belongs to
+// rank owner(m) = (m % s_rows) / rows_per_chunk; instead of C, the bf16 partial tile is stored straight into slot
+// `rank` of the owner's staging buffer over NVLink while later tiles are still being computed; the owner's reduce
+// kernel (rs_reduce_kernel) sums the `world` slots once every writer's flag has arrived. Signal-pad words (uint32):
+//   [64 + buf*8 + src]   partial of `src` is complete in my staging buffer `buf`          (written by src)
+//   [96 + buf*8 + owner] `owner` has finished reducing ITS staging buffer `buf`           (written by owner)
+//   [128] finished GEMM blocks of the running call (local)    [129] finished reduce blocks (local)
+struct ScatterArgs {
+  int enabled;
+  int rank, world;
+  int rows_per_chunk;     // S / T
+  int s_rows;             // S
+  unsigned seq;
+  unsigned long long slot_base[8];   // per owner: address of slot `rank` in the owner's staging buffer of this call
+  unsigned long long pads[8];
+};
+
 struct GemmArgs {
   void* C;
   const __nv_bfloat16* bias;  // [N] or nullptr
@@ -42,6 +59,7 @@ struct GemmArgs {
   int stages;         // debug: ring depth used by the CTA-pair kernel (0 = all)
   int debug_mode;     // 0 normal; 1 = MMAs without waiting for data (producer idle); 2 = loads without MMAs (timing probes)
   long long* trace;   // debug: per-CTA cycle counters {mma total, wait full, wait tempty, producer wait empty} or nullptr
+  ScatterArgs sc;
 };
 
 // Sequence-parallel all-gather fused into the GEMM (A operand = rows gathered from all ranks of the TP group).
@@ -157,6 +175,42 @@ __device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_
   }
 }
 
+// First M block a rank visits: with a fused all-gather its own rows (already local), with a fused reduce-scatter the
+// rows of the next rank (remote partials leave first, the rank's own rows need no transfer and come last).
+__device__ __forceinline__ int tile_rotation(const GatherArgs& g, const ScatterArgs& sc, int tile_m) {
+  if (g.enabled) return (g.rank * g.rows_per_chunk) / tile_m;
+  if (sc.enabled) return (((sc.rank + 1) % sc.world) * sc.rows_per_chunk) / tile_m;
+  return 0;
+}
+
+// Fused reduce-scatter, start of the kernel (one thread): every owner must have finished reducing the call that last
+// used this staging buffer (two calls ago) before its slot is overwritten. Bounded; false on timeout.
+__device__ bool scatter_wait_owners(const ScatterArgs& sc, int* status) {
+  const unsigned* my_pad = reinterpret_cast<const unsigned*>(sc.pads[sc.rank]);
+  const int buf = static_cast<int>(sc.seq & 1u);
+  for (int r = 0; r < sc.world; ++r) {
+    if (!wait_flag_reached(my_pad + 96 + buf * 8 + r, sc.seq - 2u, nullptr)) {
+      atomicOr(&status[0], MB_ERR_PEER_TIMEOUT);
+      status[2] = r;
+      return false;
+    }
+  }
+  return true;
+}
+
+// Fused reduce-scatter, end of the kernel (one thread per block, after a block-wide barrier that follows every thread's
+// __threadfence_system): the last block tells every owner that this rank's partial is complete.
+__device__ void scatter_publish(const ScatterArgs& sc, unsigned n_blocks) {
+  unsigned* my_pad = reinterpret_cast<unsigned*>(sc.pads[sc.rank]);
+  const unsigned done = atomicAdd(my_pad + 128, 1u);
+  if (done == n_blocks - 1) {
+    atomicExch(my_pad + 128, 0u);
+    __threadfence_system();
+    const int buf = static_cast<int>(sc.seq & 1u);
+    for (int r = 0; r < sc.world; ++r) st_release_sys(reinterpret_cast<unsigned*>(sc.pads[r]) + 64 + buf * 8 + sc.rank, sc.seq);
+  }
+}
+
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk, int group_m = kGroupM) {
   const int kGroupM = group_m;
   const int per_group = kGroupM * tiles_n;
@@ -196,6 +250,12 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& p, int row, int
     }
   } else {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.sc.enabled) {   // fused reduce-scatter: the row goes to its owner's staging slot (peer memory)
+      const int b = row / p.sc.s_rows, s = row - b * p.sc.s_rows;
+      const int owner = s / p.sc.rows_per_chunk;
+      const long long local = static_cast<long long>(b) * p.sc.rows_per_chunk + (s - owner * p.sc.rows_per_chunk);
+      dst = reinterpret_cast<__nv_bfloat16*>(p.sc.slot_base[owner]) + local * p.ldc + col0;
+    }
     if (vec_ok && !p.accumulate && col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
       // 64 contiguous bytes of one row as two 32-byte stores
 #pragma unroll
@@ -270,7 +330,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], kEpiWarps);
     }
-    *abort_flag = 0;
+    *abort_flag = (p.sc.enabled && !scatter_wait_owners(p.sc, p.status)) ? 1 : 0;
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -292,13 +352,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       const int s_rows = g.enabled ? g.rows_per_chunk * g.world : 1;
-      const int m_rot = g.enabled ? (g.rank * g.rows_per_chunk) / kBM : 0;
+      const int m_rot = tile_rotation(g, p.sc, kBM);
       const int gbuf = static_cast<int>(g.seq & 1u);
       const unsigned* my_pad = g.enabled ? reinterpret_cast<const unsigned*>(g.pads[g.rank]) : nullptr;
       for (int tile = cta; ok && tile < total_tiles; tile += n_ctas) {
         int m_blk, n_blk;
         tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
-        if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;   // own rows first, then the other sources in ring order
+        m_blk = (m_blk + m_rot) % p.tiles_m;   // gather: own rows first; scatter: the next rank's rows first
         if (g.enabled && is_a) {
           // wait for a source only when its rows are needed
           const int row_lo = m_blk * kBM, row_hi = min(row_lo + kBM, p.M) - 1;
@@ -409,11 +469,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    const int m_rot_e = g.enabled ? (g.rank * g.rows_per_chunk) / kBM : 0;
+    const int m_rot_e = tile_rotation(g, p.sc, kBM);
     for (int tile = cta; tile < total_tiles; tile += n_ctas) {
       int m_blk, n_blk;
       tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk);
-      if (g.enabled) m_blk = (m_blk + m_rot_e) % p.tiles_m;
+      m_blk = (m_blk + m_rot_e) % p.tiles_m;
       bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -438,6 +498,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
+  if (p.sc.enabled) __threadfence_system();   // this thread's partial-tile stores to peer memory
   __syncthreads();
   if (*abort_flag) {
     // Give copies that may still be in flight time to land before the CTA's shared memory goes away.
@@ -451,6 +512,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (p.sc.enabled && threadIdx.x == 0 && !*abort_flag) scatter_publish(p.sc, gridDim.x);
   if (g.enabled && threadIdx.x == 0 && !*abort_flag) {
     // the last GEMM block to finish tells every rank that this rank's gathered buffer may be overwritten
     unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
@@ -525,7 +587,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 2 * EPI_WARPS);
     }
-    *abort_flag = 0;
+    *abort_flag = (p.sc.enabled && !scatter_wait_owners(p.sc, p.status)) ? 1 : 0;
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -546,7 +608,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
   __syncthreads();
 
-  const int m_rot = g.enabled ? (g.rank * g.rows_per_chunk) / kPairTile : 0;
+  const int m_rot = tile_rotation(g, p.sc, kPairTile);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
@@ -566,7 +628,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
         int m_blk, n_blk;
         tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
-        if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;
+        m_blk = (m_blk + m_rot) % p.tiles_m;
         const int m0 = m_blk * kPairTile + static_cast<int>(cta_rank) * 128;
         const int n0 = n_blk * TILE_N + static_cast<int>(cta_rank) * B_ROWS;
         if (is_a && g.enabled && m0 < p.M) {
@@ -700,7 +762,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int tile = pair; tile < total_tiles; tile += n_pairs) {
       int m_blk, n_blk;
       tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
-      if (g.enabled) m_blk = (m_blk + m_rot) % p.tiles_m;
+      m_blk = (m_blk + m_rot) % p.tiles_m;
       bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -740,6 +802,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
+  if (p.sc.enabled) __threadfence_system();   // this thread's partial-tile stores to peer memory
   __syncthreads();
   // Neither CTA may leave while the other can still read its shared memory (UMMA operands) or signal its barriers.
   cluster_arrive();
@@ -755,6 +818,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (p.sc.enabled && threadIdx.x == 0 && !*abort_flag) scatter_publish(p.sc, gridDim.x);
   if (g.enabled && threadIdx.x == 0 && !*abort_flag) {
     unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
     const unsigned done = atomicAdd(my_pad + 32, 1u);
@@ -852,6 +916,55 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   return 0;
 }
 
+// Owner side of the fused reduce-scatter: out[r, :] = sum over sources of slot[src][r, :] (fp32 accumulation), after
+// every source's flag for this call has arrived. One thread per block does the (bounded) waiting.
+__global__ void __launch_bounds__(256)
+rs_reduce_kernel(const __nv_bfloat16* __restrict__ stage, long long slot_elems, int world, int rank, unsigned seq,
+                 const unsigned long long* __restrict__ pads_dev, unsigned long long my_pad_addr, __nv_bfloat16* __restrict__ out,
+                 long long n_vec, int* status) {
+  __shared__ int s_ok;
+  unsigned* my_pad = reinterpret_cast<unsigned*>(my_pad_addr);
+  const int buf = static_cast<int>(seq & 1u);
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    for (int src = 0; ok && src < world; ++src) ok = wait_flag_reached(my_pad + 64 + buf * 8 + src, seq, nullptr);
+    if (!ok) atomicOr(&status[0], MB_ERR_PEER_TIMEOUT);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const uint4* base = reinterpret_cast<const uint4*>(stage);
+    const long long slot_vec = slot_elems >> 3;
+    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int src = 0; src < world; ++src) {
+        const uint4 q = base[src * slot_vec + v];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]), o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]), o.w = pack_bf16x2(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(out)[v] = o;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned done = atomicAdd(my_pad + 129, 1u);
+    if (done == gridDim.x - 1) {   // staging buffer fully read: every writer may reuse its slot two calls from now
+      atomicExch(my_pad + 129, 0u);
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) st_release_sys(reinterpret_cast<unsigned*>(pads_dev[r]) + 96 + buf * 8 + rank, seq);
+    }
+  }
+}
+
 // Debug override of the descriptor geometry {lbo, sbo, kstep} per operand; negative = built-in value.
 static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
 static long long* g_trace = nullptr;
@@ -911,6 +1024,7 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   args.tiles_m = (M + kBM - 1) / kBM;
   args.k_blocks = (K + kBK - 1) / kBK;
   args.status = status;
+  args.sc.enabled = 0;
   args.trace = g_trace;
   args.group_m = g_pair_group_m;
   args.debug_mode = g_debug_mode;
@@ -980,6 +1094,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.tiles_m = (args.M + kBM - 1) / kBM;
   args.k_blocks = (K + kBK - 1) / kBK;
   args.status = status;
+  args.sc.enabled = 0;
   args.trace = nullptr;
   args.group_m = g_pair_group_m;
   args.debug_mode = g_debug_mode;
@@ -1010,4 +1125,82 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   if (pair) return launch_gemm_pair<false>(tmA, tmB, args, stream, &g);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream, &g);
   return launch_gemm<128, 6>(tmA, tmB, args, stream, &g);
+}
+
+// Row-parallel GEMM fused with the sequence-parallel reduce-scatter:
+//   out[B*S/T, N] = sum over ranks of (X[B*S, K_local] op(W))  restricted to this rank's rows
+// op(W) = W[N, K]^T (b_mn = 0, forward of a row-parallel layer) or W[K, N] (b_mn = 1, input gradient of a column-parallel
+// layer). `stage` / `pads`: for every rank, the address at which its double-buffered staging buffer (2 x world slots of
+// B*S/T x N bf16) / signal pad is mapped here; `pads_dev` the same pad table in device memory. `seq` counts the calls
+// of this entry point on the context (1, 2, ...), identical on all ranks.
+MB_API int mb_gemm_rs_bf16(const void* X, long long lda, const void* W, int b_mn, long long ldb, void* out, int batches,
+                           int rows_per_chunk, int N, int K, int rank, int world, unsigned seq,
+                           const unsigned long long* stage, const unsigned long long* pads,
+                           const unsigned long long* pads_dev, cudaStream_t stream) {
+  using namespace mb;
+  if (world < 2 || world > kMaxPeers) {
+    set_last_error("mb_gemm_rs_bf16: group size must be in [2, 8]");
+    return -1;
+  }
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) {
+    set_last_error("mb_gemm_rs_bf16: operands must be 16-byte aligned with N and leading dimensions multiple of 8");
+    return -2;
+  }
+  int* status = status_ptr();
+  if (!status) return -4;
+  const long long rows_local = static_cast<long long>(batches) * rows_per_chunk;
+  const long long M = rows_local * world;
+  const long long slot_elems = rows_local * N;
+  GemmArgs args;
+  args.C = nullptr;
+  args.bias = nullptr;
+  args.ldc = N;
+  args.M = static_cast<int>(M), args.N = N, args.K = K;
+  args.a_mn = 0, args.b_mn = b_mn ? 1 : 0;
+  args.out_fp32 = 0, args.accumulate = 0;
+  args.tiles_m = (args.M + kBM - 1) / kBM;
+  args.k_blocks = (K + kBK - 1) / kBK;
+  args.status = status;
+  args.trace = nullptr;
+  args.group_m = g_pair_group_m;
+  args.debug_mode = 0;
+  args.stages = 0;
+  args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
+  args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;
+  ScatterArgs& sc = args.sc;
+  sc.enabled = 1;
+  sc.rank = rank, sc.world = world;
+  sc.rows_per_chunk = rows_per_chunk, sc.s_rows = rows_per_chunk * world;
+  sc.seq = seq;
+  const long long buf_off = static_cast<long long>(seq & 1u) * world * slot_elems;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    sc.slot_base[r] = r < world ? stage[r] + static_cast<unsigned long long>((buf_off + rank * slot_elems) * 2) : 0ull;
+    sc.pads[r] = r < world ? pads[r] : 0ull;
+  }
+  const int kind = choose_gemm_kind(args.M, N);
+  const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
+  const int bn = wide ? 256 : (pair ? 128 : kind);
+  CUtensorMap tmA, tmB;
+  if (!encode_tmap_2d(&tmA, X, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, kBK, kBM, 2, true)) return -5;
+  bool ok;
+  if (!b_mn)
+    ok = encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true);
+  else
+    ok = encode_tmap_2d(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBK, 2, true);
+  if (!ok) return -5;
+  int rc;
+  if (wide) rc = launch_gemm_pair<true>(tmA, tmB, args, stream);
+  else if (pair) rc = launch_gemm_pair<false>(tmA, tmB, args, stream);
+  else if (bn == 256) rc = launch_gemm<256, 4>(tmA, tmB, args, stream);
+  else rc = launch_gemm<128, 6>(tmA, tmB, args, stream);
+  if (rc != 0) return rc;
+  const __nv_bfloat16* my_stage = reinterpret_cast<const __nv_bfloat16*>(stage[rank]) + buf_off;
+  const long long n_vec = slot_elems >> 3;
+  long long blocks = (n_vec + 255) / 256;
+  if (blocks > 4LL * sm_count()) blocks = 4LL * sm_count();
+  rs_reduce_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, stream>>>(
+      my_stage, slot_elems, world, rank, seq, pads_dev, pads[rank], static_cast<__nv_bfloat16*>(out), n_vec, status);
+  count_launch();
+  MB_CHECK_CUDA(cudaGetLastError());
+  return 0;
 }

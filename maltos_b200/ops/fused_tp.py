@@ -6,7 +6,10 @@ CUDA-IPC mapped memory, per-source flags), while the tcgen05 GEMM blocks start o
 reach a peer's rows only after its flag arrived - the transfer hides behind the math tile by tile. Buffers are
 double-buffered by call parity and a "consumed" flag keeps a fast rank from overwriting a buffer a slow rank still reads.
 
-Backward (and the GEMM -> reduce-scatter of row-parallel layers) currently use NCCL collectives around the tcgen05 GEMMs.
+``linear_reduce_scatter`` / the input gradient of ``all_gather_grouped_linear``: GEMM and reduce-scatter are one GEMM
+launch whose epilogue stores partial tiles into the owner rank's staging slots over NVLink, plus a small reduce kernel
+(:func:`gemm_reduce_scatter`). The remaining backward collectives (re-gather of ``x`` for the weight gradient, gather of
+``dy`` of row-parallel layers) use NCCL around the tcgen05 GEMMs.
 """
 from __future__ import annotations
 
@@ -43,6 +46,39 @@ def _nccl_reduce_scatter_rows(y_full: torch.Tensor, ctx, B: int, rows: int) -> t
     return out
 
 
+def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool) -> torch.Tensor:
+    """``reduce_scatter_over_ranks(x2 @ op(w))`` along the sequence in ONE GEMM launch plus a small reduce kernel.
+
+    ``x2 [B*S, K_local]``; ``op(w) = w[N, K_local]^T`` (``b_mn=False``) or ``w[K_local, N]`` (``b_mn=True``). The GEMM epilogue
+    stores each bf16 partial tile straight into the owner rank's staging slot over NVLink (tile by tile, behind the math
+    of the following tiles); the owner sums the slots in fp32 once every writer's flag has arrived. Returns this rank's
+    ``[B*rows, N]`` rows. Staging is double-buffered by call parity with a "reduced" flag as back-pressure.
+    """
+    T = symm.world
+    K = x2.shape[1]
+    N = w.shape[1] if b_mn else w.shape[0]
+    if x2.stride(1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    if w.stride(1) != 1 or w.stride(0) % 8:
+        w = w.contiguous()
+    slot_elems = B * rows * N
+    stage = symm.ensure_buffer("sp_scatter", 2 * T * slot_elems * 2)
+    seq = symm.next_seq("scatter")
+    out = torch.empty((B * rows, N), dtype=x2.dtype, device=x2.device)
+    stage_ptrs = (ctypes.c_ulonglong * 8)(*(stage.peer_ptrs + [0] * (8 - T)))
+    pads = (ctypes.c_ulonglong * 8)(*(symm.pad.peer_ptrs + [0] * (8 - T)))
+    rc = _lib.lib().mb_gemm_rs_bf16(
+        _lib.ptr(x2), _lib.c_ll(x2.stride(0)), _lib.ptr(w), _lib.c_int(1 if b_mn else 0), _lib.c_ll(w.stride(0)), _lib.ptr(out),
+        _lib.c_int(B), _lib.c_int(rows), _lib.c_int(N), _lib.c_int(K), _lib.c_int(symm.rank), _lib.c_int(T),
+        ctypes.c_uint(seq & 0xFFFFFFFF), stage_ptrs, pads, _lib.ptr(symm.pad.table), _lib.stream_ptr())
+    _lib.check(rc, "mb_gemm_rs_bf16")
+    return out
+
+
+def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
+    return getattr(symm, "fused_scatter", True) and x2.dtype == torch.bfloat16 and x2.is_cuda and n_out % 8 == 0
+
+
 class _AllGatherGroupedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_local, symm, *weights):
@@ -58,7 +94,7 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         M = B * rows * T
         buf_elems = M * K
         buf = symm.ensure_buffer("sp_gather", 2 * buf_elems * 2)
-        seq = symm.next_seq()
+        seq = symm.next_seq("gather")
         out = torch.empty((M, N), dtype=x_local.dtype, device=x_local.device)
         gathered = (ctypes.c_ulonglong * 8)(*(buf.peer_ptrs + [0] * (8 - T)))
         pads = (ctypes.c_ulonglong * 8)(*(symm.pad.peer_ptrs + [0] * (8 - T)))
@@ -84,8 +120,11 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         dx_local = None
         dws = [None] * len(weights)
         if ctx.needs_input_grad[0]:
-            dx_full = gemm(d2, fused, b_mn=True)                       # [B*S, K]
-            dx_local = _nccl_reduce_scatter_rows(dx_full, symm, B, rows).view(B, rows, K)
+            if _fused_scatter_ok(symm, d2, K):
+                dx_local = gemm_reduce_scatter(d2, fused, symm, B, rows, b_mn=True).view(B, rows, K)
+            else:
+                dx_full = gemm(d2, fused, b_mn=True)                   # [B*S, K]
+                dx_local = _nccl_reduce_scatter_rows(dx_full, symm, B, rows).view(B, rows, K)
         if any(ctx.needs_input_grad[2:]):
             x_full = _nccl_all_gather_rows(x2, symm, B, rows)          # re-gathered, as the forward buffer is recycled
             dwf = gemm(d2, x_full, a_mn=True, b_mn=True)               # [N, K]
@@ -119,8 +158,11 @@ class _LinearReduceScatter(torch.autograd.Function):
         T = symm.world
         rows = S // T
         x2 = x.reshape(B * S, Kin)
-        y_full = gemm(x2, weight)                                       # partial sums [B*S, H]
-        y = _nccl_reduce_scatter_rows(y_full, symm, B, rows)
+        if _fused_scatter_ok(symm, x2, weight.shape[0]):
+            y = gemm_reduce_scatter(x2, weight, symm, B, rows, b_mn=False)
+        else:
+            y_full = gemm(x2, weight)                                   # partial sums [B*S, H]
+            y = _nccl_reduce_scatter_rows(y_full, symm, B, rows)
         ctx.save_for_backward(x2, weight)
         ctx.symm, ctx.dims = symm, (B, S, rows, Kin)
         return y.view(B, rows, weight.shape[0])

@@ -56,7 +56,7 @@ class SymmetricContext:
     def __init__(self, group, rank: int, world: int, device: torch.device) -> None:
         self.group, self.rank, self.world, self.device = group, rank, world, device
         self.buffers: dict[str, SymmetricBuffer] = {}
-        self.seq = 0
+        self.seq: dict[str, int] = {}
         self.pad: SymmetricBuffer | None = None
 
     # ------------------------------------------------------------------ construction
@@ -120,9 +120,10 @@ class SymmetricContext:
         lib.mb_symm_free(ctypes.c_void_p(sb.local_ptr))
         self.buffers.pop(sb.name, None)
 
-    def next_seq(self) -> int:
-        self.seq += 1
-        return self.seq
+    def next_seq(self, protocol: str = "gather") -> int:
+        """Next call number of one flag protocol (each fused op family counts its own calls, starting at 1)."""
+        self.seq[protocol] = self.seq.get(protocol, 0) + 1
+        return self.seq[protocol]
 
     def close(self) -> None:
         if not self.buffers:

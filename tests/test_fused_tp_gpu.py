@@ -52,6 +52,31 @@ def _worker(rank, world, port, queue):
                 results.append((B, rows, K, rep, err, gerr))
                 for w in ws:
                     w.grad = None
+        # row-parallel GEMM fused with the reduce-scatter (forward) and its backward
+        from maltos_b200.ops.fused_tp import linear_reduce_scatter
+
+        for (B, S, Kin, H) in [(1, 512, 256, 256), (2, 384, 128, 512), (1, 2048, 512, 1024)]:
+            w = torch.nn.Parameter((torch.randn(H, Kin, device="cuda", generator=torch.Generator(device="cuda").manual_seed(50 + rank)) * 0.05).bfloat16())
+            g = torch.Generator(device="cuda").manual_seed(200 + rank)
+            rows = S // world
+            for rep in range(3):
+                x = torch.randn(B, S, Kin, device="cuda", generator=g).bfloat16().requires_grad_()
+                y = linear_reduce_scatter(x, w, ctx)
+                ref_full = x.detach().float() @ w.detach().float().t()
+                dist.all_reduce(ref_full, group=group)
+                ref = ref_full.view(B, world, rows, H)[:, rank]
+                err = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+                dy = torch.randn_like(y)
+                y.backward(dy)
+                dy_full = torch.empty(world, B, rows, H, device="cuda", dtype=torch.bfloat16)
+                dist.all_gather_into_tensor(dy_full.view(-1, H), dy.reshape(-1, H).contiguous(), group=group)
+                dyf = dy_full.permute(1, 0, 2, 3).reshape(B, S, H).float()
+                dx_ref = dyf @ w.detach().float()
+                gerr = ((x.grad.float() - dx_ref).abs().max() / dx_ref.abs().max()).item()
+                dw_ref = dyf.reshape(-1, H).t() @ x.detach().float().reshape(-1, Kin)
+                gerr = max(gerr, ((w.grad.float() - dw_ref).abs().max() / dw_ref.abs().max()).item())
+                results.append((B, S, Kin, 10 + rep, err, gerr))
+                w.grad = None
         status = _lib.fetch_status(raise_on_error=False)
         queue.put((rank, "ok", (results, status)))
         ctx.close()
