@@ -118,7 +118,9 @@ __device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_
   const long long s_rows = static_cast<long long>(g.rows_per_chunk) * g.world;   // rows of one batch in the gathered buffer
   unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
   for (int step = 0; step < g.world; ++step) {
-    const int dst = (g.rank + step) % g.world;
+    // Destinations in descending ring order: every rank's GEMM visits the sources as rank, rank+1, rank+2, ..., so
+    // rank r needs the rows of r+1 first - which r+1 delivers first when it starts with destination (r+1)-1.
+    const int dst = (g.rank - step + g.world) % g.world;
     if (tid == 0) {
       // the destination must have finished the call that last used this buffer (two calls ago)
       bool ok = step == 0 ? true : wait_flag_reached(my_pad + 16 + buf * 8 + dst, g.seq - 2u, nullptr);
@@ -970,6 +972,7 @@ static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
 static long long* g_trace = nullptr;
 static int g_pair_group_m = 8;
 static int g_debug_mode = 0;
+static int g_scatter_kind = 0;   // tuning: kernel kind forced for the fused reduce-scatter GEMM (0 = cost model)
 static int g_debug_stages = 0;
 
 }  // namespace mb
@@ -985,6 +988,7 @@ MB_API void mb_gemm_set_tuning(int group_m) {
 // Timing probes of the CTA-pair kernel (results are meaningless): 1 = math only, 2 = loads only, 0 = normal.
 MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
+MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
 // Debug: cap the number of CTA pairs of the pair kernel (0 = one pair per two SMs).
 MB_API void mb_gemm_set_debug_max_pairs(int pairs) { mb::g_debug_max_pairs = pairs; }
 
@@ -1177,7 +1181,8 @@ MB_API int mb_gemm_rs_bf16(const void* X, long long lda, const void* W, int b_mn
     sc.slot_base[r] = r < world ? stage[r] + static_cast<unsigned long long>((buf_off + rank * slot_elems) * 2) : 0ull;
     sc.pads[r] = r < world ? pads[r] : 0ull;
   }
-  const int kind = choose_gemm_kind(args.M, N);
+  int kind = choose_gemm_kind(args.M, N);
+  if (g_scatter_kind > 0) kind = g_scatter_kind;
   const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
   const int bn = wide ? 256 : (pair ? 128 : kind);
   CUtensorMap tmA, tmB;

@@ -14,6 +14,7 @@ launch whose epilogue stores partial tiles into the owner rank's staging slots o
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -75,7 +76,16 @@ def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: i
     return out
 
 
+_SCATTER_KIND = int(os.environ.get("MALTOS_B200_SCATTER_KIND", "0"))
+if _SCATTER_KIND:
+    _lib.lib().mb_gemm_set_scatter_kind(ctypes.c_int(_SCATTER_KIND))
+
+
 def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
+    # Opt-in: on NVSwitch systems NCCL reduces inside the switch, and the epilogue's 32-byte peer stores reach only about
+    # 200 GB/s, so GEMM + NCCL reduce-scatter is currently the faster pair (187 vs 237 us for o_proj at TP=4 on B200).
+    if os.environ.get("MALTOS_B200_FUSED_SCATTER", "0") != "1":
+        return False
     return getattr(symm, "fused_scatter", True) and x2.dtype == torch.bfloat16 and x2.is_cuda and n_out % 8 == 0
 
 
