@@ -26,15 +26,21 @@ from .attn_masking_utils import canonical_position_ids, canonical_sequence_ids
 
 
 class _RingComm:
-    """Shift tensors one rank forward along the ring; requests are posted early and waited late."""
+    """Shift tensors one place forward along a ring; requests are posted early and waited late. The ring is the whole
+    group, or - for per-document dynamic context parallelism - an ordered subset of its ranks (no sub-group is ever
+    created: members talk point to point inside the parent group)."""
 
-    def __init__(self, group) -> None:
+    def __init__(self, group, participant_ranks=None) -> None:
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
-        ranks = dist.get_process_group_ranks(group)
-        self.next_rank = ranks[(self.rank + 1) % self.world]
-        self.prev_rank = ranks[(self.rank - 1) % self.world]
+        members = list(participant_ranks) if participant_ranks is not None else list(range(dist.get_world_size(group)))
+        me = dist.get_rank(group)
+        if me not in members:
+            raise ValueError(f"rank {me} is not a member of ring {members}")
+        self.world = len(members)
+        self.rank = members.index(me)
+        to_global = dist.get_process_group_ranks(group)
+        self.next_rank = to_global[members[(self.rank + 1) % self.world]]
+        self.prev_rank = to_global[members[(self.rank - 1) % self.world]]
 
     def start(self, tensors: list[torch.Tensor]):
         outs, works = [], []
@@ -57,8 +63,8 @@ def _block_visible(q_pos, k_pos) -> bool:
 
 class _RingAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, q_pos, q_seq, group, scale):
-        comm = _RingComm(group)
+    def forward(ctx, q, k, v, q_pos, q_seq, group, scale, participants=None):
+        comm = _RingComm(group, participants)
         B, S, hq, D = q.shape
         out = torch.zeros((B, S, hq, D), dtype=torch.float32, device=q.device)
         lse = torch.full((B, hq, S), float("-inf"), dtype=torch.float32, device=q.device)
@@ -76,13 +82,13 @@ class _RingAttention(torch.autograd.Function):
                 cur = nxt
         result = out.to(q.dtype)
         ctx.save_for_backward(q, k, v, result, lse, q_pos, seq_or_zero)
-        ctx.group, ctx.scale, ctx.has_seq = group, scale, q_seq is not None
+        ctx.group, ctx.scale, ctx.has_seq, ctx.participants = group, scale, q_seq is not None, participants
         return result
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, q_pos, seq_ids = ctx.saved_tensors
-        comm = _RingComm(ctx.group)
+        comm = _RingComm(ctx.group, ctx.participants)
         q_seq = seq_ids if ctx.has_seq else None
         dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
         dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
@@ -105,12 +111,15 @@ class _RingAttention(torch.autograd.Function):
             comm.finish(gworks)
             if nxt is not None:
                 cur = nxt
-        return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None, None, None
+        return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None, None, None, None
 
 
-def flash_ring_attention(q, k, v, group, *, q_positions, q_sequence_ids=None, scale=None, module_id=None, mb_idx: int = 0):
+def flash_ring_attention(q, k, v, group, *, q_positions, q_sequence_ids=None, scale=None, module_id=None, mb_idx: int = 0,
+                         participant_ranks=None):
+    """Ring attention of ``[B, S, h, D]`` blocks over ``group`` or over the ordered subset ``participant_ranks`` of it."""
     with span("maltos::cp.ring.flash" if q.is_cuda else "maltos::cp.ring.eager"):
-        return _RingAttention.apply(q, k, v, q_positions, q_sequence_ids, group, scale)
+        return _RingAttention.apply(q, k, v, q_positions, q_sequence_ids, group, scale,
+                                    tuple(participant_ranks) if participant_ranks is not None else None)
 
 
 class RingAttentionCore(nn.Module):

@@ -1,0 +1,176 @@
+"""ByteScale HDP: scheduler invariants, batch materialisation, and training equivalence with a single process."""
+import random
+
+import pytest
+import torch
+
+from maltos_b200.data.bytescale_hdp import ByteScaleHdpDataLoader, build_bytescale_local_batches, schedule_document_waves
+from maltos_b200.parallel.hdp_helper import (BYTESCALE_HDP_SCHEDULE_KEY, BYTESCALE_HDP_WAVES_KEY, ByteScaleHdpBalancedConfig,
+                                             ByteScaleHdpCostModel, DocumentIndices)
+from maltos_b200.utils.constants import IGNORE_INDEX, PAD_SEQUENCE_ID
+from tests.dist_utils import run_distributed
+
+VOCAB, SEQ = 96, 48
+
+
+def _packed_batch(seed=0, rows=3):
+    """[rows, SEQ] packed rows: documents of random length, the tail of each row is padding."""
+    rng = random.Random(seed)
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(1, VOCAB, (rows, SEQ), generator=g)
+    seq = torch.full((rows, SEQ), PAD_SEQUENCE_ID, dtype=torch.long)
+    pos = torch.zeros((rows, SEQ), dtype=torch.long)
+    labels = torch.full((rows, SEQ), IGNORE_INDEX, dtype=torch.long)
+    for r in range(rows):
+        at, doc = 0, 0
+        while at < SEQ - 4:
+            n = min(rng.choice([3, 5, 9, 14, 30]), SEQ - 2 - at)
+            seq[r, at:at + n] = doc
+            pos[r, at:at + n] = torch.arange(n)
+            labels[r, at:at + n - 1] = ids[r, at + 1:at + n]
+            at += n
+            doc += 1
+    ids[seq == PAD_SEQUENCE_ID] = 0
+    return {"input_ids": ids, "labels": labels, "position_ids": pos, "sequence_ids": seq}
+
+
+def test_cost_model_and_config_validation():
+    cm = ByteScaleHdpCostModel(alpha=0.5, beta=2.0, gamma=3.0)
+    assert cm.sequence_cost(4) == 8 + 8 + 3 and cm.participant_cost(4, 2) == 8 + 3
+    with pytest.raises(ValueError):
+        ByteScaleHdpCostModel(alpha=-1)
+    with pytest.raises(ValueError):
+        ByteScaleHdpBalancedConfig(partition_tokens=7)
+    cfg = ByteScaleHdpBalancedConfig(partition_tokens=8)
+    assert cfg.participant_count(8, world_size=4) == 1 and cfg.participant_count(9, world_size=4) == 2
+    with pytest.raises(ValueError):
+        cfg.participant_count(33, world_size=4)
+    with pytest.raises(ValueError):
+        cfg.validate_tp_sp_partition(tp_size=3, use_sp=True)
+
+
+@pytest.mark.parametrize("world,partition", [(2, 16), (4, 16), (4, 10)])
+def test_schedule_covers_every_token_once_within_capacity(world, partition):
+    batch = _packed_batch(seed=world + partition)
+    docs = DocumentIndices.from_batch(batch)
+    cfg = ByteScaleHdpBalancedConfig(partition_tokens=partition, cost_model=ByteScaleHdpCostModel(1.0, 4.0, 16.0))
+    per_rank = [schedule_document_waves(docs, rank=r, world_size=world, config=cfg, global_valid_targets=1) for r in range(world)]
+    waves = {len(l) for l in per_rank}
+    assert len(waves) == 1                                    # every rank runs the same number of waves
+    seen: dict[tuple[int, int], int] = {}
+    for layouts in per_rank:
+        for lay in layouts:
+            assert lay.placement_tokens <= partition and lay.packed_rows <= 1
+            spans = sorted((d.local_start, d.local_end) for d in lay.documents)
+            assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))      # no overlap inside the row
+            for d in lay.documents:
+                degree = len(d.participant_ranks)
+                assert d.padded_length % (2 * degree) == 0 and d.local_length == d.padded_length // degree
+                assert degree == cfg.participant_count(d.sequence_length, world_size=world)
+                for p in d.document_positions:
+                    if p is not None:
+                        seen[(d.document_id, p)] = seen.get((d.document_id, p), 0) + 1
+    expected = {(i, p) for i, doc in enumerate(docs) for p in range(len(doc.source_indices))}
+    assert set(seen) == expected and set(seen.values()) == {1}
+
+
+def test_materialised_waves_carry_the_right_tokens_and_weights():
+    batch = _packed_batch(seed=5)
+    cfg = ByteScaleHdpBalancedConfig(partition_tokens=16)
+    world = 2
+    total_targets = int((batch["labels"] != IGNORE_INDEX).sum())
+    weight_sum, target_sum = 0.0, 0
+    for rank in range(world):
+        waves, layouts = build_bytescale_local_batches(batch, rank=rank, world_size=world, config=cfg)
+        for wave, lay in zip(waves, layouts):
+            assert wave[BYTESCALE_HDP_SCHEDULE_KEY] is lay
+            n = int((wave["labels"] != IGNORE_INDEX).sum())
+            target_sum += n
+            weight_sum += wave["loss_weight"]
+            for d in lay.documents:
+                for off, (src, p) in enumerate(zip(d.source_indices, d.document_positions)):
+                    col = d.local_start + off
+                    if src is None:
+                        assert wave["sequence_ids"][d.local_row, col] == PAD_SEQUENCE_ID
+                    else:
+                        assert wave["input_ids"][d.local_row, col] == batch["input_ids"][d.source_row, src]
+                        assert wave["position_ids"][d.local_row, col] == p
+    assert target_sum == total_targets and abs(weight_sum - world) < 1e-9
+
+
+class _FixedLoader:
+    consumed_tokens = 0
+
+    def __init__(self, batches):
+        self.batches, self.i = batches, 0
+
+    def next_batch(self, cp_rank=None):
+        b = self.batches[self.i % len(self.batches)]
+        self.i += 1
+        return b
+
+    def state_dict(self):
+        return {"i": self.i}
+
+    def load_state_dict(self, s):
+        self.i = s["i"]
+
+
+def _model():
+    import maltos_b200  # noqa: F401
+    from maltos_b200 import models
+
+    torch.manual_seed(77)
+    return models.TinyTransformer(64, 4, 2, 128, 1e-5, 2, VOCAB, SEQ)
+
+
+def _opt(params):
+    return torch.optim.AdamW(params, lr=1e-2, weight_decay=0.0)
+
+
+def _hdp_worker(rank, world):
+    import maltos_b200  # noqa: F401
+    from maltos_b200.runtime import MeshConfig, RuntimeCore
+    from maltos_b200.runtime.plugins import ddp
+    from maltos_b200.runtime.plugins.hdp import ByteScaleHdpPlugin
+
+    cfg = ByteScaleHdpBalancedConfig(partition_tokens=16, cost_model=ByteScaleHdpCostModel(1.0, 8.0, 32.0))
+    rt = RuntimeCore(model=_model(), mesh=MeshConfig(dp=world), plugins=[ddp.DataParallelPlugin(), ByteScaleHdpPlugin(config=cfg)],
+                     optimizer_factory=_opt, grad_accum_steps=1)
+    rt.setup()
+    loader = ByteScaleHdpDataLoader(_FixedLoader([_packed_batch(seed=11), _packed_batch(seed=12)]), hdp_rank=rank, hdp_world_size=world, config=cfg)
+    losses = []
+    for _ in range(2):
+        env = loader.next_batch()
+        assert len(env[BYTESCALE_HDP_WAVES_KEY]) >= 1
+        loss, should = rt.run_step(env)
+        assert should
+        rt.step_optimizer()
+        losses.append(float(loss))
+    metrics = rt.collect_metrics()
+    params = {n: p.detach().clone() for n, p in rt.model.named_parameters()}
+    rt.close()
+    return losses, params, {k: v for k, v in metrics.items() if "wave" in k}
+
+
+def test_hdp_training_matches_single_process():
+    model = _model()
+    opt = _opt(model.parameters())
+    ref_losses = []
+    for seed in (11, 12):
+        opt.zero_grad(set_to_none=True)
+        out = model(_packed_batch(seed=seed))
+        loss = out.loss if hasattr(out, "loss") else out
+        loss.backward()
+        opt.step()
+        ref_losses.append(float(loss.detach()))
+    ref_params = {n: p.detach().clone() for n, p in model.named_parameters()}
+    world = 2
+    results = run_distributed(_hdp_worker, world)
+    for step in range(2):   # each rank reports world x its share of the global mean
+        total = sum(r[0][step] for r in results) / world
+        assert abs(total - ref_losses[step]) < 2e-4, (total, ref_losses[step])
+    for _, params, wave_metrics in results:
+        assert wave_metrics.get("hdp/real_wave_count", wave_metrics.get("real_wave_count", 1)) >= 1
+        for name, ref in ref_params.items():
+            assert torch.allclose(params[name], ref, atol=2e-4, rtol=1e-3), name
