@@ -1,0 +1,61 @@
+"""Command-line tools that run without a GPU: synthetic throughput profiler and the upload planner."""
+import json
+
+import pytest
+import torch
+
+from maltos_b200.tools import profile_train_perf as ptp
+from maltos_b200.tools.upload_wandb_checkpoint import plan_uploads, sanitize_artifact_name
+from maltos_b200.utils.constants import IGNORE_INDEX, PAD_SEQUENCE_ID
+
+
+def test_packed_synthetic_batch_is_well_formed():
+    cfg = ptp.SyntheticBatchConfig(layout="packed", segment_count_min=2, segment_count_max=5, supervised_fraction_min=0.4,
+                                   supervised_fraction_max=0.6, max_padding_fraction=0.1)
+    b = ptp.make_synthetic_batch(rows=4, seq_len=128, vocab_size=50, config=cfg, generator=torch.Generator().manual_seed(0))
+    ids, labels, pos, seq = b["input_ids"], b["labels"], b["position_ids"], b["sequence_ids"]
+    for r in range(4):
+        pad = seq[r] == PAD_SEQUENCE_ID
+        assert (labels[r][pad] == IGNORE_INDEX).all() and (ids[r][pad] == 0).all()
+        docs = seq[r][~pad]
+        assert (docs[1:] >= docs[:-1]).all() and 2 <= int(docs.max()) + 1 <= 5
+        starts = torch.nonzero(torch.cat([torch.tensor([True]), docs[1:] != docs[:-1]])).flatten()
+        assert (pos[r][starts] == 0).all()
+        # a supervised target is the next token of the same document
+        sup = torch.nonzero(labels[r] != IGNORE_INDEX).flatten()
+        assert len(sup) > 0 and all(seq[r, i] == seq[r, i + 1] and labels[r, i] == ids[r, i + 1] for i in sup.tolist() if i + 1 < 128 and not pad[i + 1])
+    with pytest.raises(ValueError):
+        ptp.SyntheticBatchConfig(layout="ragged")
+
+
+def test_case_file_and_profiler_run(tmp_path):
+    recipe = tmp_path / "r.yaml"
+    recipe.write_text("seed: 1\ndata: {seq_len: 32, micro_batch_size: 2}\nmodel: {type: llama, hidden_size: 64, num_heads: 4, num_kv_heads: 2, "
+                      "intermediate_size: 128, num_layers: 2, vocab_size: 128}\ntraining: {grad_accum_steps: 2, lr: 0.001}\n")
+    cases = tmp_path / "cases.yaml"
+    cases.write_text(f"cases:\n  tiny:\n    description: tiny\n    recipe: {recipe}\n    synthetic: {{packed: true}}\n    warmup: 1\n    steps: 2\n")
+    assert set(ptp._load_cases(cases)) == {"tiny"}
+    ptp.main(["--case-file", str(cases), "--case", "tiny", "--output-dir", str(tmp_path / "out")])
+    summary = json.loads((tmp_path / "out" / "summary.json").read_text())
+    assert summary["timed_steps"] == 2 and summary["tokens_per_step"] == 2 * 32 * 2 and summary["learning_rate"] == 0.0
+    assert summary["synthetic"]["layout"] == "packed" and summary["tokens_per_second"] > 0
+    assert (tmp_path / "out" / "summary.txt").read_text().startswith("case: tiny")
+
+
+def test_upload_plan_validation(tmp_path):
+    assert sanitize_artifact_name("my run/1") == "my-run-1"
+    with pytest.raises(ValueError):
+        sanitize_artifact_name("///")
+    root = tmp_path / "ckpt"
+    (root / "step_00000002").mkdir(parents=True)
+    with pytest.raises(ValueError):
+        plan_uploads(root, [2], "p", [])
+    (root / "runtime_spec.json").write_text("{}")
+    with pytest.raises(ValueError):
+        plan_uploads(root, [2], "p", [])
+    (root / "step_00000002" / "manifest.json").write_text("{}")
+    (root / "step_00000004").mkdir()
+    (root / "step_00000004" / "manifest.json").write_text("{}")
+    plan = plan_uploads(root, [2, 4], "p", ["best"])
+    assert [i["name"] for i in plan] == ["p-step-00000002", "p-step-00000004"]
+    assert plan[0]["aliases"] == ["best", "step_2"] and plan[1]["aliases"] == ["best", "step_4", "latest"]
