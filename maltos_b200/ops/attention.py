@@ -76,9 +76,12 @@ def causal_attention(q, k, v, *, position_ids=None, sequence_ids=None, scale: fl
     if sequence_ids is None:
         return attention(q, k, v, causal=True, scale=scale)
     B, S = q.shape[:2]
-    pos = position_ids
-    if pos is None:
-        pos = torch.arange(S, device=q.device).unsqueeze(0).expand(B, S)
+    if scale is None and _kernel_eligible(q, k, v):
+        # packed rows on the GPU: compact the valid tokens and run ONE variable-length fused attention over all documents
+        from maltos_b200.runtime.layers.flash_utils import flash_attn_fallback_reason, flash_attn_varlen
+
+        if flash_attn_fallback_reason(q) is None:
+            return flash_attn_varlen(q, k, v, sequence_ids)
     # inside a packed row, positions restart per document; visibility needs an order that is monotone in the row,
     # so the row index is used for causality and the document id for the block structure
     order = torch.arange(S, device=q.device).unsqueeze(0).expand(B, S)

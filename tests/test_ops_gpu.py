@@ -222,3 +222,27 @@ def test_causal_attention_matches_fp32_reference(D, Hq, Hkv):
     _close(q.grad, qf.grad, 3e-2)
     _close(k.grad, kf.grad, 3e-2)
     _close(v.grad, vf.grad, 3e-2)
+
+
+def test_packed_document_attention_matches_fp32_reference():
+    from maltos_b200.ops.attention import attention_reference, causal_attention
+    from maltos_b200.utils.constants import PAD_SEQUENCE_ID
+
+    torch.manual_seed(5)
+    B, S, Hq, Hkv, D = 2, 256, 8, 2, 64
+    q, k, v = (torch.randn(B, S, h, D, device=DEV).bfloat16().requires_grad_() for h in (Hq, Hkv, Hkv))
+    seq = torch.full((B, S), PAD_SEQUENCE_ID, dtype=torch.long, device=DEV)
+    seq[0, :100], seq[0, 100:230] = 0, 1
+    seq[1, :17], seq[1, 17:256] = 0, 1
+    out = causal_attention(q, k, v, sequence_ids=seq)
+    keep = (seq != PAD_SEQUENCE_ID).unsqueeze(-1).unsqueeze(-1)
+    do = torch.randn_like(out) * keep
+    out.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    order = torch.arange(S, device=DEV).unsqueeze(0).expand(B, S)
+    ref = attention_reference(qf, kf, vf, q_positions=order, k_positions=order, q_sequence_ids=seq, k_sequence_ids=seq) * keep
+    ref.backward(do.float())
+    _close(out * keep, ref, 2e-2)
+    _close(q.grad, qf.grad, 3e-2)
+    _close(k.grad, kf.grad, 3e-2)
+    _close(v.grad, vf.grad, 3e-2)
