@@ -1063,11 +1063,11 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
 }
 
 // Sequence-parallel all-gather fused into a column-parallel GEMM:
-//   C[B*S, N] = gather_over_ranks(x_local)[B*S, K] @ W[N, K]^T
+//   C[B*S, N] = gather_over_ranks(x_local)[B*S, K] @ op(W),  op(W) = W[N, K]^T (b_mn = 0) or W[K, N] (b_mn = 1)
 // x_local is this rank's [B * rows_per_chunk, K] slice (row stride x_ld). `gathered` / `pads` hold, for every rank of
 // the group, the address at which that rank's double-buffered gathered buffer / signal pad is mapped in this process.
 // `seq` is the call's sequence number (same on every rank, starting at 1, +1 per call on this context).
-MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int rows_per_chunk, const void* W,
+MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int rows_per_chunk, const void* W, int b_mn,
                            long long ldb, void* C, long long ldc, int N, int K, int rank, int world, unsigned seq,
                            const unsigned long long* gathered, const unsigned long long* pads, long long buf_elems,
                            int push_ctas, cudaStream_t stream) {
@@ -1093,7 +1093,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.bias = nullptr;
   args.ldc = ldc;
   args.M = static_cast<int>(M), args.N = N, args.K = K;
-  args.a_mn = 0, args.b_mn = 0;
+  args.a_mn = 0, args.b_mn = b_mn ? 1 : 0;
   args.out_fp32 = 0, args.accumulate = 0;
   args.tiles_m = (args.M + kBM - 1) / kBM;
   args.k_blocks = (K + kBK - 1) / kBK;
@@ -1104,7 +1104,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.debug_mode = g_debug_mode;
   args.stages = g_debug_stages;
   args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
-  args.b_lbo = 16u, args.b_sbo = 1024u, args.b_kstep = 32u;
+  args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;
   GatherArgs g;
   g.enabled = 1;
   g.push_ctas = (push_ctas > 0 && push_ctas * 32 <= kMaxPushThreads) ? push_ctas : kMaxPushThreads / 32;
@@ -1124,7 +1124,9 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   const int bn = wide ? 256 : (pair ? 128 : kind);
   CUtensorMap tmA, tmB;
   if (!encode_tmap_2d(&tmA, a_base, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM, 2, true)) return -5;
-  if (!encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true)) return -5;
+  if (!(b_mn ? encode_tmap_2d(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBK, 2, true)
+             : encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true)))
+    return -5;
   if (wide) return launch_gemm_pair<true>(tmA, tmB, args, stream, &g);
   if (pair) return launch_gemm_pair<false>(tmA, tmB, args, stream, &g);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream, &g);

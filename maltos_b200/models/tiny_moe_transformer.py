@@ -38,6 +38,19 @@ def route_tokens(router_logits: torch.Tensor, top_k: int, renormalize: bool = Tr
     return idx, gate
 
 
+def route_and_balance(router_logits: torch.Tensor, top_k: int, *, need_aux: bool):
+    """``(expert_idx [N,k], gate [N,k], load-balance loss or None)``. On CUDA one fused router kernel produces the
+    selection, the gates and the statistics of the loss; elsewhere the eager helpers above."""
+    from maltos_b200.ops.moe_router import _kernel_ok, load_balance_loss_from_stats, route
+
+    if _kernel_ok(router_logits, top_k):
+        idx, gate, mean_prob, counts = route(router_logits, top_k, True)
+        return idx, gate, (load_balance_loss_from_stats(mean_prob, counts) if need_aux else None)
+    idx, gate = route_tokens(router_logits, top_k)
+    aux = load_balance_loss(router_logits, idx if top_k > 1 else idx.squeeze(-1)) if need_aux else None
+    return idx, gate, aux
+
+
 def capacity_keep_mask(expert_idx: torch.Tensor, num_experts: int, capacity: int) -> torch.Tensor:
     """True for assignments that fit: per expert, the first ``capacity`` assignments in token order are kept."""
     flat = expert_idx.reshape(-1)
@@ -73,7 +86,7 @@ class TopKMoE(nn.Module):
         B, S, H = x.shape
         flat = x.reshape(-1, H)
         logits = self.router(flat)
-        idx, gate = route_tokens(logits, self.top_k)
+        idx, gate, aux = route_and_balance(logits, self.top_k, need_aux=return_aux_loss)
         keep = None
         if self.capacity_factor is not None:
             cap = max(1, int(self.capacity_factor * flat.shape[0] * self.top_k / self._num_experts + 0.999999))
@@ -81,7 +94,7 @@ class TopKMoE(nn.Module):
         out = moe_experts_forward(flat, idx, gate, keep, list(self.experts)).view(B, S, H)
         if not return_aux_loss:
             return out
-        return out, load_balance_loss(logits, idx if self.top_k > 1 else idx.squeeze(-1))
+        return out, aux
 
 
 Top1MoE = TopKMoE

@@ -89,6 +89,38 @@ def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
     return getattr(symm, "fused_scatter", True) and x2.dtype == torch.bfloat16 and x2.is_cuda and n_out % 8 == 0
 
 
+def all_gather_gemm(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool):
+    """``(gather_over_ranks(x2) @ op(w), gathered)`` in one launch (see module docstring).
+
+    ``x2 [B*rows, K]`` local rows; ``op(w) = w[N, K]^T`` (``b_mn=False``) or ``w[K, N]`` (``b_mn=True``). ``gathered`` is a view
+    ``[B*rows*T, K]`` of this rank's symmetric buffer holding the gathered operand; it stays valid until the second next
+    call of this function on the context (peers overwrite a slot only after they have seen this rank start the NEXT call,
+    which in stream order is after every kernel launched before it), so a weight-gradient GEMM issued right after may read it.
+    """
+    T = symm.world
+    K = x2.shape[1]
+    N = w.shape[1] if b_mn else w.shape[0]
+    if x2.stride(1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    if w.stride(1) != 1 or w.stride(0) % 8:
+        w = w.contiguous()
+    M = B * rows * T
+    buf_elems = M * K
+    buf = symm.ensure_buffer("sp_gather", 2 * buf_elems * 2)
+    buf_stride = buf.nbytes // 4      # elements per half: the two call parities never share memory, whatever the call sizes
+    seq = symm.next_seq("gather")
+    out = torch.empty((M, N), dtype=x2.dtype, device=x2.device)
+    gathered = (ctypes.c_ulonglong * 8)(*(buf.peer_ptrs + [0] * (8 - T)))
+    pads = (ctypes.c_ulonglong * 8)(*(symm.pad.peer_ptrs + [0] * (8 - T)))
+    rc = _lib.lib().mb_ag_gemm_bf16(
+        _lib.ptr(x2), _lib.c_ll(x2.stride(0)), _lib.c_int(B), _lib.c_int(rows), _lib.ptr(w), _lib.c_int(1 if b_mn else 0),
+        _lib.c_ll(w.stride(0)), _lib.ptr(out), _lib.c_ll(out.stride(0)), _lib.c_int(N), _lib.c_int(K), _lib.c_int(symm.rank), _lib.c_int(T),
+        ctypes.c_uint(seq & 0xFFFFFFFF), gathered, pads, _lib.c_ll(buf_stride), _lib.c_int(PUSH_CTAS), _lib.stream_ptr())
+    _lib.check(rc, "mb_ag_gemm_bf16")
+    full = buf.local_tensor(torch.bfloat16, 2 * buf_stride, x2.device)[(seq & 1) * buf_stride:(seq & 1) * buf_stride + buf_elems].view(M, K)
+    return out, full
+
+
 class _AllGatherGroupedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_local, symm, *weights):
@@ -101,18 +133,7 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         x2 = x_local.reshape(B * rows, K)
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
-        M = B * rows * T
-        buf_elems = M * K
-        buf = symm.ensure_buffer("sp_gather", 2 * buf_elems * 2)
-        seq = symm.next_seq("gather")
-        out = torch.empty((M, N), dtype=x_local.dtype, device=x_local.device)
-        gathered = (ctypes.c_ulonglong * 8)(*(buf.peer_ptrs + [0] * (8 - T)))
-        pads = (ctypes.c_ulonglong * 8)(*(symm.pad.peer_ptrs + [0] * (8 - T)))
-        rc = _lib.lib().mb_ag_gemm_bf16(
-            _lib.ptr(x2), _lib.c_ll(x2.stride(0)), _lib.c_int(B), _lib.c_int(rows), _lib.ptr(fused), _lib.c_ll(fused.stride(0)),
-            _lib.ptr(out), _lib.c_ll(out.stride(0)), _lib.c_int(N), _lib.c_int(K), _lib.c_int(symm.rank), _lib.c_int(T),
-            ctypes.c_uint(seq & 0xFFFFFFFF), gathered, pads, _lib.c_ll(buf_elems), _lib.c_int(PUSH_CTAS), _lib.stream_ptr())
-        _lib.check(rc, "mb_ag_gemm_bf16")
+        out, _ = all_gather_gemm(x2, fused, symm, B, rows, b_mn=False)
         ctx.save_for_backward(x2, *weights)
         ctx.symm, ctx.layout, ctx.fused_ok = symm, layout, order is not None
         ctx.dims = (B, rows, K, N)
@@ -182,8 +203,14 @@ class _LinearReduceScatter(torch.autograd.Function):
         x2, weight = ctx.saved_tensors
         B, S, rows, Kin = ctx.dims
         H = weight.shape[0]
-        dy_full = _nccl_all_gather_rows(dy.reshape(B * rows, H), ctx.symm, B, rows)   # [B*S, H]
-        dx = gemm(dy_full, weight, b_mn=True).view(B, S, Kin) if ctx.needs_input_grad[0] else None
+        dy2 = dy.reshape(B * rows, H)
+        if ctx.needs_input_grad[0] and dy2.dtype == torch.bfloat16 and dy2.is_cuda and Kin % 8 == 0:
+            # dX = gather(dY) @ W in one launch; the gathered dY stays in the symmetric buffer for the weight gradient
+            dx_full, dy_full = all_gather_gemm(dy2, weight, ctx.symm, B, rows, b_mn=True)
+            dx = dx_full.view(B, S, Kin)
+        else:
+            dy_full = _nccl_all_gather_rows(dy2, ctx.symm, B, rows)   # [B*S, H]
+            dx = gemm(dy_full, weight, b_mn=True).view(B, S, Kin) if ctx.needs_input_grad[0] else None
         dw = gemm(dy_full, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
         return dx, dw, None
 

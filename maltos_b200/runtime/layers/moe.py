@@ -86,13 +86,13 @@ class ExpertParallelMoE(nn.Module):
                    capacity_factor=getattr(moe, "capacity_factor", None))
 
     def forward(self, x: torch.Tensor, *, return_aux_loss: bool = False):
-        from maltos_b200.models.tiny_moe_transformer import capacity_keep_mask, load_balance_loss, route_tokens
+        from maltos_b200.models.tiny_moe_transformer import capacity_keep_mask, route_and_balance
 
         B, S, H = x.shape
         flat = x.reshape(-1, H)
         N = flat.shape[0]
         logits = self.router(flat)
-        idx, gate = route_tokens(logits, self.top_k)                      # [N,k]
+        idx, gate, aux = route_and_balance(logits, self.top_k, need_aux=return_aux_loss)   # [N,k]
         if self.capacity_factor is not None:
             cap = max(1, int(self.capacity_factor * N * self.top_k / self.num_experts + 0.999999))
             keep = capacity_keep_mask(idx, self.num_experts, cap)
@@ -134,4 +134,4 @@ class ExpertParallelMoE(nn.Module):
         out = out.view(B, S, H)
         if not return_aux_loss:
             return out
-        return out, load_balance_loss(logits, idx if self.top_k > 1 else idx.squeeze(-1))
+        return out, aux

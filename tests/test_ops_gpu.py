@@ -246,3 +246,24 @@ def test_packed_document_attention_matches_fp32_reference():
     _close(q.grad, qf.grad, 3e-2)
     _close(k.grad, kf.grad, 3e-2)
     _close(v.grad, vf.grad, 3e-2)
+
+
+@pytest.mark.parametrize("E,k,renorm,dtype", [(64, 1, True, torch.float32), (64, 2, True, torch.bfloat16), (8, 2, False, torch.float32),
+                                              (200, 4, True, torch.float32)])
+def test_moe_router_matches_reference(E, k, renorm, dtype):
+    from maltos_b200.ops.moe_router import load_balance_loss_from_stats, route, route_reference
+
+    torch.manual_seed(9)
+    N = 1000
+    logits = (torch.randn(N, E, device=DEV) * 2).to(dtype).requires_grad_()
+    idx, gate, mean_prob, counts = route(logits, k, renorm)
+    ref_logits = logits.detach().float().requires_grad_()
+    ridx, rgate, rmean, rcounts = route_reference(ref_logits, k, renorm)
+    assert torch.equal(idx, ridx) and torch.equal(counts, rcounts)
+    _close(gate, rgate, 1e-2 if dtype == torch.bfloat16 else 1e-5)
+    _close(mean_prob, rmean, 1e-4)
+    dg = torch.randn(N, k, device=DEV)
+    (gate.float() * dg).sum().add(3.0 * load_balance_loss_from_stats(mean_prob, counts)).backward()
+    (rgate.float() * dg).sum().add(3.0 * load_balance_loss_from_stats(rmean, rcounts)).backward()
+    _close(logits.grad, ref_logits.grad, 2e-2 if dtype == torch.bfloat16 else 1e-4)
+    _lib.fetch_status()
