@@ -45,6 +45,7 @@ def parse_args(argv=None):
     ap.add_argument("--small", action="store_true", help="tiny model/sequence: plumbing check only, NOT a benchmark number")
     ap.add_argument("--device", default=None, help="override device (cpu allowed only with --small)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
+    ap.add_argument("--kernel-table", default=None, help="debugging: write rank 0's per-kernel device-time table of one extra step to this file")
     ap.add_argument("--layers", type=int, default=None, help="debugging only: fewer layers (the JSON line is then marked invalid)")
     return ap.parse_args(argv)
 
@@ -265,6 +266,18 @@ def run_ours(args) -> None:
     for _ in range(args.warmup):
         one_step(dev_batches, read_loss=False)
     barrier_sync(device)
+
+    if args.kernel_table and use_cuda:
+        # debugging aid (outside the timed region): device time per kernel of ONE step on rank 0, NCCL kernels included
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            one_step(dev_batches, read_loss=False)
+            torch.cuda.synchronize(device)
+        if rank == 0:
+            Path(args.kernel_table).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.kernel_table).write_text(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=90))
+        barrier_sync(device)
 
     sampler = ClockSampler(device.index if use_cuda else 0)
     sampler.start()

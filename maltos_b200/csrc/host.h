@@ -24,6 +24,9 @@ bool encode_tmap_3d(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t 
                     uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
                     int elem_bytes, bool swizzle128);
 
+bool encode_tmap_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                    const uint32_t box[4], int elem_bytes, bool swizzle128);
+
 void set_last_error(const char* msg);
 
 }  // namespace mb

@@ -132,6 +132,32 @@ bool encode_tmap_3d(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t 
   return true;
 }
 
+// 4-D tiled map, used for [batch, token, head, dim] activations: dim0 = head_dim (innermost), dim1 = heads, dim2 = tokens,
+// dim3 = batch. A box of {64, 1, rows, 1} is one head's [rows x 64] tile; rows past the end of a batch read as zero.
+bool encode_tmap_4d(CUtensorMap* out, const void* base, const uint64_t dims_in[4], const uint64_t strides_bytes[3],
+                    const uint32_t box_in[4], int elem_bytes, bool swizzle128) {
+  bind_context();
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_last_error("cuTensorMapEncodeTiled entry point not available");
+    return false;
+  }
+  cuuint64_t dims[4] = {dims_in[0], dims_in[1], dims_in[2], dims_in[3]};
+  cuuint64_t strides[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t box[4] = {box_in[0], box_in[1], box_in[2], box_in[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, dtype_of(elem_bytes), 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[256];
+    std::snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled(4d) failed: %d", static_cast<int>(r));
+    set_last_error(buf);
+    return false;
+  }
+  return true;
+}
+
 }  // namespace mb
 
 // ------------------------------------------------------------------ exported C API

@@ -204,7 +204,8 @@ class _LinearReduceScatter(torch.autograd.Function):
         B, S, rows, Kin = ctx.dims
         H = weight.shape[0]
         dy2 = dy.reshape(B * rows, H)
-        if ctx.needs_input_grad[0] and dy2.dtype == torch.bfloat16 and dy2.is_cuda and Kin % 8 == 0:
+        if (ctx.needs_input_grad[0] and dy2.dtype == torch.bfloat16 and dy2.is_cuda and Kin % 8 == 0
+                and os.environ.get("MALTOS_B200_FUSED_DGRAD_GATHER", "0") == "1"):
             # dX = gather(dY) @ W in one launch; the gathered dY stays in the symmetric buffer for the weight gradient
             dx_full, dy_full = all_gather_gemm(dy2, weight, ctx.symm, B, rows, b_mn=True)
             dx = dx_full.view(B, S, Kin)

@@ -5,6 +5,7 @@
     python -m maltos_b200.tools.bench_kernels rmsnorm --rows 65536 --hidden 4096
     python -m maltos_b200.tools.bench_kernels swiglu --rows 65536 --hidden 14336
     python -m maltos_b200.tools.bench_kernels adamw --numel 500000000
+    python -m maltos_b200.tools.bench_kernels attention --seq 8192 --heads 32 --kv-heads 8
 
 Every line reports the achieved rate and, where ``--peaks MEASURED_PEAKS.json`` is given, the fraction of the measured
 copy bandwidth / cuBLAS throughput of the machine. Small ``--iters`` runs are what profiler captures are taken from.
@@ -133,6 +134,32 @@ def bench_adamw(args) -> None:
     _report_bw(f"adamw multi-tensor {per * chunks:,} params", per * chunks * (12 + 2 + 12 + 2), ms, _peaks(args.peaks))
 
 
+def bench_attention(args) -> None:
+    from maltos_b200.ops import _lib
+    from maltos_b200.ops.flash_attn import _sdpa_cudnn, flash_forward
+
+    B, S, Hq, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(B, S, Hq, D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda", generator=g).bfloat16()
+    flops = 4.0 * B * S * S * D * Hq / (2 if args.causal else 1)
+    rows = []
+    with torch.no_grad():
+        rows.append(("tcgen05 flash forward (this library)", _time(lambda: flash_forward(q, k, v, mode=1 if args.causal else 0), args.iters)))
+        if _sdpa_cudnn(q, k, v, args.causal, None) is not None:
+            rows.append(("cuDNN fused attention (library)", _time(lambda: _sdpa_cudnn(q, k, v, args.causal, None), args.iters)))
+        try:
+            from flash_attn import flash_attn_func
+
+            rows.append(("flash-attn 2 (library)", _time(lambda: flash_attn_func(q, k, v, causal=args.causal), args.iters)))
+        except ImportError:
+            pass
+    for name, ms in rows:
+        print(f"attention fwd B{B} S{S} h{Hq}/{Hkv} D{D} {'causal' if args.causal else 'full'} {name:>38}: {ms * 1e3:8.1f} us  {flops / ms / 1e9:7.1f} TFLOP/s")
+    _lib.fetch_status()
+
+
 def main(argv=None) -> None:
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     p.add_argument("--peaks", default="MEASURED_PEAKS.json", help="JSON with hbm_gbs / bf16_tflops of this machine")
@@ -148,12 +175,19 @@ def main(argv=None) -> None:
         s = sub.add_parser(name)
         s.add_argument("--rows", type=int, default=65536)
         s.add_argument("--hidden", type=int, default=4096)
+    t = sub.add_parser("attention")
+    t.add_argument("--batch", type=int, default=2)
+    t.add_argument("--seq", type=int, default=8192)
+    t.add_argument("--heads", type=int, default=32)
+    t.add_argument("--kv-heads", type=int, default=8)
+    t.add_argument("--head-dim", type=int, default=128)
+    t.add_argument("--causal", action=argparse.BooleanOptionalAction, default=True)
     a = sub.add_parser("adamw")
     a.add_argument("--numel", type=int, default=500_000_000)
     args = p.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")
-    {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw}[args.what](args)
+    {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "attention": bench_attention}[args.what](args)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,75 @@
+"""tcgen05 flash-attention forward against the fp32 restatement: mask modes, GQA, ragged lengths, log-sum-exp."""
+import pytest
+import torch
+
+from maltos_b200.ops import _lib
+from maltos_b200.ops.attention import attention_block_forward, attention_reference
+from maltos_b200.ops.flash_attn import flash_forward
+from maltos_b200.utils.constants import PAD_SEQUENCE_ID
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _qkv(B, Sq, Sk, Hq, Hkv, D, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    mk = lambda s, h: torch.randn(B, s, h, D, device=DEV, generator=g).bfloat16()   # noqa: E731
+    return mk(Sq, Hq), mk(Sk, Hkv), mk(Sk, Hkv)
+
+
+def _check(out, lse, ref, ref_lse, tol=2e-2):
+    finite = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), finite)
+    assert (lse[finite] - ref_lse[finite]).abs().max().item() < 2e-2
+    err = (out.float() - ref.float()).abs().max().item()
+    assert err <= tol * max(ref.float().abs().max().item(), 1e-3), err
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D", [(1, 128, 128, 2, 2, 128), (2, 384, 384, 4, 2, 128), (1, 300, 300, 4, 1, 64),
+                                              (1, 1024, 1024, 8, 2, 128), (2, 200, 456, 2, 2, 64)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_dense_modes(B, Sq, Sk, Hq, Hkv, D, causal):
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hkv, D)
+    out, lse = flash_forward(q, k, v, mode=1 if causal else 0)
+    _lib.fetch_status()
+    ref, ref_lse = attention_reference(q.float(), k.float(), v.float(), causal=causal, return_lse=True)
+    _check(out, lse, ref, ref_lse)
+
+
+def test_general_mask_zigzag_blocks_and_documents():
+    B, S, Hq, Hkv, D = 2, 256, 4, 2, 128
+    q, k, v = _qkv(B, S, S, Hq, Hkv, D, seed=3)
+    # query block = zigzag chunks (1, 6) of an 8-chunk sequence, key block = chunks (2, 5): partly visible
+    chunk = S // 2
+    q_pos = torch.cat([torch.arange(1 * chunk, 2 * chunk), torch.arange(6 * chunk, 7 * chunk)]).to(DEV).unsqueeze(0).expand(B, S).contiguous()
+    k_pos = torch.cat([torch.arange(2 * chunk, 3 * chunk), torch.arange(5 * chunk, 6 * chunk)]).to(DEV).unsqueeze(0).expand(B, S).contiguous()
+    out, lse = flash_forward(q, k, v, mode=2, q_positions=q_pos, k_positions=k_pos)
+    ref, ref_lse = attention_reference(q.float(), k.float(), v.float(), q_positions=q_pos, k_positions=k_pos, return_lse=True)
+    _check(out, lse, ref, ref_lse)
+    assert not torch.isfinite(lse[:, :, :chunk]).any() and float(out[:, :chunk].abs().max()) == 0.0   # first half sees nothing
+    # packed documents with padding
+    seq = torch.full((B, S), PAD_SEQUENCE_ID, dtype=torch.long, device=DEV)
+    seq[0, :100], seq[0, 100:250] = 0, 1
+    seq[1, :30], seq[1, 30:256] = 0, 1
+    order = torch.arange(S, device=DEV).unsqueeze(0).expand(B, S).contiguous()
+    out, lse = flash_forward(q, k, v, mode=2, q_positions=order, k_positions=order, q_sequence_ids=seq, k_sequence_ids=seq)
+    ref, ref_lse = attention_reference(q.float(), k.float(), v.float(), q_positions=order, k_positions=order, q_sequence_ids=seq,
+                                       k_sequence_ids=seq, return_lse=True)
+    _check(out, lse, ref, ref_lse)
+    _lib.fetch_status()
+
+
+def test_block_primitive_uses_the_kernel_and_strided_inputs(monkeypatch):
+    B, S, Hq, Hkv, D = 1, 512, 8, 2, 128
+    packed = torch.randn(B, S, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    q = packed[..., :Hq * D].view(B, S, Hq, D)
+    k = packed[..., Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
+    v = packed[..., (Hq + Hkv) * D:].view(B, S, Hkv, D)
+    pos = torch.arange(S, device=DEV).unsqueeze(0)
+    monkeypatch.setenv("MALTOS_B200_FLASH_BLOCKS", "1")
+    before = _lib.launch_count()
+    out, lse = attention_block_forward(q, k, v, q_positions=pos, k_positions=pos)
+    assert _lib.launch_count() == before + 1 and out.dtype == torch.bfloat16
+    ref, ref_lse = attention_reference(q.float(), k.float(), v.float(), causal=True, return_lse=True)
+    _check(out, lse, ref, ref_lse)
+    _lib.fetch_status()

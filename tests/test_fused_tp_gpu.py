@@ -16,7 +16,7 @@ def _worker(rank, world, port, queue):
     import traceback
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
-                      MALTOS_B200_FUSED_SCATTER="1")   # the fused GEMM -> reduce-scatter is opt-in
+                      MALTOS_B200_FUSED_SCATTER="1", MALTOS_B200_FUSED_DGRAD_GATHER="1")   # the fused GEMM -> reduce-scatter is opt-in
     try:
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
