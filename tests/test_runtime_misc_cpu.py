@@ -1,0 +1,94 @@
+"""SFT loader resume and DP interleave, ChainedWork re-firing, asynchronous metric reduction over two gloo ranks."""
+import json
+
+import numpy as np
+import torch
+
+from maltos_b200.data.sft import PackedSFTDataset, SFTDataLoader
+from maltos_b200.runtime.plugins.zero_common import ChainedWork
+from maltos_b200.utils.sft_messages import EncodedSFTExample
+from maltos_b200.utils.sft_packing import PackedSFTWriter, export_packing_metadata
+from tests.dist_utils import run_distributed
+
+
+def _sft_dataset(tmp_path, rows=11, seq_len=16):
+    w = PackedSFTWriter(output_dir=tmp_path, seq_len=seq_len, sequences_per_shard=4, max_sequences=None, pad_token_id=0,
+                        packing_algorithm="next_fit")
+    for r in range(rows):
+        w.add_example(EncodedSFTExample([1000 * (r + 1) + i for i in range(seq_len)], [0] * 4 + [1] * (seq_len - 4)))
+    summary = w.finish()
+    meta = {"format": "maltos_sft_packed", "format_version": 2,
+            "packing": export_packing_metadata(summary=summary, seq_len=seq_len, sequences_per_shard=4, packing_algorithm="next_fit", packing_buffer_size=1)}
+    (tmp_path / "meta.json").write_text(json.dumps(meta))
+    return PackedSFTDataset(tmp_path)
+
+
+def test_sft_loader_interleaves_ranks_wraps_and_resumes(tmp_path):
+    ds = _sft_dataset(tmp_path)
+    assert len(ds) == 11 and len(ds.shards) == 3
+    world, mb = 2, 2
+    loaders = [SFTDataLoader(ds, micro_batch_size=mb, dp_rank=r, dp_world_size=world) for r in range(world)]
+    seen = []
+    for step in range(5):                      # 20 rows drawn from 11: wraps around
+        for r, ld in enumerate(loaders):
+            b = ld.next_batch()
+            assert set(b) == {"input_ids", "labels", "position_ids", "sequence_ids"} and b["input_ids"].dtype == torch.int64
+            for i in range(mb):
+                k = (step * mb + i) * world + r
+                assert int(b["input_ids"][i, 0]) == 1000 * (k % 11 + 1)
+                seen.append(k)
+    assert sorted(seen) == list(range(20))
+    state = loaders[1].state_dict().__dict__
+    again = SFTDataLoader(ds, micro_batch_size=mb, dp_rank=1, dp_world_size=world)
+    again.load_state_dict(json.loads(json.dumps(state)))
+    for _ in range(3):
+        assert torch.equal(loaders[1].next_batch()["input_ids"], again.next_batch()["input_ids"])
+    assert again.consumed_sequences == loaders[1].consumed_sequences
+
+
+class _Handle:
+    def __init__(self, log, name):
+        self.log, self.name = log, name
+
+    def wait(self):
+        self.log.append(f"wait:{self.name}")
+
+    def block_current_stream(self):
+        self.log.append(f"block:{self.name}")
+
+
+def test_chained_work_replays_its_whole_chain_on_every_fire():
+    log = []
+    root = ChainedWork(None, lambda: (log.append("fire:a"), _Handle(log, "a"))[1])
+    mid = ChainedWork(root, lambda: (log.append("fire:b"), _Handle(log, "b"))[1], blocks_by_stream=False)
+    leaf = ChainedWork(mid, lambda: (log.append("fire:c"), _Handle(log, "c"))[1])
+    leaf.wait()                                 # not fired yet: fires the chain, then waits on the leaf
+    assert log == ["fire:a", "block:a", "fire:b", "wait:b", "fire:c", "wait:c"]
+    log.clear()
+    leaf.fire()                                 # persistent chain: a second round starts from the root again
+    leaf.wait()
+    assert log == ["fire:a", "block:a", "fire:b", "wait:b", "fire:c", "wait:c"]
+
+
+def _metric_worker(rank, world):
+    from maltos_b200.utils import metrics as M
+
+    agg = M.MetricAggregator()
+    agg.update({"loss": 1.0 + rank, "tokens": 10 * (rank + 1), "lr": 0.1 * (rank + 1), "fp16/overflow": rank == 1, "perf/step_sec": 2.0 + rank,
+                "memory/max_allocated_gb": 3.0 + rank, "step": 5})
+    pending = agg.flush_async(step_delta=1)
+    # the reduction is in flight: more values can be recorded for the next interval meanwhile
+    agg.update({"loss": 100.0})
+    out = pending.wait()
+    return out, agg.has_values()
+
+
+def test_metric_reduction_rules_across_ranks():
+    results = run_distributed(_metric_worker, 2)
+    for out, has_more in results:
+        assert has_more
+        assert out["loss"] == 1.5                      # mean over ranks
+        assert out["step"] == 5 and abs(out["lr"] - 0.1) < 1e-12      # rank 0's value
+        assert out["memory/max_allocated_gb"] == 4.0   # max over ranks
+        assert bool(out["fp16/overflow"]) is True      # any
+    assert results[0][0].keys() == results[1][0].keys()
