@@ -73,6 +73,7 @@ constexpr int kMaxPeers = 8;
 struct GatherArgs {
   int enabled;
   int push_ctas;          // push warps per block
+  int bulk;               // 1: push with bulk async copies through a shared-memory staging buffer (one thread per block)
   int rank, world;
   int batches;            // B
   int rows_per_chunk;     // S / T rows of one rank per batch
@@ -174,6 +175,79 @@ __device__ void gather_push_role(const GatherArgs& g, int K, int* status, int n_
       }
     }
     push_sync();
+  }
+}
+
+// Bulk variant of the push role: ONE thread per block moves 16 KB pieces global -> shared (bulk load, mbarrier) ->
+// destination (bulk store into local or peer memory). No registers or issue slots of the other warps are used and the
+// NVLink writes leave as large bursts. `stage` is 128-byte aligned: two mbarriers, then two 16 KB buffers.
+constexpr uint32_t kBulkPiece = 16384;
+constexpr uint32_t kPushSmemBytes = 128 + 2 * kBulkPiece;
+
+__device__ void gather_push_role_bulk(const GatherArgs& g, int K, int* status, int n_ctas, uint8_t* stage, volatile int* abort_flag) {
+  uint64_t* bar = reinterpret_cast<uint64_t*>(stage);
+  uint8_t* buf_smem = stage + 128;
+  mbar_init(&bar[0], 1);
+  mbar_init(&bar[1], 1);
+  fence_barrier_init();
+  fence_proxy_async_smem();
+  const int gbuf = static_cast<int>(g.seq & 1u);
+  const long long chunk_bytes = static_cast<long long>(g.rows_per_chunk) * K * 2;      // one batch's rows of this rank
+  const long long pieces_per_chunk = (chunk_bytes + kBulkPiece - 1) / kBulkPiece;
+  const long long n_pieces = pieces_per_chunk * g.batches;
+  const long long s_rows = static_cast<long long>(g.rows_per_chunk) * g.world;
+  unsigned* my_pad = reinterpret_cast<unsigned*>(g.pads[g.rank]);
+  const uint8_t* src_base = reinterpret_cast<const uint8_t*>(g.x_local);
+  uint32_t use[2] = {0u, 0u};     // completed uses of each staging buffer (mbarrier phase)
+  for (int step = 0; step < g.world; ++step) {
+    const int dst = (g.rank - step + g.world) % g.world;
+    if (!wait_flag_reached(my_pad + 16 + gbuf * 8 + dst, g.seq - 2u, abort_flag)) {
+      atomicOr(&status[0], MB_ERR_PEER_TIMEOUT);
+      status[2] = dst;
+      return;
+    }
+    uint8_t* out = reinterpret_cast<uint8_t*>(g.gathered[dst]) + static_cast<long long>(gbuf) * g.buf_elems * 2;
+    auto piece_bytes = [&](long long pc) -> uint32_t {
+      const long long within = (pc % pieces_per_chunk) * kBulkPiece;
+      const long long left = chunk_bytes - within;
+      return static_cast<uint32_t>(left < kBulkPiece ? left : kBulkPiece);
+    };
+    auto issue_load = [&](long long pc, int b) {
+      const long long batch = pc / pieces_per_chunk, within = (pc % pieces_per_chunk) * kBulkPiece;
+      const uint32_t bytes = piece_bytes(pc);
+      mbar_arrive_expect_tx(&bar[b], bytes);
+      bulk_load(buf_smem + b * kBulkPiece, src_base + batch * chunk_bytes + within, bytes, &bar[b]);
+    };
+    long long pc = blockIdx.x;
+    int b = 0;
+    if (pc < n_pieces) issue_load(pc, 0);
+    bool ok = true;
+    for (; pc < n_pieces; pc += n_ctas, b ^= 1) {
+      const long long next = pc + n_ctas;
+      if (next < n_pieces) {
+        tma_store_wait_read<0>();            // the other buffer's previous store has finished reading it
+        issue_load(next, b ^ 1);
+      }
+      if (!mbar_wait(&bar[b], use[b] & 1u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      ++use[b];
+      const long long batch = pc / pieces_per_chunk, within = (pc % pieces_per_chunk) * kBulkPiece;
+      uint8_t* drow = out + ((batch * s_rows + static_cast<long long>(g.rank) * g.rows_per_chunk) * K) * 2 + within;
+      bulk_store(drow, buf_smem + b * kBulkPiece, piece_bytes(pc));
+      tma_store_commit();
+    }
+    tma_store_wait_all<0>();                 // every store of this destination is complete
+    if (!ok) return;
+    fence_proxy_async_global();
+    __threadfence_system();
+    const unsigned done = atomicAdd(my_pad + 40 + dst, 1u);
+    if (done == static_cast<unsigned>(n_ctas - 1)) {
+      atomicExch(my_pad + 40 + dst, 0u);
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<unsigned*>(g.pads[dst]) + gbuf * 8 + g.rank, g.seq);
+    }
   }
 }
 
@@ -463,7 +537,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ all-gather push (fused launches only)
     // Every block carries push warps, so the copy is spread over all SMs and no block of the persistent GEMM is
     // delayed behind a copy-only block.
-    gather_push_role(g, p.K, p.status, n_ctas);
+    if (g.bulk) {
+      if (threadIdx.x == kGemmThreads)
+        gather_push_role_bulk(g, p.K, p.status, n_ctas, smem + STAGES * (A_BYTES + B_BYTES) + 256, abort_flag);
+    } else {
+      gather_push_role(g, p.K, p.status, n_ctas);
+    }
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may touch
@@ -752,7 +831,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     __syncwarp();
   } else if (warp >= FIRST_PUSH_THREAD / 32) {
-    gather_push_role(g, p.K, p.status, static_cast<int>(gridDim.x), FIRST_PUSH_THREAD);
+    if (g.bulk) {
+      if (threadIdx.x == FIRST_PUSH_THREAD)
+        gather_push_role_bulk(g, p.K, p.status, static_cast<int>(gridDim.x), smem + STAGES * (A_BYTES + B_BYTES) + 256, abort_flag);
+    } else {
+      gather_push_role(g, p.K, p.status, static_cast<int>(gridDim.x), FIRST_PUSH_THREAD);
+    }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     const int q = warp & 3;
@@ -838,13 +922,14 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
                             const GatherArgs* gather = nullptr) {
   constexpr int stages = WIDE ? kWideStages : kPairStages;
   constexpr int tile_n = WIDE ? 512 : 256;
-  constexpr size_t smem = 1024 + stages * ((128 + tile_n / 2) * kBK * 2) + 256;
+  constexpr size_t smem_base = 1024 + stages * ((128 + tile_n / 2) * kBK * 2) + 256;
+  constexpr size_t smem_max = smem_base + kPushSmemBytes;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
     MB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem)));
+                                       static_cast<int>(smem_max)));
     configured[dev & 63] = true;
   }
   args.tiles_m = (args.M + kPairTile - 1) / kPairTile;
@@ -856,11 +941,13 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   } else {
     g.enabled = 0;
     g.push_ctas = 0;
+    g.bulk = 0;
   }
   const int max_pairs = g_debug_max_pairs > 0 ? g_debug_max_pairs : sm_count() / 2;
   const int grid = 2 * (total < max_pairs ? total : max_pairs);
   const int base_threads = WIDE ? kWideThreads : kGemmThreads;
   const int threads = g.enabled ? base_threads + 32 * g.push_ctas : base_threads;
+  const size_t smem = (g.enabled && g.bulk) ? smem_max : smem_base;
   gemm_bf16_pair_kernel<WIDE><<<grid, threads, smem, stream>>>(tmA, tmB, args, g);
   count_launch();
   MB_CHECK_CUDA(cudaGetLastError());
@@ -892,13 +979,14 @@ static GemmKind choose_gemm_kind(int M, int N) {
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& args, cudaStream_t stream,
                        const GatherArgs* gather = nullptr) {
-  constexpr size_t smem = 1024 + STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 256;
+  constexpr size_t smem_base = 1024 + STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 256;
+  constexpr size_t smem_max = smem_base + kPushSmemBytes;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
     MB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem)));
+                                       static_cast<int>(smem_max)));
     configured[dev & 63] = true;
   }
   args.tiles_n = (args.N + BN - 1) / BN;
@@ -909,9 +997,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   } else {
     g.enabled = 0;
     g.push_ctas = 0;
+    g.bulk = 0;
   }
   const int grid = total < sm_count() ? total : sm_count();
   const int threads = g.enabled ? kGemmThreads + 32 * g.push_ctas : kGemmThreads;
+  const size_t smem = (g.enabled && g.bulk) ? smem_max : smem_base;
   gemm_bf16_kernel<BN, STAGES><<<grid, threads, smem, stream>>>(tmA, tmB, args, g);
   count_launch();
   MB_CHECK_CUDA(cudaGetLastError());
@@ -972,6 +1062,7 @@ static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
 static long long* g_trace = nullptr;
 static int g_pair_group_m = 8;
 static int g_debug_mode = 0;
+static int g_push_bulk = 0;      // fused all-gather: 1 = push with bulk async copies, 0 = push with the copy warps
 static int g_scatter_kind = 0;   // tuning: kernel kind forced for the fused reduce-scatter GEMM (0 = cost model)
 static int g_debug_stages = 0;
 
@@ -989,6 +1080,7 @@ MB_API void mb_gemm_set_tuning(int group_m) {
 MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
+MB_API void mb_gemm_set_push_bulk(int on) { mb::g_push_bulk = on ? 1 : 0; }
 // Debug: cap the number of CTA pairs of the pair kernel (0 = one pair per two SMs).
 MB_API void mb_gemm_set_debug_max_pairs(int pairs) { mb::g_debug_max_pairs = pairs; }
 
@@ -1108,6 +1200,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   GatherArgs g;
   g.enabled = 1;
   g.push_ctas = (push_ctas > 0 && push_ctas * 32 <= kMaxPushThreads) ? push_ctas : kMaxPushThreads / 32;
+  g.bulk = (g_push_bulk && x_ld == K) ? 1 : 0;   // bulk copies need dense rows
   g.rank = rank, g.world = world;
   g.batches = batches, g.rows_per_chunk = rows_per_chunk;
   g.x_local = static_cast<const __nv_bfloat16*>(x_local);

@@ -125,6 +125,19 @@ __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Untiled bulk copies (16-byte aligned addresses, size a multiple of 16): global -> shared with mbarrier completion, and
+// shared -> global (local or peer memory) tracked by bulk groups.
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+               "l"(reinterpret_cast<uint64_t>(src_gmem)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(reinterpret_cast<uint64_t>(dst_gmem)),
+               "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 // Allocation is warp-wide; `ncols` a power of two in [32, 512]; the base address lands in smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {

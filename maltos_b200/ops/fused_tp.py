@@ -76,6 +76,15 @@ def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: i
     return out
 
 
+def set_push_mode(bulk: bool) -> None:
+    """How the fused all-gather moves rows to the peers: ``bulk=True`` one thread per block issues 16 KB bulk async copies
+    through a shared-memory staging buffer; ``False`` four copy warps per block use 16-byte loads / stores."""
+    _lib.lib().mb_gemm_set_push_bulk(ctypes.c_int(1 if bulk else 0))
+
+
+if os.environ.get("MALTOS_B200_PUSH_BULK", "0") == "1":
+    set_push_mode(True)
+
 _SCATTER_KIND = int(os.environ.get("MALTOS_B200_SCATTER_KIND", "0"))
 if _SCATTER_KIND:
     _lib.lib().mb_gemm_set_scatter_kind(ctypes.c_int(_SCATTER_KIND))

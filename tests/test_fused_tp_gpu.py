@@ -35,7 +35,10 @@ def _worker(rank, world, port, queue):
             ws = [torch.nn.Parameter((torch.randn(n, K, device="cuda") * 0.05).bfloat16()) for n in outs]
             fuse_parameters(ws)
             g = torch.Generator(device="cuda").manual_seed(100 + rank)
-            for rep in range(3):          # several calls: both buffer parities and the consumed handshake
+            for rep in range(4):          # several calls: both buffer parities, the consumed handshake, both push modes
+                from maltos_b200.ops.fused_tp import set_push_mode
+
+                set_push_mode(rep >= 2)
                 x = torch.randn(B, rows, K, device="cuda", generator=g).bfloat16().requires_grad_()
                 y, offs = all_gather_grouped_linear(x, ws, ctx)
                 full = torch.empty(world, B, rows, K, device="cuda", dtype=torch.bfloat16)
@@ -53,6 +56,7 @@ def _worker(rank, world, port, queue):
                 results.append((B, rows, K, rep, err, gerr))
                 for w in ws:
                     w.grad = None
+        set_push_mode(False)
         # row-parallel GEMM fused with the reduce-scatter (forward) and its backward
         from maltos_b200.ops.fused_tp import linear_reduce_scatter
 
