@@ -87,7 +87,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     mbar_init(p_full, 4);
     mbar_init(o_full, 1);
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = p.status[3];
     fence_barrier_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);

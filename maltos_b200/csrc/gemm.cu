@@ -98,11 +98,12 @@ __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence
 // Wait until *flag has reached `want` (sequence numbers, wrap-safe). Bounded: false after the deadline.
 __device__ __forceinline__ bool wait_flag_reached(const unsigned* flag, unsigned want, volatile int* abort_flag) {
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = wait_limit_ns(abort_flag);
 #pragma unroll 1
   while (true) {
     if (static_cast<int>(ld_acquire_sys(flag) - want) >= 0) return true;
     if (abort_flag && *abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
+    if (globaltimer_ns() - t0 > limit) return false;
     __nanosleep(200);
   }
 }
@@ -406,6 +407,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], kEpiWarps);
     }
+    abort_flag[1] = p.status[3];   // wait limit in ms (0 = default)
     *abort_flag = (p.sc.enabled && !scatter_wait_owners(p.sc, p.status)) ? 1 : 0;
     fence_barrier_init();
     prefetch_tmap(&tmA);
@@ -668,6 +670,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 2 * EPI_WARPS);
     }
+    abort_flag[1] = p.status[3];   // wait limit in ms (0 = default)
     *abort_flag = (p.sc.enabled && !scatter_wait_owners(p.sc, p.status)) ? 1 : 0;
     fence_barrier_init();
     prefetch_tmap(&tmA);

@@ -20,6 +20,13 @@ enum : int {
 
 constexpr uint64_t kWaitTimeoutNs = 4000000000ull;  // 4 s: far above any legitimate wait
 
+// The abort flag of a CTA is two ints in shared memory: [0] = abort raised, [1] = wait limit in milliseconds taken from
+// word 3 of the device status block at kernel start (0 = the default above). Tests shorten it to make a wait run out.
+__device__ __forceinline__ uint64_t wait_limit_ns(volatile int* abort_flag) {
+  const int ms = abort_flag ? abort_flag[1] : 0;
+  return ms > 0 ? static_cast<uint64_t>(ms) * 1000000ull : kWaitTimeoutNs;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -75,11 +82,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
   }
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = wait_limit_ns(abort_flag);
 #pragma unroll 1
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+    if (globaltimer_ns() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }

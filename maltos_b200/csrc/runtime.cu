@@ -171,8 +171,17 @@ MB_API int mb_status_fetch_and_clear(int* out4, cudaStream_t stream) {
   int* p = mb::status_ptr();
   if (!p) return -1;
   MB_CHECK_CUDA(cudaMemcpyAsync(out4, p, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream));
-  MB_CHECK_CUDA(cudaMemsetAsync(p, 0, 4 * sizeof(int), stream));
+  MB_CHECK_CUDA(cudaMemsetAsync(p, 0, 3 * sizeof(int), stream));   // word 3 holds the wait limit and is kept
   MB_CHECK_CUDA(cudaStreamSynchronize(stream));
+  return 0;
+}
+
+// Limit of every bounded device-side wait in milliseconds on the current device (0 restores the default of 4 s).
+MB_API int mb_set_wait_timeout_ms(int ms) {
+  int* p = mb::status_ptr();
+  if (!p) return -1;
+  if (ms < 0) ms = 0;
+  MB_CHECK_CUDA(cudaMemcpy(p + 3, &ms, sizeof(int), cudaMemcpyHostToDevice));
   return 0;
 }
 

@@ -32,6 +32,15 @@ class DeviceStatusError(RuntimeError):
     """Raised when a kernel left an error code in the per-device status word (bounded wait ran out...)."""
 
 
+class CommTimeoutError(DeviceStatusError):
+    """A bounded wait on a flag that another rank writes ran out: the peer never delivered. ``peer`` is the rank (within
+    the op's process group) whose flag was missing; the kernel returned cleanly and the context stays usable."""
+
+    def __init__(self, message: str, *, peer: int, block: int) -> None:
+        super().__init__(message)
+        self.peer, self.block = peer, block
+
+
 def library_path() -> Path:
     return _LIB_PATH
 
@@ -92,6 +101,11 @@ def check(rc: int, what: str) -> None:
         raise KernelLibraryError(f"{what} failed (code {rc}): {msg}")
 
 
+def set_wait_timeout_ms(ms: int) -> None:
+    """Limit of every bounded device-side wait on the current device (0 restores the default of 4 s)."""
+    check(lib().mb_set_wait_timeout_ms(c_int(int(ms))), "mb_set_wait_timeout_ms")
+
+
 def launch_count() -> int:
     """Number of kernels launched by this library in this process so far (0 if it was never loaded)."""
     if _lib is None:
@@ -116,5 +130,8 @@ def fetch_status(raise_on_error: bool = True) -> tuple[int, int, int, int]:
             names.append("peer flag wait timed out")
         if vals[0] & 4:
             names.append("index out of bounds")
-        raise DeviceStatusError(f"kernel status {vals[0]} ({', '.join(names)}); block {vals[1]}, detail {vals[2]}")
+        msg = f"kernel status {vals[0]} ({', '.join(names)}); block {vals[1]}, detail {vals[2]}"
+        if vals[0] & 2:
+            raise CommTimeoutError(msg, peer=vals[2], block=vals[1])
+        raise DeviceStatusError(msg)
     return vals  # type: ignore[return-value]

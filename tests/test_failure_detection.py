@@ -1,0 +1,149 @@
+"""Failure detection without faulting a GPU.
+
+* Host side (CPU / gloo): a rank that leaves before a collective makes the survivor's collective fail within the process
+  group's timeout; a data loader that raises mid-run propagates out of the trainer after the runtime was closed; a
+  truncated checkpoint artifact and a full disk guard are refused with clear errors.
+* Device side: a kernel waits (with a short limit) on a flag that nothing ever sets; it must return by itself, report
+  "peer flag wait timed out" through the status word, and leave the context usable for the next launch.
+"""
+import datetime
+import json
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.dist_utils import free_port
+
+
+# ------------------------------------------------------------------------------------------------ host side
+def _leaver_worker(rank, world, port, queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    t = torch.ones(4)
+    dist.all_reduce(t)                       # one healthy step
+    if rank == 1:
+        queue.put((rank, "left"))
+        queue.close()
+        queue.join_thread()
+        os._exit(0)                          # the rank disappears between steps, nothing of its own in flight
+    try:
+        dist.all_reduce(t)
+        queue.put((rank, "no error"))
+    except Exception as exc:  # noqa: BLE001 - any backend error type is fine, it must be an error and not a hang
+        queue.put((rank, f"error:{type(exc).__name__}"))
+    queue.close()
+    queue.join_thread()
+    os._exit(0)
+
+
+def test_survivor_sees_an_error_not_a_hang_when_a_rank_leaves():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=60) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    assert got[1] == "left" and got[0].startswith("error:"), got
+
+
+class _ExplodingLoader:
+    consumed_tokens = 0
+
+    def __init__(self, good: int) -> None:
+        self.good = good
+
+    def next_batch(self, cp_rank=None):
+        if self.good == 0:
+            raise OSError("shard vanished")
+        self.good -= 1
+        g = torch.Generator().manual_seed(self.good)
+        ids = torch.randint(0, 64, (2, 16), generator=g)
+        return {"input_ids": ids, "labels": ids.roll(-1, 1)}
+
+    def state_dict(self):
+        return {}
+
+    def load_state_dict(self, state):
+        pass
+
+
+def test_loader_failure_propagates_and_checkpoint_guards(tmp_path):
+    import maltos_b200  # noqa: F401
+    from maltos_b200 import models
+    from maltos_b200.runtime import RuntimeCore
+    from maltos_b200.state.checkpoint import load_sharded_checkpoint, save_sharded_checkpoint
+    from maltos_b200.train import Trainer, TrainerConfig
+
+    torch.manual_seed(0)
+    rt = RuntimeCore(model=models.TinyTransformer(32, 2, 2, 64, 1e-5, 1, 64, 16), optimizer_factory=lambda ps: torch.optim.AdamW(ps, lr=1e-3))
+    trainer = Trainer(runtime=rt, dataloader=_ExplodingLoader(good=3), config=TrainerConfig(max_steps=10, log_every=100))
+    trainer.setup()
+    with pytest.raises(OSError, match="shard vanished"):
+        trainer.fit()
+    # a healthy runtime to exercise the checkpoint guards
+    rt2 = RuntimeCore(model=models.TinyTransformer(32, 2, 2, 64, 1e-5, 1, 64, 16), optimizer_factory=lambda ps: torch.optim.AdamW(ps, lr=1e-3))
+    rt2.setup()
+    ckpt = tmp_path / "step_00000001"
+    save_sharded_checkpoint(rt2.state_manager, ckpt)
+    with pytest.raises((ValueError, FileExistsError)):
+        save_sharded_checkpoint(rt2.state_manager, ckpt)                      # never overwrite
+    with pytest.raises(RuntimeError, match="insufficient free space"):
+        save_sharded_checkpoint(rt2.state_manager, tmp_path / "step_00000002", min_free_gb=1e9)   # disk-space guard
+    manifest = json.loads((ckpt / "manifest.json").read_text())
+    model_file = next(a["path"] for a in manifest["artifacts"] if a["kind"] == "model")
+    data = (ckpt / model_file).read_bytes()
+    (ckpt / model_file).write_bytes(data[: len(data) // 3])                   # truncated artifact
+    with pytest.raises(Exception):
+        load_sharded_checkpoint(rt2.state_manager, ckpt)
+    rt2.close()
+
+
+# ------------------------------------------------------------------------------------------------ device side
+@pytest.mark.gpu
+def test_wait_on_a_flag_nobody_sets_times_out_cleanly():
+    import ctypes
+
+    from maltos_b200.ops import _lib
+    from maltos_b200.ops.gemm import gemm
+
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    B, rows, K, N, world = 1, 256, 256, 256, 2
+    x = torch.randn(B * rows, K, device=dev).bfloat16()
+    w = torch.randn(N, K, device=dev).bfloat16()
+    out = torch.empty(B * rows * world, N, device=dev, dtype=torch.bfloat16)
+    buf_elems = B * rows * world * K
+    # a two-rank group of which only rank 0 exists: rank 1's buffers are plain local memory that nothing ever fills,
+    # so its "rows have arrived" flag in rank 0's signal pad is never written
+    bufs = [torch.zeros(2 * buf_elems, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    pads = [torch.zeros(1024, device=dev, dtype=torch.int32) for _ in range(world)]
+    gathered = (ctypes.c_ulonglong * 8)(*([b.data_ptr() for b in bufs] + [0] * 6))
+    pad_ptrs = (ctypes.c_ulonglong * 8)(*([p.data_ptr() for p in pads] + [0] * 6))
+    _lib.fetch_status(raise_on_error=False)
+    _lib.set_wait_timeout_ms(300)
+    try:
+        rc = L.mb_ag_gemm_bf16(_lib.ptr(x), _lib.c_ll(K), _lib.c_int(B), _lib.c_int(rows), _lib.ptr(w), _lib.c_int(0), _lib.c_ll(K), _lib.ptr(out),
+                               _lib.c_ll(N), _lib.c_int(N), _lib.c_int(K), _lib.c_int(0), _lib.c_int(world), ctypes.c_uint(1), gathered, pad_ptrs,
+                               _lib.c_ll(buf_elems), _lib.c_int(4), _lib.stream_ptr())
+        assert rc == 0
+        with pytest.raises(_lib.CommTimeoutError) as err:
+            _lib.fetch_status()
+        assert err.value.peer == 1
+    finally:
+        _lib.set_wait_timeout_ms(0)
+    # the kernel returned by itself, the status word is clear again and the context still works
+    assert _lib.fetch_status(raise_on_error=False)[0] == 0
+    a = torch.randn(256, 128, device=dev).bfloat16()
+    c = gemm(a, w[:, :128].contiguous())
+    ref = a.float() @ w[:, :128].float().t()
+    assert ((c.float() - ref).abs().max() / ref.abs().max()).item() < 1e-2
+    _lib.fetch_status()
+    # the rows that WERE local have been multiplied correctly
+    ref0 = x.float() @ w.float().t()
+    assert ((out[:rows].float() - ref0).abs().max() / ref0.abs().max()).item() < 1e-2
