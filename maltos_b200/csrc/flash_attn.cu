@@ -283,7 +283,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = mbar_wait(o_full, (n_blocks - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok && row_valid) {
+    if (ok) {
+      // TMEM loads are warp-collective: every lane takes part, only rows inside the sequence are stored
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* dst = p.out + (static_cast<long long>(batch) * p.Sq + qi) * p.out_tstride + static_cast<long long>(head) * D;
       if (n_blocks > 0) {
@@ -294,23 +295,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_o + c0, r);
           tmem_ld_wait();
+          if (row_valid) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            v.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            v.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            v.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+            }
           }
         }
-      } else {
+      } else if (row_valid) {
         for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
       }
-      p.lse[(static_cast<long long>(batch) * p.Hq + head) * p.Sq + qi] =
-          l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-    } else if (ok && n_blocks > 0) {
-      tc_fence_after();   // rows past the end of the sequence: nothing to write
+      if (row_valid)
+        p.lse[(static_cast<long long>(batch) * p.Hq + head) * p.Sq + qi] =
+            l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
