@@ -5,8 +5,8 @@
 //   mode 0  every key is visible (blocks below the diagonal of ring attention);
 //   mode 1  causal with offset: key j visible to query i  <=>  j <= i + (Sk - Sq);
 //   mode 2  general: k_pos[j] <= q_pos[i] and k_seq[j] == q_seq[i] and k_seq[j] != -1 (packed documents, zigzag blocks).
-// One CTA handles 128 query rows of one (batch, head): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = softmax,
-// rescale and output. The reference gets this op from the flash-attn 2 package (utils/attention_backend.py:42-135).
+// One CTA handles 128 query rows of one (batch, head): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = softmax,
+// rescale and output (two threads per query row, each owning half of the key columns). The reference gets this op from the flash-attn 2 package (utils/attention_backend.py:42-135).
 #include "host.h"
 #include "ptx.cuh"
 
@@ -14,7 +14,8 @@ namespace mb {
 
 constexpr int kFaBM = 128;          // query rows per CTA
 constexpr int kFaBN = 128;          // keys per block
-constexpr int kFaThreads = 32 * 6;
+constexpr int kFaSoftmaxWarps = 8;   // two warps per TMEM lane quarter: each thread owns one query row and half of the key columns
+constexpr int kFaThreads = 32 * (2 + kFaSoftmaxWarps);
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct FlashArgs {
@@ -32,6 +33,12 @@ struct FlashArgs {
 };
 
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled [rows x 64 bf16] atom
+__device__ __forceinline__ float fast_exp2(float x) {   // x <= 0 here; one MUFU instruction
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) {
   return static_cast<uint32_t>((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
@@ -62,6 +69,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* o_full = bars + 10;       // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_xchg = reinterpret_cast<float*>(sP + P_BYTES + 256);   // exchange area: [2 parities][2 halves][128 rows] floats, then [2 halves][128 rows] int tags
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long (late) tiles first under a causal mask
@@ -83,9 +91,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&s_empty[i], kFaSoftmaxWarps);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, kFaSoftmaxWarps);
     mbar_init(o_full, 1);
     abort_flag[0] = 0;
     abort_flag[1] = p.status[3];
@@ -94,6 +102,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
   }
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) reinterpret_cast<int*>(s_xchg + 768)[i] = 0;   // exchange tags
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
@@ -167,29 +176,56 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ softmax, rescale, output (thread = query row)
+    // ------------------------------------------------------------------ softmax, rescale, output
+    // Thread = (query row, half of the key columns): warps 2..5 take key columns 0..63 of every block, warps 6..9 columns
+    // 64..127; the two threads of a row exchange their partial row maxima through shared memory. Two warps per
+    // scheduler hide each other's instruction latencies, which a single warp per scheduler could not.
     const int qw = warp & 3;                       // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;              // 0: key columns [0, 64), 1: [64, 128)
     const int row = qw * 32 + lane;                // row inside the tile
     const int qi = q0 + row;                       // query index in the sequence
     const bool row_valid = qi < p.Sq;
     const uint32_t t_lane = static_cast<uint32_t>(qw * 32) << 16;
     const int my_pos = (p.mode == 2 && row_valid) ? p.q_pos[static_cast<long long>(batch) * p.Sq + qi] : 0;
     const int my_seq = (p.mode == 2 && row_valid && p.q_seq) ? p.q_seq[static_cast<long long>(batch) * p.Sq + qi] : 0;
-    float m_run = -INFINITY, l_run = 0.f;
+    // Pairwise exchange between the two threads of a row through shared memory: value, then a monotonically increasing
+    // tag; the reader polls the partner's tag with the usual bound (no block-wide barrier, so an aborting warp cannot
+    // strand the others).
+    volatile int* x_tag = reinterpret_cast<volatile int*>(s_xchg + 768);     // [2 halves][128 rows]
+    auto exchange = [&](float mine, int tag, float& theirs) -> bool {
+      volatile float* val = s_xchg + (tag & 1) * 256;
+      val[half * 128 + row] = mine;
+      __threadfence_block();
+      x_tag[half * 128 + row] = tag;
+      const int partner = (half ^ 1) * 128 + row;
+      const uint64_t t0 = globaltimer_ns();
+      const uint64_t limit = wait_limit_ns(abort_flag);
+      while (x_tag[partner] < tag) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > limit) {
+          *abort_flag = 1;
+          return false;
+        }
+      }
+      theirs = val[partner];
+      return true;
+    };
+    float m_run = -INFINITY, l_run = 0.f;          // l_run: this thread's half of the row sum
     bool ok = true;
+    constexpr int HALF_N = kFaBN / 2;
+    constexpr int HALF_D = D / 2;
     for (int j = 0; j < n_blocks; ++j) {
       const int s = j & 1;
       ok = mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t_s = tmem_base + S_COL0 + static_cast<uint32_t>(s * kFaBN) + t_lane;
-      const int key0 = j * kFaBN;
-      // does this block need per-element masking for this tile?
-      bool need_mask = key0 + kFaBN > p.Sk;
-      if (p.mode == 1) need_mask = need_mask || (key0 + kFaBN - 1 > q0 + causal_off);
+      const uint32_t t_s = tmem_base + S_COL0 + static_cast<uint32_t>(s * kFaBN + half * HALF_N) + t_lane;
+      const int key0 = j * kFaBN + half * HALF_N;  // first key of this thread's columns
+      bool need_mask = j * kFaBN + kFaBN > p.Sk;
+      if (p.mode == 1) need_mask = need_mask || (j * kFaBN + kFaBN - 1 > q0 + causal_off);
       if (p.mode == 2) need_mask = true;
-      auto visible = [&](int c) -> bool {          // c = key column inside the block
+      auto visible = [&](int c) -> bool {          // c = column inside this thread's half
         const int kj = key0 + c;
         if (kj >= p.Sk) return false;
         if (p.mode == 1) return kj <= qi + causal_off;
@@ -203,36 +239,39 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         return true;
       };
-      // pass 1: row maximum of the scaled scores
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kFaBN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_s + c0, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      // scores of this thread's 64 columns stay in registers for both passes
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(t_s, r0);
+      tmem_ld_32x32b_x32(t_s + 32, r1);
+      tmem_ld_wait();
+      float m_part = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (visible(c0 + i)) m_blk = fmaxf(m_blk, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; ++i) {
+          if (!visible(i)) r0[i] = __float_as_uint(-INFINITY);
+          if (!visible(32 + i)) r1[i] = __float_as_uint(-INFINITY);
         }
       }
-      m_blk *= p.scale_log2;                       // scale > 0: max commutes with the scaling
+#pragma unroll
+      for (int i = 0; i < 32; ++i) m_part = fmaxf(m_part, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+      float m_other = -INFINITY;
+      ok = exchange(m_part, j + 1, m_other);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float m_blk = fmaxf(m_part, m_other) * p.scale_log2;   // scale > 0: max commutes with it
       const float m_new = fmaxf(m_run, m_blk);
       const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.f : 0.f) : exp2f(m_run - m_new);
+      const float alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.f : 0.f) : fast_exp2(m_run - m_new);
       // the previous P V product must be complete before O is rescaled or the P tile is overwritten
       if (j > 0) {
         ok = mbar_wait(o_full, (j - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          const uint32_t t_o = tmem_base + O_COL + t_lane;
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {   // this thread rescales its half of the head dimension
+          const uint32_t t_o = tmem_base + O_COL + static_cast<uint32_t>(half * HALF_D) + t_lane;
 #pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 16) {
+          for (int c0 = 0; c0 < HALF_D; c0 += 16) {
             uint32_t r[16];
             tmem_ld_32x32b_x16(t_o + c0, r);
             tmem_ld_wait();
@@ -243,30 +282,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
-      // pass 2: probabilities, row sum, P tile (bf16, 128-byte swizzled, K-major over the keys)
+      // probabilities, partial row sum, this thread's atom of the P tile (bf16, 128-byte swizzled, K-major over keys)
       float l_blk = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kFaBN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_s + c0, r);
-        tmem_ld_wait();
-        float pr[32];
+      uint8_t* atom = sP + half * (kFaBM * 128);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool vis = !need_mask || visible(c0 + i);
-          pr[i] = vis ? exp2f(__uint_as_float(r[i]) * p.scale_log2 - m_safe) : 0.f;
+      for (int ch = 0; ch < 8; ++ch) {             // 8 chunks of 8 keys
+        float pr[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float sc = __uint_as_float(ch < 4 ? r0[ch * 8 + i] : r1[(ch - 4) * 8 + i]);
+          pr[i] = fast_exp2(sc * p.scale_log2 - m_safe);    // masked scores are -inf -> 0
           l_blk += pr[i];
         }
-        uint8_t* atom = sP + (c0 >> 6) * (kFaBM * 128);
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {           // 4 chunks of 8 keys = 32 keys
-          uint4 v;
-          v.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]);
-          v.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-          v.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]);
-          v.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(atom + sw128_offset(row, ((c0 & 63) >> 3) + ch)) = v;
-        }
+        uint4 v;
+        v.x = pack_bf16x2(pr[0], pr[1]);
+        v.y = pack_bf16x2(pr[2], pr[3]);
+        v.z = pack_bf16x2(pr[4], pr[5]);
+        v.w = pack_bf16x2(pr[6], pr[7]);
+        *reinterpret_cast<uint4*>(atom + sw128_offset(row, ch)) = v;
       }
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
@@ -283,15 +316,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = mbar_wait(o_full, (n_blocks - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
+    // the two halves of a row add up their partial sums (all softmax warps reach this point, also after an abort)
+    float l_other = 0.f;
+    if (ok) {
+      ok = exchange(l_run, n_blocks + 1, l_other);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    const float l_tot = l_run + l_other;
     if (ok) {
       // TMEM loads are warp-collective: every lane takes part, only rows inside the sequence are stored
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (static_cast<long long>(batch) * p.Sq + qi) * p.out_tstride + static_cast<long long>(head) * D;
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* dst = p.out + (static_cast<long long>(batch) * p.Sq + qi) * p.out_tstride + static_cast<long long>(head) * D + half * HALF_D;
       if (n_blocks > 0) {
         tc_fence_after();
-        const uint32_t t_o = tmem_base + O_COL + t_lane;
+        const uint32_t t_o = tmem_base + O_COL + static_cast<uint32_t>(half * HALF_D) + t_lane;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < HALF_D; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_o + c0, r);
           tmem_ld_wait();
@@ -308,11 +348,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       } else if (row_valid) {
-        for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+        for (int c = 0; c < HALF_D; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
       }
-      if (row_valid)
+      if (row_valid && half == 0)
         p.lse[(static_cast<long long>(batch) * p.Hq + head) * p.Sq + qi] =
-            l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+            l_tot > 0.f ? (m_run + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -335,7 +375,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 template <int D>
 static int launch_flash_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FlashArgs& args,
                             cudaStream_t stream) {
-  constexpr size_t smem = 1024 + 5 * (kFaBM * D * 2) + kFaBM * kFaBN * 2 + 256;
+  constexpr size_t smem = 1024 + 5 * (kFaBM * D * 2) + kFaBM * kFaBN * 2 + 256 + 4 * 1024;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -100,7 +100,7 @@ def flash_forward(q, k, v, *, mode: int, q_positions=None, k_positions=None, q_s
 def flash_block_forward(q, k, v, q_positions, k_positions, q_sequence_ids, k_sequence_ids, scale):
     """Kernel block forward returning ``(out, lse)`` for the general visibility rule; None when the kernel does not cover
     the case (then the caller uses the fp32 block primitive)."""
-    if os.environ.get("MALTOS_B200_FLASH_BLOCKS", "0") != "1":
+    if os.environ.get("MALTOS_B200_FLASH_BLOCKS", "1") == "0":
         return None
     if q.dtype != torch.bfloat16 or q.shape[-1] not in (64, 128) or q.shape[2] % k.shape[2]:
         return None

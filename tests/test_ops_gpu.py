@@ -255,7 +255,11 @@ def test_moe_router_matches_reference(E, k, renorm, dtype):
 
     torch.manual_seed(9)
     N = 1000
-    logits = (torch.randn(N, E, device=DEV) * 2).to(dtype).requires_grad_()
+    if dtype == torch.bfloat16:
+        # bf16 logits tie easily and tie order is unspecified: use distinct, exactly representable values per row
+        logits = (torch.argsort(torch.rand(N, E, device=DEV), dim=1).float() * 0.125 - 2.0).to(dtype).requires_grad_()
+    else:
+        logits = (torch.randn(N, E, device=DEV) * 2).to(dtype).requires_grad_()
     idx, gate, mean_prob, counts = route(logits, k, renorm)
     ref_logits = logits.detach().float().requires_grad_()
     ridx, rgate, rmean, rcounts = route_reference(ref_logits, k, renorm)
