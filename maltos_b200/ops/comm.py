@@ -28,7 +28,7 @@ def context_for(group):
         return None
     key = id(group)
     if key in _contexts:
-        return _contexts[key]
+        return _contexts[key][1]
     if key in _disabled_reason:
         return None
     try:
@@ -38,8 +38,16 @@ def context_for(group):
     except Exception as exc:  # noqa: BLE001 - any failure means "no peer path", the NCCL path is always valid
         _disabled_reason[key] = f"{type(exc).__name__}: {exc}"
         return None
-    _contexts[key] = ctx
+    _contexts[key] = (group, ctx)     # holding the group keeps its id from being reused by a later group
     return ctx
+
+
+def release_context(group) -> None:
+    """Collective over ``group``: unmap and free its symmetric memory (call before the group is destroyed)."""
+    entry = _contexts.pop(id(group), None)
+    _disabled_reason.pop(id(group), None)
+    if entry is not None:
+        entry[1].close()
 
 
 def disabled_reason(group) -> str | None:

@@ -221,5 +221,8 @@ class ProcessGroupManager:
                 if handle is None or id(handle) in done:
                     continue
                 done.add(id(handle))
+                from maltos_b200.ops import comm
+
+                comm.release_context(handle)
                 dist.destroy_process_group(handle)
         self.groups = {axis: None for axis in MeshAxis}

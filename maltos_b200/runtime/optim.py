@@ -30,6 +30,9 @@ class FusedAdamW(torch.optim.AdamW):
         self.low_precision_params: dict[int, torch.Tensor] = {}
         #: optional {id(master_param): tensor} gradients to use instead of ``param.grad`` (e.g. bf16 model grads)
         self.external_grads: dict[int, torch.Tensor] = {}
+        #: optional {id(master_param): callable -> device addresses}: the updated values of that parameter are stored as
+        #: bf16 at every address (peers' flat parameter buffers over NVLink) by the same kernel that does the update
+        self.push_destinations: dict[int, object] = {}
 
     def _state_for(self, p: torch.Tensor) -> dict:
         st = self.state[p]
@@ -61,20 +64,29 @@ class FusedAdamW(torch.optim.AdamW):
             if group.get("amsgrad") or group.get("maximize"):
                 raise NotImplementedError("FusedAdamW supports neither amsgrad nor maximize")
             beta1, beta2 = group["betas"]
-            items = []
+            items, pushed = [], []
             for p in group["params"]:
                 g = self.external_grads.get(id(p), p.grad)
                 if g is None:
                     continue
                 st = self._state_for(p)
                 st["step"] += 1
-                items.append((p, g, st["exp_avg"], st["exp_avg_sq"], self.low_precision_params.get(id(p)), float(st["step"])))
-            if not items:
-                continue
+                destinations = self.push_destinations.get(id(p)) if p.is_cuda else None
+                if destinations is not None:
+                    pushed.append((p, g, st, destinations))
+                else:
+                    items.append((p, g, st["exp_avg"], st["exp_avg_sq"], self.low_precision_params.get(id(p)), float(st["step"])))
             lr = group["lr"]
             lr = float(lr) if not torch.is_tensor(lr) else float(lr.item())
-            adamw_multi_tensor(items, lr=lr, beta1=beta1, beta2=beta2, eps=group["eps"],
-                               weight_decay=group["weight_decay"], grad_scale=self.grad_scale)
+            if items:
+                adamw_multi_tensor(items, lr=lr, beta1=beta1, beta2=beta2, eps=group["eps"],
+                                   weight_decay=group["weight_decay"], grad_scale=self.grad_scale)
+            if pushed:
+                from maltos_b200.ops.zero_fused import adamw_push
+
+                for p, g, st, destinations in pushed:
+                    adamw_push(p.data, g.contiguous(), st["exp_avg"], st["exp_avg_sq"], destinations(), step=float(st["step"]), lr=lr,
+                               beta1=beta1, beta2=beta2, eps=group["eps"], weight_decay=group["weight_decay"], grad_scale=self.grad_scale)
         return loss
 
 

@@ -8,9 +8,17 @@ POST_STEP all-gathers the updated slices back into the data buffer (reference ``
 
 Stage 2 keeps no full gradient buffer between micro-steps: a pooled buffer lives for one backward, its reduce-scatter
 runs every micro-step and the result is *added* to the shard gradient (reference ``runtime/plugins/zero2.py:183-397``).
+
+Peer-memory mode (``peer_memory=True`` or ``MALTOS_B200_ZERO_PEER=1``; bf16 parameters, NCCL group on one node): the flat
+parameter and gradient buffers live in CUDA-IPC symmetric memory. After backward each owner reads its gradient slice
+from all ranks' buffers and reduces, scales, accumulates and norms it in one kernel, and the AdamW kernel stores the
+updated bf16 slice into every rank's parameter buffer, so neither a reduce-scatter nor an all-gather is launched
+(``ops/zero_fused.py``). The kernels never wait on a peer; one-element all-reduces before and after each phase order them
+across ranks. Stage 2 keeps its gradient buffer for the whole run in this mode.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -44,6 +52,10 @@ class FlatBucket:
     fired: bool = False
     work: ChainedWork | None = None
     shard_scratch: torch.Tensor | None = None
+    peer_data_ptrs: list[int] | None = None   # peer-memory mode: device address of this bucket in every rank's data buffer
+    peer_grad_ptrs: list[int] | None = None   # ... and in every rank's gradient buffer
+    direct: bool = False                      # the reduce kernel wrote the shard gradient itself
+    fused_sq: torch.Tensor | None = None      # ||shard gradient||^2 from the reduce kernel (fp64 device scalar)
 
     @property
     def shard_numel(self) -> int:
@@ -69,9 +81,13 @@ class FlatBucket:
 class Zero1Plugin(ZeroPluginBase):
     accumulate_on_shard = False     # stage 2 flips this
 
-    def __init__(self, bucket_mb_size: int = 25, *, _id: PluginId = PluginId.ZERO1, _name: str = "zero1") -> None:
+    def __init__(self, bucket_mb_size: int = 25, *, peer_memory: bool | None = None, _id: PluginId = PluginId.ZERO1,
+                 _name: str = "zero1") -> None:
         super().__init__(id=_id, name=_name, owns_optimizer=True, bucket_mb_size=bucket_mb_size,
                          runs_after={PluginId.TP, PluginId.TP_SP, PluginId.PP, PluginId.EP, PluginId.CP})
+        self.peer_memory = (os.environ.get("MALTOS_B200_ZERO_PEER", "0") == "1") if peer_memory is None else bool(peer_memory)
+        self._barrier_tokens: dict[int, torch.Tensor] = {}
+        self._pushes = False
 
     # ------------------------------------------------------------------ setup
     def bind(self, runtime) -> None:
@@ -87,6 +103,7 @@ class Zero1Plugin(ZeroPluginBase):
             self._build_buckets(model)
             locals_ = [b.local_param for b in self.buckets]
             self.optimizer = self.runtime.create_optimizer(locals_)
+            self._register_push_destinations()
             self.scheduler = self.runtime.create_scheduler(self.optimizer)
         elif phase is SetupPhase.FINALIZE:
             names = {id(p): n for n, p in model.named_parameters()}
@@ -102,11 +119,15 @@ class Zero1Plugin(ZeroPluginBase):
             params = self._role_params(model, role)
             if not params:
                 continue
+            first_of_role = len(self.buckets)
             gc = self._group_context_for_role(role)
-            for group in self._build_param_buckets(params):
+            groups = self._build_param_buckets(params)
+            peer_slices = self._peer_buffers(role, gc, groups)
+            for group in groups:
                 total = sum(p.numel() for p in group)
                 padded = padded_len(total, gc.world_size)
-                data = torch.zeros(padded, dtype=group[0].dtype, device=group[0].device)
+                peer = None if peer_slices is None else peer_slices[len(self.buckets) - first_of_role]
+                data = torch.zeros(padded, dtype=group[0].dtype, device=group[0].device) if peer is None else peer[0]
                 offsets, at = [], 0
                 with torch.no_grad():
                     for p in group:
@@ -116,9 +137,72 @@ class Zero1Plugin(ZeroPluginBase):
                         at += p.numel()
                 bucket = FlatBucket(index=len(self.buckets), role=role, params=group, group_context=gc, data=data, offsets=offsets, total=total)
                 bucket.local_param = nn.Parameter(data[bucket.shard_start:bucket.shard_end].detach().clone())
-                if not self.accumulate_on_shard:
+                if peer is not None:
+                    bucket.grad, bucket.peer_data_ptrs, bucket.peer_grad_ptrs = peer[1], peer[2], peer[3]
+                elif not self.accumulate_on_shard:
                     bucket.grad = torch.zeros_like(data)
                 self.buckets.append(bucket)
+
+    def _peer_buffers(self, role: ParamRole, gc: GroupContext, groups):
+        """Peer-memory mode: per bucket ``(data, grad, data addresses per rank, grad addresses per rank)`` carved out of two
+        symmetric allocations of the role's shard group; None when the mode is off or cannot be used for this role."""
+        if not self.peer_memory or not groups or gc.group is None or gc.world_size <= 1 or gc.world_size > 16:
+            return None
+        first = groups[0][0]
+        if not first.is_cuda or any(p.dtype != torch.bfloat16 for g in groups for p in g):
+            return None
+        from maltos_b200.ops import comm
+
+        ctx = comm.context_for(gc.group)
+        if ctx is None:
+            return None
+        sizes = [padded_len(sum(p.numel() for p in g), gc.world_size) for g in groups]
+        starts, at = [], 0
+        for n in sizes:
+            starts.append(at)
+            at += (n + 127) // 128 * 128         # every bucket starts on a 256-byte boundary
+        data_sb = ctx.ensure_buffer(f"{self.name}.{role.name}.data", at * 2)
+        grad_sb = ctx.ensure_buffer(f"{self.name}.{role.name}.grad", at * 2)
+        data_all = data_sb.local_tensor(torch.bfloat16, at, first.device).zero_()
+        grad_all = grad_sb.local_tensor(torch.bfloat16, at, first.device).zero_()
+        self._barrier(gc.group)   # nobody reads a peer's buffer before it is zeroed
+        return [(data_all[s:s + n], grad_all[s:s + n], [p + 2 * s for p in data_sb.peer_ptrs], [p + 2 * s for p in grad_sb.peer_ptrs])
+                for s, n in zip(starts, sizes)]
+
+    def _barrier(self, group) -> None:
+        """Stream-ordered barrier of ``group``: everything queued before it on any rank completes before anything queued
+        after it on any rank starts."""
+        tok = self._barrier_tokens.get(id(group))
+        if tok is None:
+            tok = self._barrier_tokens[id(group)] = torch.zeros(1, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        dist.all_reduce(tok, group=group)
+
+    def _peer_groups(self):
+        seen = {}
+        for b in self.buckets:
+            if b.peer_grad_ptrs is not None:
+                seen[id(b.group_context.group)] = b.group_context.group
+        return list(seen.values())
+
+    def _register_push_destinations(self) -> None:
+        """When the optimizer is the fused AdamW over fp32 masters, let its kernel store every updated slice into all
+        ranks' parameter buffers (and into the local slice parameter) instead of all-gathering afterwards."""
+        from maltos_b200.ops.zero_fused import ring_order
+        from maltos_b200.runtime.optim import FusedAdamW, MasterWeightsOptimizer
+
+        opt = self.optimizer
+        if not isinstance(opt, MasterWeightsOptimizer) or not isinstance(opt.inner, FusedAdamW):
+            return
+        master_of = {id(p): m for p, m in zip(opt.model_params, opt.master_params)}
+        for b in self.buckets:
+            master = master_of.get(id(b.local_param))
+            if b.peer_data_ptrs is None or master is None:
+                continue
+            shard_bytes = b.shard_start * 2
+            ring = ring_order([p + shard_bytes for p in b.peer_data_ptrs], b.group_context.rank)
+            opt.inner.push_destinations[id(master)] = lambda ring=ring, b=b: ring + [b.local_param.data_ptr()]
+            opt.inner.low_precision_params.pop(id(master), None)
+            self._pushes = True
 
     # ------------------------------------------------------------------ backward
     def _attach_grad_views(self, b: FlatBucket) -> None:
@@ -142,6 +226,10 @@ class Zero1Plugin(ZeroPluginBase):
             b.shard_scratch = torch.empty(b.shard_numel, dtype=b.grad.dtype, device=b.grad.device)
         dst = b.shard_scratch
 
+        b.direct = False
+        if b.peer_grad_ptrs is not None:
+            return self._peer_reduce_chain(b, dst)
+
         def reduce():
             if gc.group is None or gc.world_size == 1:
                 if gc.correction != 1.0:
@@ -155,7 +243,38 @@ class Zero1Plugin(ZeroPluginBase):
         chain = ChainedWork(None, reduce, blocks_by_stream=gc.supports_async_overlap)
         return self._apply_chained_work_wrappers(chain, dst, b.role)
 
+    def _peer_reduce_chain(self, b: FlatBucket, dst: torch.Tensor) -> ChainedWork:
+        """Owner-side pull of the shard from every rank's gradient buffer. Without further reduction links for the role
+        the kernel writes (stage 1) or accumulates into (stage 2) the shard gradient itself and produces its squared norm."""
+        from maltos_b200.ops.zero_fused import peer_reduce_shard
+
+        gc = b.group_context
+        lp = b.local_param
+        has_links = any(only is None or only == b.role for _, only in self._chained_work_wrappers)
+        existed = lp.grad is not None
+        if not has_links and not existed:
+            lp.grad = torch.empty(b.shard_numel, dtype=b.grad.dtype, device=b.grad.device)
+        b.direct = not has_links and lp.grad.dtype == b.grad.dtype and lp.grad.is_contiguous() and lp.grad.numel() == b.shard_numel
+        accumulate = b.direct and existed and self.accumulate_on_shard
+        out = lp.grad if b.direct else dst
+        plain_norm = all(float(self.runtime.grad_norm_replica_factor(p)) == 1.0 for p in b.params)
+        if b.direct and plain_norm:
+            b.fused_sq = torch.zeros((), dtype=torch.float64, device=dst.device) if b.fused_sq is None else b.fused_sq.zero_()
+        else:
+            b.fused_sq = None
+        srcs = [p + 2 * b.shard_start for p in b.peer_grad_ptrs]
+
+        def reduce():
+            peer_reduce_shard(srcs, gc.rank, b.shard_numel, gc.correction / gc.world_size, out,
+                              accumulate=accumulate, sumsq=b.fused_sq)
+            return CompletedWork()
+
+        chain = ChainedWork(None, reduce, blocks_by_stream=True)
+        return self._apply_chained_work_wrappers(chain, dst, b.role)
+
     def _fire(self, b: FlatBucket) -> None:
+        if b.peer_grad_ptrs is not None and not self._peers_ready:
+            return              # the peers' gradients are complete only after the barrier in POST_BACKWARD
         b.work = self._reduce_chain(b)
         b.work.fire()
         b.fired = True
@@ -165,7 +284,9 @@ class Zero1Plugin(ZeroPluginBase):
             self._fire(b)   # a rank whose hooks did not all run still joins the collective
         b.work.wait()
         lp = b.local_param
-        if lp.grad is None:
+        if b.direct:
+            pass
+        elif lp.grad is None:
             lp.grad = b.shard_scratch.detach().clone()
         elif self.accumulate_on_shard:
             lp.grad.add_(b.shard_scratch)
@@ -195,18 +316,31 @@ class Zero1Plugin(ZeroPluginBase):
             b.pending = len(b.params) if ctx.is_step_boundary else 0
             b.fired = False
 
+    _peers_ready = False
+
+    def _peer_phase(self, begin: bool) -> None:
+        """Brackets the owner-side reductions: all ranks' gradients are complete before the first read, and every read is
+        done before any rank touches its gradient buffer again."""
+        for g in self._peer_groups():
+            self._barrier(g)
+        self._peers_ready = begin
+
     def _post_backward(self, ctx) -> None:
         if not ctx.is_step_boundary:
             return
         with span("maltos::zero.grad_sync.wait"):
+            self._peer_phase(True)
             for b in self.buckets:
                 self._finish(b)
+            self._peer_phase(False)
 
     def _gather_updated_params(self) -> None:
         works = []
         with torch.no_grad():
             for b in self.buckets:
                 gc = b.group_context
+                if self._pushes and b.peer_data_ptrs is not None:
+                    continue            # the optimizer kernel stored the slice into every rank's buffer
                 src = b.local_param.detach().contiguous()
                 if gc.group is None or gc.world_size == 1:
                     b.data[b.shard_start:b.shard_end].copy_(src)
@@ -216,6 +350,9 @@ class Zero1Plugin(ZeroPluginBase):
                         works.append(w)
             for w in works:
                 w.wait()
+            if self._pushes:
+                for g in self._peer_groups():
+                    self._barrier(g)    # all peers' stores have landed before the next forward reads the parameters
 
     def _resync_from_buffers(self) -> None:
         with torch.no_grad():
@@ -231,6 +368,8 @@ class Zero1Plugin(ZeroPluginBase):
         out = torch.zeros((), dtype=torch.float64, device=b.local_param.device)
         if g is None:
             return out
+        if b.direct and b.fused_sq is not None:
+            return b.fused_sq.clone()
         lo, hi = b.shard_start, b.shard_end
         for p, at in zip(b.params, b.offsets):
             s, e = max(at, lo), min(at + p.numel(), hi)
@@ -242,8 +381,8 @@ class Zero1Plugin(ZeroPluginBase):
 class Zero2Plugin(Zero1Plugin):
     accumulate_on_shard = True
 
-    def __init__(self, bucket_mb_size: int = 25) -> None:
-        super().__init__(bucket_mb_size, _id=PluginId.ZERO2, _name="zero2")
+    def __init__(self, bucket_mb_size: int = 25, *, peer_memory: bool | None = None) -> None:
+        super().__init__(bucket_mb_size, peer_memory=peer_memory, _id=PluginId.ZERO2, _name="zero2")
 
     def _pre_backward(self, ctx) -> None:
         for b in self.buckets:
@@ -259,13 +398,16 @@ class Zero2Plugin(Zero1Plugin):
 
     def _post_backward(self, ctx) -> None:
         with span("maltos::zero.grad_sync.wait"):
+            self._peer_phase(True)
             for b in self.buckets:
                 self._finish(b)
                 for p in b.params:
                     p.grad = None
                 if b.grad_handle is not None:
                     release_buffer(b.grad_handle)
-                b.grad, b.grad_handle = None, None
+                if b.peer_grad_ptrs is None:
+                    b.grad, b.grad_handle = None, None
+            self._peer_phase(False)
 
     def export_plugin_state(self):
         ctx = self.runtime.state.step_context
