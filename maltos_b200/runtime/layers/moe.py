@@ -7,8 +7,10 @@ where the gated outputs are summed per token. Every local expert is called even 
 execute the same module sequence (ZeRO-3 hooks depend on it). The Switch-style load-balance loss is computed from the
 local tokens. With the defaults (top-1, no capacity) this is the reference layer (``runtime/layers/moe.py:19-163``).
 
-On CUDA with peer access the dispatch/combine transfers are P2P stores issued by the grouped-GEMM kernels
-(``maltos_b200.ops.comm``); the ``all_to_all_single`` path below is the gloo / oracle implementation.
+On CUDA with peer access (``MALTOS_B200_MOE_PEER=1``) dispatch and combine are one-sided row transfers over NVLink into /
+out of the peers' expert-major buffers (``maltos_b200.ops.moe_dispatch``): one count all-gather instead of the count
+exchange, no gate / expert-id traffic, two row kernels instead of four all-to-alls. The ``all_to_all_single`` path below
+is the NCCL / gloo implementation and the oracle.
 """
 from __future__ import annotations
 
@@ -105,6 +107,12 @@ class ExpertParallelMoE(nn.Module):
         if keep is not None:                                              # dropped assignments are not sent at all
             sel = keep.reshape(-1).nonzero(as_tuple=False).flatten()
             a_expert, a_gate, a_token = a_expert[sel], a_gate[sel], a_token[sel]
+        from maltos_b200.ops import moe_dispatch
+
+        peer = moe_dispatch.peer_context(self.ep_group, flat)
+        if peer is not None:
+            out = self._forward_peer(peer, flat, a_expert, a_gate, a_token).view(B, S, H)
+            return (out, aux) if return_aux_loss else out
         dest = torch.div(a_expert, per, rounding_mode="floor")
         order = torch.argsort(dest, stable=True)
         send_tok = flat.index_select(0, a_token[order])
@@ -135,3 +143,19 @@ class ExpertParallelMoE(nn.Module):
         if not return_aux_loss:
             return out
         return out, aux
+
+    def _forward_peer(self, peer, flat, a_expert, a_gate, a_token):
+        """Dispatch / combine as one-sided row transfers through the peers' symmetric buffers."""
+        from maltos_b200.ops import moe_dispatch
+
+        plan = moe_dispatch.build_plan(peer, self.ep_group, a_expert, self.num_experts, flat.shape[1], flat.dtype)
+        token_of_row = a_token[plan.order]
+        received = moe_dispatch.dispatch(flat, token_of_row, plan)          # [rows, H], sorted by local expert
+        outs, at = [], 0
+        for e, n in enumerate(plan.local_counts):                           # every expert is entered, also with zero rows
+            outs.append(self.local_experts[e](received[at:at + n]))
+            at += n
+        processed = torch.cat(outs, dim=0).to(flat.dtype) if outs else received
+        back = moe_dispatch.combine(processed, plan)                        # [assignments, H] in dispatch order
+        gated = back * a_gate[plan.order].unsqueeze(1).to(back.dtype)
+        return torch.zeros_like(flat).index_add(0, token_of_row, gated)
