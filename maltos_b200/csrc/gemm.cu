@@ -12,6 +12,8 @@
 //   a_mn = 0 : A is [M,K] row-major ("K-major").      a_mn = 1 : A is stored as [K,M] row-major.
 //   b_mn = 0 : B is [N,K] row-major ("K-major").      b_mn = 1 : B is stored as [K,N] row-major.
 // which covers forward (x W^T), dgrad (dy W) and wgrad (dy^T x) of a linear layer.
+#include <cstdlib>
+
 #include "host.h"
 #include "ptx.cuh"
 
@@ -59,6 +61,7 @@ struct GemmArgs {
   int stages;         // debug: ring depth used by the CTA-pair kernel (0 = all)
   int debug_mode;     // 0 normal; 1 = MMAs without waiting for data (producer idle); 2 = loads without MMAs (timing probes)
   long long* trace;   // debug: per-CTA cycle counters {mma total, wait full, wait tempty, producer wait empty} or nullptr
+  int quad_epilogue;  // 1: interior bf16 tiles of the CTA-pair kernels are written with the line-coalesced epilogue
   ScatterArgs sc;
 };
 
@@ -370,6 +373,42 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& p, int row, int
         dst[i] = __float2bfloat16(o);
       }
     }
+  }
+}
+
+// Line-coalesced bf16 epilogue of a 16-row x 64-column accumulator block loaded with tmem_ld_16x256b_x8: after packing
+// to bf16 pairs the four threads of a quad exchange 2-register blocks (a 4x4 transpose in two xor-shuffle stages) so
+// that thread q of the quad holds columns 16q..16q+15 of its row; one 32-byte store per thread then makes every warp
+// store instruction cover 8 rows x 128 contiguous bytes (8 lines) instead of 32 rows x 32 bytes (32 lines).
+// `dst` points at (first row of the block, first column of the block); rows g and g+8 of the block are written.
+__device__ __forceinline__ void epilogue_store_quad(__nv_bfloat16* dst, long long ldc, const uint32_t (&r)[32], int lane) {
+  const int qd = lane & 3, g = lane >> 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {   // h = 0: row g, h = 1: row g + 8
+    uint32_t x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = pack_bf16x2(__uint_as_float(r[4 * i + 2 * h]), __uint_as_float(r[4 * i + 2 * h + 1]));
+    // block j = (x[2j], x[2j+1]) = columns 16j + 2qd (+1) and 16j + 8 + 2qd (+1); transpose blocks across the quad
+#pragma unroll
+    for (int s = 1; s <= 2; s <<= 1) {
+      const bool upper = (qd & s) != 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j & s) continue;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t lo = x[2 * j + e], hi = x[2 * (j ^ s) + e];
+          const uint32_t got = __shfl_xor_sync(0xffffffffu, upper ? lo : hi, s);
+          if (upper) x[2 * j + e] = got;
+          else x[2 * (j ^ s) + e] = got;
+        }
+      }
+    }
+    // now block j came from quad thread j: x[2j] = columns 16qd + 2j (+1), x[2j+1] = columns 16qd + 8 + 2j (+1)
+    __nv_bfloat16* out = dst + static_cast<long long>(g + 8 * h) * ldc + 16 * qd;
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out), "r"(x[0]), "r"(x[2]), "r"(x[4]), "r"(x[6]),
+                 "r"(x[1]), "r"(x[3]), "r"(x[5]), "r"(x[7])
+                 : "memory");
   }
 }
 
@@ -847,6 +886,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint32_t acc_phase = 0;
     const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const bool quad_ok = WIDE && p.quad_epilogue && !p.out_fp32 && !p.accumulate && !p.bias && !p.sc.enabled && (p.ldc & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.C) & 31) == 0;
     const uint32_t tempty_leader[2] = {mapa_u32(&tempty_bar[0], 0), mapa_u32(&tempty_bar[1], 0)};
     for (int tile = pair; tile < total_tiles; tile += n_pairs) {
       int m_blk, n_blk;
@@ -867,17 +908,37 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         return WIDE ? n_blk * TILE_N + ((c & 4) ? 256 : 0) + (c >> 3) * 128 + (c & 3) * 32 : n_blk * kPairTile + c * 32;
       };
       uint32_t ra[32], rb[32];
-      tmem_ld_32x32b_x32(t_row + c_begin * 32, ra);
+      const int tile_row0 = m_blk * kPairTile + static_cast<int>(cta_rank) * 128;
+      const int tile_col0 = n_blk * (WIDE ? TILE_N : kPairTile);
+      if (quad_ok && tile_row0 + 128 <= p.M && tile_col0 + (WIDE ? TILE_N : kPairTile) <= p.N) {
+        // interior tile, plain bf16 output: 16-row x 64-column blocks, whole 128-byte lines per store instruction
+        __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(tile_row0 + q * 32) * p.ldc;
+        const uint32_t t_lo = tmem_base + static_cast<uint32_t>(acc * kPairTile) + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t t_hi = t_lo + (16u << 16);
+        tmem_ld_16x256b_x8(t_lo + c_begin * 32, ra);
 #pragma unroll 1
-      for (int c = c_begin; c < c_end; c += 2) {
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(t_row + (c + 1) * 32, rb);
-        int col0 = out_col(c);
-        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, ra, vec_ok);
-        tmem_ld_wait();
-        if (c + 2 < c_end) tmem_ld_32x32b_x32(t_row + (c + 2) * 32, ra);
-        col0 = out_col(c + 1);
-        if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, rb, vec_ok);
+        for (int c = c_begin; c < c_end; c += 2) {
+          tmem_ld_wait();
+          tmem_ld_16x256b_x8(t_hi + c * 32, rb);
+          __nv_bfloat16* blk = c_base + out_col(c);
+          epilogue_store_quad(blk, p.ldc, ra, lane);
+          tmem_ld_wait();
+          if (c + 2 < c_end) tmem_ld_16x256b_x8(t_lo + (c + 2) * 32, ra);
+          epilogue_store_quad(blk + 16 * p.ldc, p.ldc, rb, lane);
+        }
+      } else {
+        tmem_ld_32x32b_x32(t_row + c_begin * 32, ra);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 2) {
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(t_row + (c + 1) * 32, rb);
+          int col0 = out_col(c);
+          if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, ra, vec_ok);
+          tmem_ld_wait();
+          if (c + 2 < c_end) tmem_ld_32x32b_x32(t_row + (c + 2) * 32, ra);
+          col0 = out_col(c + 1);
+          if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, rb, vec_ok);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -1065,6 +1126,10 @@ static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
 static long long* g_trace = nullptr;
 static int g_pair_group_m = 8;
 static int g_debug_mode = 0;
+static int g_quad_epilogue = [] {
+  const char* e = getenv("MALTOS_B200_QUAD_EPILOGUE");
+  return e ? atoi(e) : 0;
+}();
 static int g_push_bulk = 0;      // fused all-gather: 1 = push with bulk async copies, 0 = push with the copy warps
 static int g_scatter_kind = 0;   // tuning: kernel kind forced for the fused reduce-scatter GEMM (0 = cost model)
 static int g_debug_stages = 0;
@@ -1081,6 +1146,9 @@ MB_API void mb_gemm_set_tuning(int group_m) {
 }
 // Timing probes of the CTA-pair kernel (results are meaningless): 1 = math only, 2 = loads only, 0 = normal.
 MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
+// 0 selects the row-per-thread epilogue everywhere, 1 the line-coalesced one where it applies
+// (initial value: environment variable MALTOS_B200_QUAD_EPILOGUE, default 0).
+MB_API void mb_gemm_set_quad_epilogue(int on) { mb::g_quad_epilogue = on ? 1 : 0; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
 MB_API void mb_gemm_set_push_bulk(int on) { mb::g_push_bulk = on ? 1 : 0; }
@@ -1127,6 +1195,7 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
   args.trace = g_trace;
   args.group_m = g_pair_group_m;
   args.debug_mode = g_debug_mode;
+  args.quad_epilogue = g_quad_epilogue;
   args.stages = g_debug_stages;
   args.a_lbo = a_mn ? 8192u : 16u, args.a_sbo = 1024u, args.a_kstep = a_mn ? 2048u : 32u;
   args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;
@@ -1197,6 +1266,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   args.trace = nullptr;
   args.group_m = g_pair_group_m;
   args.debug_mode = g_debug_mode;
+  args.quad_epilogue = g_quad_epilogue;
   args.stages = g_debug_stages;
   args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
   args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;
@@ -1266,6 +1336,7 @@ MB_API int mb_gemm_rs_bf16(const void* X, long long lda, const void* W, int b_mn
   args.trace = nullptr;
   args.group_m = g_pair_group_m;
   args.debug_mode = 0;
+  args.quad_epilogue = g_quad_epilogue;
   args.stages = 0;
   args.a_lbo = 16u, args.a_sbo = 1024u, args.a_kstep = 32u;
   args.b_lbo = b_mn ? 8192u : 16u, args.b_sbo = 1024u, args.b_kstep = b_mn ? 2048u : 32u;

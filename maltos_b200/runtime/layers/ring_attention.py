@@ -9,7 +9,9 @@ its owner after a full turn (reference ``runtime/layers/ring_attention.py:36-258
 packed-document batches share one code path; blocks that are entirely invisible are skipped.
 
 On CUDA bf16 the per-block work is the tcgen05 flash kernel (``maltos_b200.ops.flash_attn``); elsewhere the fp32 block
-primitives of ``maltos_b200.ops.attention``.
+primitives of ``maltos_b200.ops.attention``. With ``MALTOS_B200_RING_PEER=1`` the exchange itself goes over peer memory
+(``maltos_b200.ops.peer_ring``): blocks are pulled from their owners on a copy stream, dK/dV contributions are pushed
+once to the owner's slots; the point-to-point ring below is the NCCL / gloo implementation and the oracle.
 """
 from __future__ import annotations
 
@@ -64,12 +66,34 @@ def _block_visible(q_pos, k_pos) -> bool:
 class _RingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, q_pos, q_seq, group, scale, participants=None):
-        comm = _RingComm(group, participants)
+        from maltos_b200.ops.peer_ring import peer_ring_for
+
         B, S, hq, D = q.shape
         out = torch.zeros((B, S, hq, D), dtype=torch.float32, device=q.device)
         lse = torch.full((B, hq, S), float("-inf"), dtype=torch.float32, device=q.device)
         seq_or_zero = q_seq if q_seq is not None else torch.zeros_like(q_pos)
         cur = [k, v, q_pos, seq_or_zero]
+        ring = peer_ring_for(group, q, participants)
+        if ring is not None:
+            layout, _ = ring.publish(cur)
+            main = torch.cuda.current_stream()
+            nxt = ring.pull(layout, (ring.rank - 1) % ring.world) if ring.world > 1 else None
+            for step in range(ring.world):
+                k_b, v_b, kp_b, ks_b = cur
+                upcoming = nxt
+                nxt = ring.pull(layout, (ring.rank - step - 2) % ring.world) if step + 2 < ring.world else None
+                if _block_visible(q_pos, kp_b):
+                    o_b, l_b = attention_block_forward(q, k_b, v_b, q_positions=q_pos, k_positions=kp_b, q_sequence_ids=q_seq,
+                                                       k_sequence_ids=ks_b if q_seq is not None else None, scale=scale)
+                    out, lse = merge_attention_blocks(out, lse, o_b.float(), l_b.float())
+                if upcoming is not None:
+                    main.wait_event(upcoming[1])
+                    cur = upcoming[0]
+            result = out.to(q.dtype)
+            ctx.save_for_backward(q, k, v, result, lse, q_pos, seq_or_zero)
+            ctx.group, ctx.scale, ctx.has_seq, ctx.participants = group, scale, q_seq is not None, participants
+            return result
+        comm = _RingComm(group, participants)
         for step in range(comm.world):
             nxt, works = (comm.start(cur) if step + 1 < comm.world else (None, []))
             k_b, v_b, kp_b, ks_b = cur
@@ -87,14 +111,37 @@ class _RingAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
+        from maltos_b200.ops.peer_ring import peer_ring_for
+
         q, k, v, out, lse, q_pos, seq_ids = ctx.saved_tensors
-        comm = _RingComm(ctx.group, ctx.participants)
         q_seq = seq_ids if ctx.has_seq else None
         dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        dout = dout.contiguous()
+        ring = peer_ring_for(ctx.group, q, ctx.participants)
+        if ring is not None:
+            cur = [k, v, q_pos, seq_ids]
+            layout, slots = ring.publish(cur, grad_slots_like=[k, v])
+            main = torch.cuda.current_stream()
+            nxt = ring.pull(layout, (ring.rank - 1) % ring.world) if ring.world > 1 else None
+            for step in range(ring.world):
+                k_b, v_b, kp_b, ks_b = cur
+                upcoming = nxt
+                nxt = ring.pull(layout, (ring.rank - step - 2) % ring.world) if step + 2 < ring.world else None
+                if _block_visible(q_pos, kp_b):
+                    dq_b, dk_b, dv_b = attention_block_backward(q, k_b, v_b, out, lse, dout, q_positions=q_pos, k_positions=kp_b,
+                                                                q_sequence_ids=q_seq, k_sequence_ids=ks_b if ctx.has_seq else None,
+                                                                scale=ctx.scale)
+                    dq += dq_b
+                    ring.push_grads(slots, (ring.rank - step) % ring.world, [dk_b, dv_b])
+                if upcoming is not None:
+                    main.wait_event(upcoming[1])
+                    cur = upcoming[0]
+            dk, dv = ring.reduce_grads(slots, [k.shape, v.shape])
+            return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
+        comm = _RingComm(ctx.group, ctx.participants)
         dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
         dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
         cur = [k, v, q_pos, seq_ids]
-        dout = dout.contiguous()
         for step in range(comm.world):
             k_b, v_b, kp_b, ks_b = cur
             nxt, works = (comm.start(cur) if step + 1 < comm.world else (None, []))
