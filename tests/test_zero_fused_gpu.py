@@ -85,7 +85,9 @@ def _train(rank, world, stage, peer):
         for _ in range(2):
             ids = torch.randint(0, 96, (world * 4, 32), generator=g)
             batch = {"input_ids": ids[rank * 4:(rank + 1) * 4].cuda(), "labels": ids.roll(-1, 1)[rank * 4:(rank + 1) * 4].cuda()}
-            rt.run_step(batch)
+            loss, _ = rt.run_step(batch)
+            if rank == 0:
+                print(f"stage {stage} peer {peer}: micro-step loss {float(loss):.4f}", flush=True)
         rt.step_optimizer()
         losses.append(float(rt.collect_metrics()["loss"]))
     params = torch.cat([p.detach().float().reshape(-1) for p in rt.model.parameters()]).cpu()
@@ -107,8 +109,10 @@ def _worker(rank, world, port, queue):
         out = {}
         for stage in (1, 2):
             for peer in (False, True):
-                losses, params, norm = _train(rank, world, stage, peer)
-                out[(stage, peer)] = (losses, params, norm)
+                try:
+                    out[(stage, peer)] = _train(rank, world, stage, peer)
+                except Exception as exc:  # noqa: BLE001 - name the failing configuration
+                    raise RuntimeError(f"stage {stage}, peer_memory={peer} failed") from exc
         from maltos_b200.ops import _lib
 
         queue.put((rank, "ok", (out, _lib.fetch_status(raise_on_error=False))))
