@@ -1024,18 +1024,23 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 // wide tiles lose when the problem has too few of them to fill the 74 SM pairs.
 enum GemmKind { kKindSingle128 = 128, kKindSingle256 = 256, kKindPair = 512, kKindWide = 1024 };
 
-static GemmKind choose_gemm_kind(int M, int N) {
+static GemmKind choose_gemm_kind(int M, int N, int K) {
+  // Estimated cycles = waves x cycles per tile. Per k-block of 64: 128x128 tiles ~640 cycles, 128x256 tiles ~850 (both
+  // shared-memory bound, epilogue overlapped with the next tile's MMAs), 256x512 pair tiles ~1080 (tensor-pipe bound)
+  // plus ~5000 cycles of epilogue that cannot overlap because the accumulator fills tensor memory. With few k-blocks
+  // the 256x512 tile therefore loses to 128x256 (measured on 8192x4096: K=512 51 vs 45 us, K=1024 75 vs 75, K=1792 110
+  // vs 120), and it loses when the problem has too few tiles to fill the 74 SM pairs.
   const int sms = sm_count(), pairs = sms / 2;
-  auto cost = [&](int tm, int tn, int slots, double rate_per_slot) {
+  const double kb = static_cast<double>((K + kBK - 1) / kBK);
+  auto waves = [&](int tm, int tn, int slots) {
     const long long tiles = static_cast<long long>((M + tm - 1) / tm) * ((N + tn - 1) / tn);
-    const long long waves = (tiles + slots - 1) / slots;
-    return static_cast<double>(waves) * tm * tn / rate_per_slot;
+    return static_cast<double>((tiles + slots - 1) / slots);
   };
   GemmKind best = kKindSingle128;
-  double best_cost = cost(128, 128, sms, 0.4);
-  const double c256 = cost(128, 256, sms, 0.7);
+  double best_cost = waves(128, 128, sms) * (kb * 640.0 > 1500.0 ? kb * 640.0 : 1500.0);
+  const double c256 = waves(128, 256, sms) * (kb * 850.0 > 3000.0 ? kb * 850.0 : 3000.0);
   if (c256 < best_cost) best = kKindSingle256, best_cost = c256;
-  const double cwide = cost(256, 512, pairs, 2 * 0.9);
+  const double cwide = waves(256, 512, pairs) * (kb * 1080.0 + 5000.0);
   if (cwide < best_cost) best = kKindWide, best_cost = cwide;
   return best;
 }
@@ -1128,7 +1133,7 @@ static int g_pair_group_m = 8;
 static int g_debug_mode = 0;
 static int g_quad_epilogue = [] {
   const char* e = getenv("MALTOS_B200_QUAD_EPILOGUE");
-  return e ? atoi(e) : 0;
+  return e ? atoi(e) : 1;
 }();
 static int g_push_bulk = 0;      // fused all-gather: 1 = push with bulk async copies, 0 = push with the copy warps
 static int g_scatter_kind = 0;   // tuning: kernel kind forced for the fused reduce-scatter GEMM (0 = cost model)
@@ -1147,7 +1152,7 @@ MB_API void mb_gemm_set_tuning(int group_m) {
 // Timing probes of the CTA-pair kernel (results are meaningless): 1 = math only, 2 = loads only, 0 = normal.
 MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
 // 0 selects the row-per-thread epilogue everywhere, 1 the line-coalesced one where it applies
-// (initial value: environment variable MALTOS_B200_QUAD_EPILOGUE, default 0).
+// (initial value: environment variable MALTOS_B200_QUAD_EPILOGUE, default 1).
 MB_API void mb_gemm_set_quad_epilogue(int on) { mb::g_quad_epilogue = on ? 1 : 0; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
@@ -1205,7 +1210,7 @@ MB_API int mb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, i
       if (g_desc_override[i] >= 0) *f[i] = static_cast<unsigned>(g_desc_override[i]);
   }
 
-  const int kind = (block_n == 128 || block_n == 256 || block_n == 512 || block_n == 1024) ? block_n : choose_gemm_kind(M, N);
+  const int kind = (block_n == 128 || block_n == 256 || block_n == 512 || block_n == 1024) ? block_n : choose_gemm_kind(M, N, K);
   const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
   const int bn = wide ? 256 : (pair ? 128 : kind);   // rows of B staged per CTA and k-block
   CUtensorMap tmA, tmB;
@@ -1285,7 +1290,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
     g.pads[r] = r < world ? pads[r] : 0ull;
   }
   const __nv_bfloat16* a_base = reinterpret_cast<const __nv_bfloat16*>(gathered[rank]) + static_cast<long long>(seq & 1u) * buf_elems;
-  const int kind = choose_gemm_kind(args.M, N);
+  const int kind = choose_gemm_kind(args.M, N, K);
   const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
   const int bn = wide ? 256 : (pair ? 128 : kind);
   CUtensorMap tmA, tmB;
@@ -1350,7 +1355,7 @@ MB_API int mb_gemm_rs_bf16(const void* X, long long lda, const void* W, int b_mn
     sc.slot_base[r] = r < world ? stage[r] + static_cast<unsigned long long>((buf_off + rank * slot_elems) * 2) : 0ull;
     sc.pads[r] = r < world ? pads[r] : 0ull;
   }
-  int kind = choose_gemm_kind(args.M, N);
+  int kind = choose_gemm_kind(args.M, N, K);
   if (g_scatter_kind > 0) kind = g_scatter_kind;
   const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
   const int bn = wide ? 256 : (pair ? 128 : kind);
