@@ -22,7 +22,7 @@ from . import _lib, comm
 
 
 def enabled() -> bool:
-    return os.environ.get("MALTOS_B200_MOE_PEER", "0") == "1"
+    return os.environ.get("MALTOS_B200_MOE_PEER", "1") == "1"
 
 
 def peer_context(group, x: torch.Tensor):

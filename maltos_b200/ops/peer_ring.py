@@ -25,7 +25,7 @@ _ALIGN = 256
 
 
 def enabled() -> bool:
-    return os.environ.get("MALTOS_B200_RING_PEER", "0") == "1"
+    return os.environ.get("MALTOS_B200_RING_PEER", "1") == "1"
 
 
 def peer_ring_for(group, q: torch.Tensor, participants) -> "PeerRing | None":
