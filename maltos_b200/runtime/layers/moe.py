@@ -7,7 +7,8 @@ where the gated outputs are summed per token. Every local expert is called even 
 execute the same module sequence (ZeRO-3 hooks depend on it). The Switch-style load-balance loss is computed from the
 local tokens. With the defaults (top-1, no capacity) this is the reference layer (``runtime/layers/moe.py:19-163``).
 
-On CUDA with peer access (default; ``MALTOS_B200_MOE_PEER=0`` turns it off) dispatch and combine are one-sided row transfers over NVLink into /
+On CUDA with peer access (default; ``MALTOS_B200_MOE_PEER=0`` turns it off) dispatch and combine are one-sided row
+transfers over NVLink into /
 out of the peers' expert-major buffers (``maltos_b200.ops.moe_dispatch``): one count all-gather instead of the count
 exchange, no gate / expert-id traffic, two row kernels instead of four all-to-alls. The ``all_to_all_single`` path below
 is the NCCL / gloo implementation and the oracle.

@@ -9,7 +9,8 @@ its owner after a full turn (reference ``runtime/layers/ring_attention.py:36-258
 packed-document batches share one code path; blocks that are entirely invisible are skipped.
 
 On CUDA bf16 the per-block work is the tcgen05 flash kernel (``maltos_b200.ops.flash_attn``); elsewhere the fp32 block
-primitives of ``maltos_b200.ops.attention``. With ``MALTOS_B200_RING_PEER=1`` the exchange itself goes over peer memory
+primitives of ``maltos_b200.ops.attention``. Between GPUs of one node the exchange itself goes over peer memory by default
+(``MALTOS_B200_RING_PEER=0`` turns that off)
 (``maltos_b200.ops.peer_ring``): blocks are pulled from their owners on a copy stream, dK/dV contributions are pushed
 once to the owner's slots; the point-to-point ring below is the NCCL / gloo implementation and the oracle.
 """
