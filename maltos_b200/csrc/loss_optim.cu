@@ -71,8 +71,9 @@ cross_entropy_kernel(const T* __restrict__ logits, long long row_stride, const l
   }
   // combine across the warp, then across warps
   {
+    // a thread (or a whole warp, when V < block size) without elements has m = -inf: its term must be 0, not exp(nan)
     const float wm = warp_max(m);
-    s = warp_add(s * __expf(m - wm));
+    s = warp_add(m == -INFINITY ? 0.f : s * __expf(m - wm));
     m = wm;
   }
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -82,7 +83,7 @@ cross_entropy_kernel(const T* __restrict__ logits, long long row_stride, const l
     float mm = l < kCeThreads / 32 ? red_m[l] : -INFINITY;
     float sv = l < kCeThreads / 32 ? red_s[l] : 0.f;
     const float gm = warp_max(mm);
-    sv = warp_add(sv * __expf(mm - gm));
+    sv = warp_add(mm == -INFINITY ? 0.f : sv * __expf(mm - gm));
     if (l == 0) red_m[0] = gm, red_s[0] = sv;
   }
   __syncthreads();
