@@ -886,8 +886,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     uint32_t acc_phase = 0;
     const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    const bool quad_ok = WIDE && p.quad_epilogue && !p.out_fp32 && !p.accumulate && !p.bias && !p.sc.enabled && (p.ldc & 15) == 0 &&
-                         (reinterpret_cast<uintptr_t>(p.C) & 31) == 0;
+    // (fused reduce-scatter: slots are 256-byte aligned and a 16-row block must not straddle two owners)
+    const bool quad_ok = WIDE && p.quad_epilogue && !p.out_fp32 && !p.accumulate && !p.bias && (p.ldc & 15) == 0 &&
+                         (p.sc.enabled ? (p.sc.rows_per_chunk & 15) == 0 : (reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
     const uint32_t tempty_leader[2] = {mapa_u32(&tempty_bar[0], 0), mapa_u32(&tempty_bar[1], 0)};
     for (int tile = pair; tile < total_tiles; tile += n_pairs) {
       int m_blk, n_blk;
@@ -912,7 +913,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int tile_col0 = n_blk * (WIDE ? TILE_N : kPairTile);
       if (quad_ok && tile_row0 + 128 <= p.M && tile_col0 + (WIDE ? TILE_N : kPairTile) <= p.N) {
         // interior tile, plain bf16 output: 16-row x 64-column blocks, whole 128-byte lines per store instruction
-        __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(tile_row0 + q * 32) * p.ldc;
+        // first row of a 16-row block -> where it is stored: C, or (fused reduce-scatter) the owner's staging slot
+        auto block_base = [&](int r0) -> __nv_bfloat16* {
+          if (!p.sc.enabled) return reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(r0) * p.ldc;
+          const int b = r0 / p.sc.s_rows, s = r0 - b * p.sc.s_rows;
+          const int owner = s / p.sc.rows_per_chunk;
+          const long long local = static_cast<long long>(b) * p.sc.rows_per_chunk + (s - owner * p.sc.rows_per_chunk);
+          return reinterpret_cast<__nv_bfloat16*>(p.sc.slot_base[owner]) + local * p.ldc;
+        };
+        __nv_bfloat16* c_lo = block_base(tile_row0 + q * 32);
+        __nv_bfloat16* c_hi = block_base(tile_row0 + q * 32 + 16);
         const uint32_t t_lo = tmem_base + static_cast<uint32_t>(acc * kPairTile) + (static_cast<uint32_t>(q * 32) << 16);
         const uint32_t t_hi = t_lo + (16u << 16);
         tmem_ld_16x256b_x8(t_lo + c_begin * 32, ra);
@@ -920,11 +930,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int c = c_begin; c < c_end; c += 2) {
           tmem_ld_wait();
           tmem_ld_16x256b_x8(t_hi + c * 32, rb);
-          __nv_bfloat16* blk = c_base + out_col(c);
-          epilogue_store_quad(blk, p.ldc, ra, lane);
+          const int col = out_col(c);
+          epilogue_store_quad(c_lo + col, p.ldc, ra, lane);
           tmem_ld_wait();
           if (c + 2 < c_end) tmem_ld_16x256b_x8(t_lo + (c + 2) * 32, ra);
-          epilogue_store_quad(blk + 16 * p.ldc, p.ldc, rb, lane);
+          epilogue_store_quad(c_hi + col, p.ldc, rb, lane);
         }
       } else {
         tmem_ld_32x32b_x32(t_row + c_begin * 32, ra);

@@ -60,7 +60,11 @@ def _worker(rank, world, port, queue):
         # row-parallel GEMM fused with the reduce-scatter (forward) and its backward
         from maltos_b200.ops.fused_tp import linear_reduce_scatter
 
-        for (B, S, Kin, H) in [(1, 512, 256, 256), (2, 384, 128, 512), (1, 2048, 512, 1024)]:
+        import ctypes
+
+        # the last case runs on the 256x512 kernel (forced), whose epilogue writes whole 128-byte lines into the peers' slots
+        for (B, S, Kin, H, kind) in [(1, 512, 256, 256, 0), (2, 384, 128, 512, 0), (1, 2048, 512, 1024, 0), (1, 2048, 512, 1024, 1024)]:
+            _lib.lib().mb_gemm_set_scatter_kind(ctypes.c_int(kind))
             w = torch.nn.Parameter((torch.randn(H, Kin, device="cuda", generator=torch.Generator(device="cuda").manual_seed(50 + rank)) * 0.05).bfloat16())
             g = torch.Generator(device="cuda").manual_seed(200 + rank)
             rows = S // world
@@ -82,6 +86,7 @@ def _worker(rank, world, port, queue):
                 gerr = max(gerr, ((w.grad.float() - dw_ref).abs().max() / dw_ref.abs().max()).item())
                 results.append((B, S, Kin, 10 + rep, err, gerr))
                 w.grad = None
+        _lib.lib().mb_gemm_set_scatter_kind(ctypes.c_int(0))
         status = _lib.fetch_status(raise_on_error=False)
         queue.put((rank, "ok", (results, status)))
         ctx.close()
