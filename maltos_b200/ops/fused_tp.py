@@ -142,8 +142,13 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         x2 = x_local.reshape(B * rows, K)
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
-        out, _ = all_gather_gemm(x2, fused, symm, B, rows, b_mn=False)
-        ctx.save_for_backward(x2, *weights)
+        out, gathered = all_gather_gemm(x2, fused, symm, B, rows, b_mn=False)
+        # The weight gradient needs the gathered input again. A device copy of it (taken while it is still in the
+        # symmetric buffer; only when a gradient is wanted, i.e. in the recomputation pass under activation
+        # checkpointing) replaces the all-gather the backward would otherwise launch.
+        keep = any(ctx.needs_input_grad[2:]) and os.environ.get("MALTOS_B200_KEEP_GATHERED", "1") == "1"
+        ctx.kept = keep
+        ctx.save_for_backward(x2, *weights, *([gathered.clone()] if keep else []))
         ctx.symm, ctx.layout, ctx.fused_ok = symm, layout, order is not None
         ctx.dims = (B, rows, K, N)
         return out.view(B, rows * T, N)
@@ -151,6 +156,7 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         x2, *weights = ctx.saved_tensors
+        x_kept = weights.pop() if ctx.kept else None
         B, rows, K, N = ctx.dims
         symm = ctx.symm
         d2 = dout.reshape(-1, N)
@@ -166,7 +172,7 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
                 dx_full = gemm(d2, fused, b_mn=True)                   # [B*S, K]
                 dx_local = _nccl_reduce_scatter_rows(dx_full, symm, B, rows).view(B, rows, K)
         if any(ctx.needs_input_grad[2:]):
-            x_full = _nccl_all_gather_rows(x2, symm, B, rows)          # re-gathered, as the forward buffer is recycled
+            x_full = x_kept if x_kept is not None else _nccl_all_gather_rows(x2, symm, B, rows)
             dwf = gemm(d2, x_full, a_mn=True, b_mn=True)               # [N, K]
             at = 0
             for i in ctx.layout:

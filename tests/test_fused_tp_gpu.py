@@ -53,6 +53,12 @@ def _worker(rank, world, port, queue):
                 dist.all_reduce(dx_full, group=group)
                 dx_ref = dx_full.view(B, world, rows, K)[:, rank]
                 gerr = ((x.grad.float() - dx_ref).abs().max() / dx_ref.abs().max()).item()
+                dw_ref = dyf.reshape(-1, dyf.shape[-1]).t() @ xf.reshape(-1, K)          # weight gradients from the gathered input
+                at = 0
+                for w in ws:
+                    piece = dw_ref[at:at + w.shape[0]]
+                    gerr = max(gerr, ((w.grad.float() - piece).abs().max() / piece.abs().max()).item())
+                    at += w.shape[0]
                 results.append((B, rows, K, rep, err, gerr))
                 for w in ws:
                     w.grad = None
