@@ -91,9 +91,11 @@ if _SCATTER_KIND:
 
 
 def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
-    # Opt-in: on NVSwitch systems NCCL reduces inside the switch, and the epilogue's 32-byte peer stores reach only about
-    # 200 GB/s, so GEMM + NCCL reduce-scatter is currently the faster pair (187 vs 237 us for o_proj at TP=4 on B200).
-    if os.environ.get("MALTOS_B200_FUSED_SCATTER", "0") != "1":
+    # MALTOS_B200_FUSED_SCATTER: "1" always, "0" never, unset = only for groups of two. Measured on B200 at TP=2 the fused
+    # launch beats GEMM + NCCL reduce-scatter (o_proj 214 vs 247 us, down 469 vs 542 us, +2.3 % on the training step); on
+    # larger NVSwitch groups NCCL reduces inside the switch and was the faster pair when last measured (TP=4).
+    mode = os.environ.get("MALTOS_B200_FUSED_SCATTER", "auto")
+    if mode == "0" or (mode != "1" and symm.world > 2):
         return False
     return getattr(symm, "fused_scatter", True) and x2.dtype == torch.bfloat16 and x2.is_cuda and n_out % 8 == 0
 
