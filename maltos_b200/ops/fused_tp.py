@@ -27,23 +27,31 @@ PUSH_CTAS = 4   # push warps per block
 
 
 def _nccl_all_gather_rows(x2: torch.Tensor, ctx, B: int, rows: int) -> torch.Tensor:
-    """[B*rows, K] local slices -> [B*rows*T, K] in batch-major, rank-minor order."""
+    """[B*rows, K] local slices -> [B*rows*T, K] in batch-major, rank-minor order (one collective per batch element, each
+    landing in place, so no permuting copy of the gathered tensor is needed)."""
     T = ctx.world
     K = x2.shape[1]
-    out = torch.empty((T, B * rows, K), dtype=x2.dtype, device=x2.device)
-    dist.all_gather_into_tensor(out.view(T * B * rows, K), x2.contiguous(), group=ctx.group)
-    if B == 1:
-        return out.view(T * rows, K)
-    return out.view(T, B, rows, K).permute(1, 0, 2, 3).reshape(B * T * rows, K)
+    x2 = x2.contiguous()
+    out = torch.empty((B, T * rows, K), dtype=x2.dtype, device=x2.device)
+    works = [dist.all_gather_into_tensor(out[b].view(T * rows, K), x2[b * rows:(b + 1) * rows], group=ctx.group, async_op=B > 1)
+             for b in range(B)]
+    for w in works:
+        if w is not None:
+            w.wait()
+    return out.view(B * T * rows, K)
 
 
 def _nccl_reduce_scatter_rows(y_full: torch.Tensor, ctx, B: int, rows: int) -> torch.Tensor:
-    """[B*T*rows, K] (batch-major) -> sum over ranks of this rank's [B*rows, K] slice."""
+    """[B*T*rows, K] (batch-major) -> sum over ranks of this rank's [B*rows, K] slice (one collective per batch element)."""
     T = ctx.world
     K = y_full.shape[1]
-    src = y_full if B == 1 else y_full.view(B, T, rows, K).permute(1, 0, 2, 3).reshape(T * B * rows, K)
+    y_full = y_full.contiguous()
     out = torch.empty((B * rows, K), dtype=y_full.dtype, device=y_full.device)
-    dist.reduce_scatter_tensor(out, src.contiguous(), op=dist.ReduceOp.SUM, group=ctx.group)
+    works = [dist.reduce_scatter_tensor(out[b * rows:(b + 1) * rows], y_full[b * T * rows:(b + 1) * T * rows], op=dist.ReduceOp.SUM,
+                                        group=ctx.group, async_op=B > 1) for b in range(B)]
+    for w in works:
+        if w is not None:
+            w.wait()
     return out
 
 

@@ -63,6 +63,21 @@ def _worker(rank, world, port, queue):
                 for w in ws:
                     w.grad = None
         set_push_mode(False)
+        # the NCCL helpers of the non-fused paths keep the batch-major layout for B > 1 without a permuting copy
+        from maltos_b200.ops.fused_tp import _nccl_all_gather_rows, _nccl_reduce_scatter_rows
+
+        B, rows, K = 2, 64, 128
+        xs = torch.randn(B * rows, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(300 + rank)).bfloat16()
+        got = _nccl_all_gather_rows(xs, ctx, B, rows)
+        allx = torch.empty(world, B, rows, K, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(allx.view(-1, K), xs, group=group)
+        assert torch.equal(got, allx.permute(1, 0, 2, 3).reshape(B * world * rows, K))
+        yf = torch.randn(B * world * rows, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(400 + rank)).bfloat16()
+        got = _nccl_reduce_scatter_rows(yf, ctx, B, rows)
+        tot = yf.float()
+        dist.all_reduce(tot, group=group)
+        want = tot.view(B, world, rows, K)[:, rank].reshape(B * rows, K)
+        assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
         # row-parallel GEMM fused with the reduce-scatter (forward) and its backward
         from maltos_b200.ops.fused_tp import linear_reduce_scatter
 
