@@ -13,6 +13,7 @@
 //   b_mn = 0 : B is [N,K] row-major ("K-major").      b_mn = 1 : B is stored as [K,N] row-major.
 // which covers forward (x W^T), dgrad (dy W) and wgrad (dy^T x) of a linear layer.
 #include <cstdlib>
+#include <mutex>
 
 #include "host.h"
 #include "ptx.cuh"
@@ -62,6 +63,13 @@ struct GemmArgs {
   int debug_mode;     // 0 normal; 1 = MMAs without waiting for data (producer idle); 2 = loads without MMAs (timing probes)
   long long* trace;   // debug: per-CTA cycle counters {mma total, wait full, wait tempty, producer wait empty} or nullptr
   int quad_epilogue;  // 1: interior bf16 tiles of the CTA-pair kernels are written with the line-coalesced epilogue
+  // Split tail (256x512 kernel, plain launches): when the tiles left for the last wave occupy at most half of the CTA
+  // pairs, each of them is computed by `tail_split` pairs over disjoint k ranges. Every epilogue warp writes its fp32
+  // partial block to `tail_ws`, then counts itself on `tail_cnt`; the warp that arrives last sums the partials and
+  // runs the normal epilogue. Nobody waits: the reduction is done by whoever finishes last.
+  int tail_split;         // 1 = off
+  float* tail_ws;         // [tail tiles][tail_split][2 CTAs][128 rows][512 cols] fp32
+  unsigned* tail_cnt;     // [tail tiles][2 CTAs][8 warps], zeroed before the launch
   ScatterArgs sc;
 };
 
@@ -658,9 +666,69 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // tfull[a] exist in both CTAs and are signalled by one commit addressed to both; tempty[a] lives in the leader and
 // collects the epilogue warps of both CTAs.
 static int g_debug_max_pairs = 0;   // debug cap on the number of CTA pairs (0 = all)
+static int g_tail_split = [] {
+  const char* e = getenv("MALTOS_B200_GEMM_TAIL_SPLIT");
+  return e ? atoi(e) : 1;
+}();
+
+// Workspace of the split tail, one per (device, stream) so that launches on different streams never share partials.
+// At most 74 tail tiles x slices of 512 KB each; allocated on first use and kept.
+struct TailWorkspace {
+  int dev;
+  cudaStream_t stream;
+  float* partials;
+  unsigned* counters;
+};
+constexpr size_t kTailPartialBytes = 74ull * 2 * 128 * 512 * sizeof(float);
+static TailWorkspace g_tail_ws[16];
+static int g_tail_ws_count = 0;
+static std::mutex g_tail_ws_mutex;
+static TailWorkspace* tail_workspace(int dev, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_tail_ws_mutex);
+  for (int i = 0; i < g_tail_ws_count; ++i)
+    if (g_tail_ws[i].dev == dev && g_tail_ws[i].stream == stream) return &g_tail_ws[i];
+  if (g_tail_ws_count == 16) return nullptr;
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) return nullptr;
+  TailWorkspace w{dev, stream, nullptr, nullptr};
+  if (cudaMalloc(&w.partials, kTailPartialBytes) != cudaSuccess) return nullptr;
+  if (cudaMalloc(&w.counters, 74 * 16 * sizeof(unsigned)) != cudaSuccess) {
+    cudaFree(w.partials);
+    return nullptr;
+  }
+  g_tail_ws[g_tail_ws_count] = w;
+  return &g_tail_ws[g_tail_ws_count++];
+}
 constexpr int kPairStages = 6;
 constexpr int kPairTile = 256;
 constexpr int kWideStages = 4;   // 256x512 tiles: 48 KB per stage and CTA
+
+// One unit of work of a CTA pair: a whole tile, or (split tail) one k range of a tile of the last wave.
+struct WorkUnit {
+  int tile;        // -1: nothing left
+  int kb0, kb1;    // k-block range
+  int slice;       // index of the k range, 0 when the tile is not split
+  int tail_idx;    // index among the tail tiles (for the workspace), -1 when not split
+};
+__device__ __forceinline__ WorkUnit work_unit(int it, int pair, int n_pairs, int total_tiles, int k_blocks, int split) {
+  WorkUnit u{-1, 0, k_blocks, 0, -1};
+  if (split <= 1) {
+    const int tile = pair + it * n_pairs;
+    if (tile < total_tiles) u.tile = tile;
+    return u;
+  }
+  const int full_iters = total_tiles / n_pairs, rem = total_tiles - full_iters * n_pairs;
+  if (it < full_iters) {
+    u.tile = pair + it * n_pairs;
+  } else if (it == full_iters && pair < rem * split) {
+    u.tail_idx = pair % rem;
+    u.slice = pair / rem;
+    u.tile = full_iters * n_pairs + u.tail_idx;
+    u.kb0 = static_cast<int>(static_cast<long long>(k_blocks) * u.slice / split);
+    u.kb1 = static_cast<int>(static_cast<long long>(k_blocks) * (u.slice + 1) / split);
+  }
+  return u;
+}
 
 template <bool WIDE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((WIDE ? kWideThreads : kGemmThreads) + kMaxPushThreads, 1)
@@ -748,9 +816,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int s = 0; s < STAGES; ++s) full_addr[s] = mapa_u32(&full_bar[s], 0);
       long long t_empty = 0;
       int n_issued = 0;
-      for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+      for (int it = 0; ok; ++it) {
+        const WorkUnit wu = work_unit(it, pair, n_pairs, total_tiles, p.k_blocks, p.tail_split);
+        if (wu.tile < 0) break;
         int m_blk, n_blk;
-        tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
+        tile_coords(wu.tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
         m_blk = (m_blk + m_rot) % p.tiles_m;
         const int m0 = m_blk * kPairTile + static_cast<int>(cta_rank) * 128;
         const int n0 = n_blk * TILE_N + static_cast<int>(cta_rank) * B_ROWS;
@@ -767,7 +837,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
           fence_proxy_async_global();
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = wu.kb0; kb < wu.kb1; ++kb) {
           const long long t0 = clock64();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             ok = false;
@@ -816,13 +886,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       long long t_full = 0, t_tempty = 0;
       int n_seen = 0;
       const long long t_begin = clock64();
-      for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+      for (int it = 0; ok; ++it) {
+        const WorkUnit wu = work_unit(it, pair, n_pairs, total_tiles, p.k_blocks, p.tail_split);
+        if (wu.tile < 0) break;
         long long t0 = clock64();
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) break;
         t_tempty += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairTile);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = wu.kb0; kb < wu.kb1; ++kb) {
           t0 = clock64();
           if (p.debug_mode != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
             ok = false;
@@ -847,10 +919,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int kk = 0; kk < kBK / 16; ++kk) {
             const uint64_t adesc = make_smem_desc_sw128(a_addr + kk * a_kstep, a_lbo, p.a_sbo);
             const uint64_t bdesc = make_smem_desc_sw128(b_addr + kk * b_kstep, b_lbo, p.b_sbo);
-            umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            const uint32_t accumulate = (kb != wu.kb0 || kk != 0) ? 1u : 0u;
+            umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, accumulate);
             if (WIDE) {   // second half of the tile: rows 128..255 of this CTA's B stage, accumulator columns 256..511
               const uint64_t bdesc2 = make_smem_desc_sw128(b_addr + 16384 + kk * b_kstep, b_lbo, p.b_sbo);
-              umma_bf16_ss_pair(d_tmem + 256, adesc, bdesc2, idesc, (kb | kk) != 0 ? 1u : 0u);
+              umma_bf16_ss_pair(d_tmem + 256, adesc, bdesc2, idesc, accumulate);
             }
           }
           umma_commit_pair(&empty_bar[stage], 3);   // both CTAs may refill this stage
@@ -890,9 +963,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const bool quad_ok = WIDE && p.quad_epilogue && !p.out_fp32 && !p.accumulate && !p.bias && (p.ldc & 15) == 0 &&
                          (p.sc.enabled ? (p.sc.rows_per_chunk & 15) == 0 : (reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
     const uint32_t tempty_leader[2] = {mapa_u32(&tempty_bar[0], 0), mapa_u32(&tempty_bar[1], 0)};
-    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+    for (int it = 0;; ++it) {
+      const WorkUnit wu = work_unit(it, pair, n_pairs, total_tiles, p.k_blocks, p.tail_split);
+      if (wu.tile < 0) break;
       int m_blk, n_blk;
-      tile_coords(tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
+      tile_coords(wu.tile, p.tiles_m, p.tiles_n, m_blk, n_blk, p.group_m);
       m_blk = (m_blk + m_rot) % p.tiles_m;
       bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -911,6 +986,57 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t ra[32], rb[32];
       const int tile_row0 = m_blk * kPairTile + static_cast<int>(cta_rank) * 128;
       const int tile_col0 = n_blk * (WIDE ? TILE_N : kPairTile);
+      if (WIDE && wu.tail_idx >= 0) {
+        // ---- split tail: fp32 partial of this warp's 32 rows x 256 columns -> workspace; the last arriver reduces
+        const int ew = warp - 2;                                     // 0..7: lane quarter q, column half ew / 4
+        const long long blk_elems = 128ll * 512;                     // one CTA's share of a tile
+        float* ws_tile = p.tail_ws + (static_cast<long long>(wu.tail_idx) * p.tail_split * 2) * blk_elems;
+        float* mine = ws_tile + (static_cast<long long>(wu.slice) * 2 + cta_rank) * blk_elems + static_cast<long long>(q * 32 + lane) * 512;
+        for (int c = c_begin; c < c_end; ++c) {
+          tmem_ld_32x32b_x32(t_row + c * 32, ra);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(mine + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(ra[4 * i]), __uint_as_float(ra[4 * i + 1]), __uint_as_float(ra[4 * i + 2]),
+                                 __uint_as_float(ra[4 * i + 3]));
+        }
+        // the accumulator is free again as soon as it has been read
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
+        __threadfence();
+        __syncwarp();
+        unsigned arrived = 0;
+        if (lane == 0) arrived = atomicAdd(p.tail_cnt + (wu.tail_idx * 2 + static_cast<int>(cta_rank)) * 8 + ew, 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived == static_cast<unsigned>(p.tail_split - 1)) {
+          __threadfence();
+          for (int c = c_begin; c < c_end; ++c) {
+            float acc32[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc32[i] = 0.f;
+            for (int sl = 0; sl < p.tail_split; ++sl) {
+              const float4* src = reinterpret_cast<const float4*>(ws_tile + (static_cast<long long>(sl) * 2 + cta_rank) * blk_elems +
+                                                                  static_cast<long long>(q * 32 + lane) * 512 + c * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 v = __ldcg(src + i);
+                acc32[4 * i] += v.x, acc32[4 * i + 1] += v.y, acc32[4 * i + 2] += v.z, acc32[4 * i + 3] += v.w;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(acc32[i]);
+            const int col0 = out_col(c);
+            if (row < p.M && col0 < p.N) epilogue_store32(p, row, col0, ra, vec_ok);
+          }
+        }
+        if (++acc == N_ACC) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        continue;
+      }
       if (quad_ok && tile_row0 + 128 <= p.M && tile_col0 + (WIDE ? TILE_N : kPairTile) <= p.N) {
         // interior tile, plain bf16 output: 16-row x 64-column blocks, whole 128-byte lines per store instruction
         // first row of a 16-row block -> where it is stored: C, or (fused reduce-scatter) the owner's staging slot
@@ -1018,7 +1144,28 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     g.bulk = 0;
   }
   const int max_pairs = g_debug_max_pairs > 0 ? g_debug_max_pairs : sm_count() / 2;
-  const int grid = 2 * (total < max_pairs ? total : max_pairs);
+  // Split tail: see GemmArgs. Worth it when the k range saved per pair outweighs writing and re-reading the fp32 partials
+  // (about 40k cycles): with s slices the last wave shrinks by (1 - 1/s) of a tile's main loop.
+  args.tail_split = 1;
+  args.tail_ws = nullptr;
+  args.tail_cnt = nullptr;
+  int split_pairs = 0;
+  if (WIDE && !g.enabled && !args.sc.enabled && g_tail_split && args.debug_mode == 0 && args.trace == nullptr) {
+    const int rem = total % max_pairs;
+    int s = rem > 0 ? max_pairs / rem : 1;
+    if (s > 4) s = 4;
+    while (s > 1 && args.k_blocks / s < 8) --s;
+    const double gain = args.k_blocks * 1080.0 * (1.0 - 1.0 / (s > 1 ? s : 1)) - 40000.0;
+    TailWorkspace* ws = (s > 1 && gain > 0.0) ? tail_workspace(dev, stream) : nullptr;
+    if (ws) {
+      args.tail_split = s;
+      args.tail_ws = ws->partials;
+      args.tail_cnt = ws->counters;
+      split_pairs = max_pairs;
+      MB_CHECK_CUDA(cudaMemsetAsync(ws->counters, 0, static_cast<size_t>(rem) * 16 * sizeof(unsigned), stream));
+    }
+  }
+  const int grid = split_pairs > 0 ? 2 * split_pairs : 2 * (total < max_pairs ? total : max_pairs);
   const int base_threads = WIDE ? kWideThreads : kGemmThreads;
   const int threads = g.enabled ? base_threads + 32 * g.push_ctas : base_threads;
   const size_t smem = (g.enabled && g.bulk) ? smem_max : smem_base;
@@ -1164,6 +1311,8 @@ MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
 // 0 selects the row-per-thread epilogue everywhere, 1 the line-coalesced one where it applies
 // (initial value: environment variable MALTOS_B200_QUAD_EPILOGUE, default 1).
 MB_API void mb_gemm_set_quad_epilogue(int on) { mb::g_quad_epilogue = on ? 1 : 0; }
+// 0 switches the split tail of the 256x512 kernel off (initial value: MALTOS_B200_GEMM_TAIL_SPLIT, default 1).
+MB_API void mb_gemm_set_tail_split(int on) { mb::g_tail_split = on ? 1 : 0; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
 MB_API void mb_gemm_set_push_bulk(int on) { mb::g_push_bulk = on ? 1 : 0; }

@@ -52,6 +52,36 @@ def test_gemm_pair_kernel_many_tiles_per_pair():
         assert _rel_err(out, ref + 1.0) < 2e-3
 
 
+@pytest.mark.parametrize("shape", [(512, 1024, 4096), (1000, 1500, 4224), (8192, 4096, 5120), (2560, 512, 8192)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
+def test_gemm_split_tail_of_the_wide_kernel(shape, a_mn, b_mn):
+    """Few tiles in the last wave and a long k range: the 256x512 kernel computes each tail tile on several CTA pairs
+    over disjoint k ranges and the warp that finishes last sums the fp32 partials. Same results as without the split,
+    for plain, ragged, accumulating, fp32 and biased outputs."""
+    import ctypes
+
+    M, N, K = shape
+    a, b = _mk(M, N, K, a_mn, b_mn, seed=7)
+    ref = _ref(a, b, a_mn, b_mn)
+    lib = _lib.lib()
+    for split in (1, 0):
+        lib.mb_gemm_set_tail_split(ctypes.c_int(split))
+        try:
+            c = gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024)
+            _lib.fetch_status()
+            assert _rel_err(c, ref) < 1e-2, split
+            bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+            out = torch.ones((M, N), device="cuda", dtype=torch.float32)
+            gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=True, bias=bias, block_n=1024)
+            _lib.fetch_status()
+            assert _rel_err(out, ref + bias.float() + 1.0) < 2e-3, split
+        finally:
+            lib.mb_gemm_set_tail_split(ctypes.c_int(1))
+    # twice in a row on the same stream: the counters are re-armed by every launch
+    c2 = gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024)
+    assert torch.equal(c2, gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024))
+
+
 def test_gemm_fp32_accumulate_and_bias():
     M, N, K = 256, 384, 512
     a, b = _mk(M, N, K, False, False, seed=1)
