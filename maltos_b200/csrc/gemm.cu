@@ -668,7 +668,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 static int g_debug_max_pairs = 0;   // debug cap on the number of CTA pairs (0 = all)
 static int g_tail_split = [] {
   const char* e = getenv("MALTOS_B200_GEMM_TAIL_SPLIT");
-  return e ? atoi(e) : 1;
+  return e ? atoi(e) : 0;
 }();
 
 // Workspace of the split tail, one per (device, stream) so that launches on different streams never share partials.
@@ -1311,7 +1311,7 @@ MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
 // 0 selects the row-per-thread epilogue everywhere, 1 the line-coalesced one where it applies
 // (initial value: environment variable MALTOS_B200_QUAD_EPILOGUE, default 1).
 MB_API void mb_gemm_set_quad_epilogue(int on) { mb::g_quad_epilogue = on ? 1 : 0; }
-// 0 switches the split tail of the 256x512 kernel off (initial value: MALTOS_B200_GEMM_TAIL_SPLIT, default 1).
+// 0 switches the split tail of the 256x512 kernel off (initial value: MALTOS_B200_GEMM_TAIL_SPLIT, default 0).
 MB_API void mb_gemm_set_tail_split(int on) { mb::g_tail_split = on ? 1 : 0; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }

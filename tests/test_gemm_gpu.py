@@ -76,10 +76,14 @@ def test_gemm_split_tail_of_the_wide_kernel(shape, a_mn, b_mn):
             _lib.fetch_status()
             assert _rel_err(out, ref + bias.float() + 1.0) < 2e-3, split
         finally:
-            lib.mb_gemm_set_tail_split(ctypes.c_int(1))
+            lib.mb_gemm_set_tail_split(ctypes.c_int(0))
     # twice in a row on the same stream: the counters are re-armed by every launch
-    c2 = gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024)
-    assert torch.equal(c2, gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024))
+    lib.mb_gemm_set_tail_split(ctypes.c_int(1))
+    try:
+        c2 = gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024)
+        assert torch.equal(c2, gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=1024))
+    finally:
+        lib.mb_gemm_set_tail_split(ctypes.c_int(0))
 
 
 def test_gemm_fp32_accumulate_and_bias():
