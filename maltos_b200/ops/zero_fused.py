@@ -78,3 +78,12 @@ def ring_order(ptrs, rank: int):
     """Peers starting after ``rank`` and wrapping around, the own entry last."""
     world = len(ptrs)
     return [ptrs[(rank + s) % world] for s in range(1, world + 1)]
+
+
+def peer_gather(out: torch.Tensor, src_ptrs, bytes_each: int) -> None:
+    """``out`` (contiguous) receives ``len(src_ptrs)`` pieces of ``bytes_each`` bytes back to back, piece r read from the
+    device address ``src_ptrs[r]`` (this GPU's or a peer's memory): a one-sided all-gather without a rendezvous."""
+    if not out.is_contiguous() or out.numel() * out.element_size() < len(src_ptrs) * bytes_each:
+        raise ValueError("peer_gather: out must be contiguous and hold all pieces")
+    _lib.check(_lib.lib().mb_peer_gather(_lib.ptr(out), _ptr_array(src_ptrs), _lib.c_int(len(src_ptrs)), _lib.c_ll(bytes_each),
+                                         _lib.stream_ptr()), "mb_peer_gather")

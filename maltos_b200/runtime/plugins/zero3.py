@@ -15,6 +15,8 @@ reduce-scatter runs every micro-step. Recompute under activation checkpointing r
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 
 import torch
@@ -52,6 +54,7 @@ class ShardedBucket:
     grads_pending: int = 0
     users: int = 0                  # nested materialisations (recompute inside backward)
     hook_module: nn.Module = None   # module whose forward/backward brackets the use of these parameters
+    peer_shard_ptrs: list[int] | None = None   # peer-memory mode: address of every rank's shard of this bucket
 
     @property
     def shard_numel(self) -> int:
@@ -63,10 +66,15 @@ class ShardedBucket:
 
 
 class Zero3Plugin(ZeroPluginBase):
-    def __init__(self, wrap_cls: set[type] | None = None, bucket_mb_size: int = 25) -> None:
+    def __init__(self, wrap_cls: set[type] | None = None, bucket_mb_size: int = 25, *, peer_memory: bool | None = None) -> None:
         super().__init__(id=PluginId.ZERO3, name="zero3", owns_optimizer=True, owns_model_state=True, bucket_mb_size=bucket_mb_size,
                          runs_after={PluginId.TP, PluginId.TP_SP, PluginId.PP, PluginId.EP, PluginId.CP, PluginId.COMPILE})
         self.wrap_cls = set(wrap_cls) if wrap_cls is not None else {nn.Linear}
+        #: peer-memory mode: the shards live in CUDA-IPC symmetric memory and a gather is a one-sided pull from the
+        #: peers' shards (one kernel, no rendezvous); barriers bracket only the optimizer step, when the shards change
+        self.peer_memory = (os.environ.get("MALTOS_B200_ZERO_PEER", "0") == "1") if peer_memory is None else bool(peer_memory)
+        self._peer_groups: dict[int, object] = {}
+        self._barrier_tokens: dict[int, torch.Tensor] = {}
         self._by_param: dict[int, ShardedBucket] = {}
         self._placeholder: dict[int, torch.Tensor] = {}
 
@@ -144,7 +152,8 @@ class Zero3Plugin(ZeroPluginBase):
                 for p, off, n in zip(params, offsets, numels):
                     flat[off:off + n].copy_(p.data.reshape(-1))
             lo = gc.rank * b.shard_numel
-            b.local_param = nn.Parameter(flat[lo:lo + b.shard_numel].clone())
+            shard = flat[lo:lo + b.shard_numel]
+            b.local_param = nn.Parameter(self._peer_shard(b, shard) if self._peer_ok(b, want, device) else shard.clone())
             for p in params:
                 self._by_param[id(p)] = b
                 ph = torch.empty(0, dtype=want, device=device)
@@ -152,8 +161,40 @@ class Zero3Plugin(ZeroPluginBase):
                 p.data = ph
             del flat
             self.buckets.append(b)
+        self._peer_barrier()     # every rank's shards are in place before anyone pulls them
         self.optimizer = rt.create_optimizer([b.local_param for b in self.buckets])
         self.scheduler = rt.create_scheduler(self.optimizer)
+
+    # ------------------------------------------------------------------ peer-memory mode
+    def _peer_ok(self, b: ShardedBucket, dtype, device) -> bool:
+        gc = b.group_context
+        return (self.peer_memory and device.type == "cuda" and dtype == torch.bfloat16 and gc.group is not None
+                and 1 < gc.world_size <= 16 and (b.shard_numel * 2) % 16 == 0 and self._peer_context(gc) is not None)
+
+    def _peer_context(self, gc: GroupContext):
+        from maltos_b200.ops import comm
+
+        ctx = comm.context_for(gc.group)
+        if ctx is not None:
+            self._peer_groups[id(gc.group)] = gc.group
+        return ctx
+
+    def _peer_shard(self, b: ShardedBucket, shard: torch.Tensor) -> torch.Tensor:
+        """Collective: this bucket's shard in its own symmetric allocation (values copied), addresses of all ranks' shards."""
+        ctx = self._peer_context(b.group_context)
+        sb = ctx.ensure_buffer(f"zero3.shard.{b.index}", b.shard_numel * 2)
+        local = sb.local_tensor(torch.bfloat16, b.shard_numel, shard.device)
+        local.copy_(shard)
+        b.peer_shard_ptrs = list(sb.peer_ptrs)
+        return local
+
+    def _peer_barrier(self) -> None:
+        """Stream-ordered barrier of every shard group in peer-memory mode (no-op otherwise)."""
+        for key, group in self._peer_groups.items():
+            tok = self._barrier_tokens.get(key)
+            if tok is None:
+                tok = self._barrier_tokens[key] = torch.zeros(1, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+            dist.all_reduce(tok, group=group)
 
     # ------------------------------------------------------------------ gather / release
     def _gather(self, b: ShardedBucket) -> None:
@@ -167,6 +208,10 @@ class Zero3Plugin(ZeroPluginBase):
         with torch.no_grad():
             if gc.group is None or gc.world_size == 1:
                 full.copy_(lp.data)
+            elif b.peer_shard_ptrs is not None:
+                from maltos_b200.ops.zero_fused import peer_gather
+
+                peer_gather(full, b.peer_shard_ptrs, b.shard_numel * 2)
             else:
                 all_gather_single(full, lp.data.contiguous(), group=gc.group)
         for p, off, n, shape in zip(b.params, b.offsets, b.param_numels, b.param_shapes):
@@ -285,10 +330,14 @@ class Zero3Plugin(ZeroPluginBase):
                         self._release(b, force=True)
         elif phase is RuntimePhase.PRE_STEP:
             self._maybe_clip_local_shards()
+            self._peer_barrier()     # every pull of the old shards is done before any optimizer overwrites them
+        elif phase is RuntimePhase.POST_STEP:
+            self._peer_barrier()     # every shard is updated before the next forward pulls it
         elif phase is RuntimePhase.POST_LOAD:
             sync = getattr(self.optimizer, "sync_master_params_from_model", None)
             if callable(sync):
                 sync()
+            self._peer_barrier()
 
     # ------------------------------------------------------------------ clipping
     def _bucket_local_sq(self, b: ShardedBucket) -> torch.Tensor:

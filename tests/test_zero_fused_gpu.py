@@ -59,6 +59,18 @@ def test_adamw_push_matches_reference_and_reaches_every_destination(n, grad_dtyp
         assert torch.equal(d, master.bfloat16())
 
 
+@pytest.mark.parametrize("world,bytes_each", [(2, 16), (4, 4096 + 16), (8, 3 << 20)])
+def test_peer_gather_concatenates_the_pieces(world, bytes_each):
+    from maltos_b200.ops.zero_fused import peer_gather
+
+    g = torch.Generator(device="cuda").manual_seed(bytes_each)
+    pieces = [torch.randint(0, 255, (bytes_each + 64,), dtype=torch.uint8, device="cuda", generator=g) for _ in range(world)]
+    out = torch.zeros(world * bytes_each + 32, dtype=torch.uint8, device="cuda")
+    peer_gather(out, [p.data_ptr() for p in pieces], bytes_each)
+    assert torch.equal(out[:world * bytes_each], torch.cat([p[:bytes_each] for p in pieces]))
+    assert int(out[world * bytes_each:].sum()) == 0
+
+
 # ------------------------------------------------------------------------------------------------ plugin path on 2 GPUs
 def _train(rank, world, stage, peer):
     import torch.distributed as dist
@@ -72,13 +84,24 @@ def _train(rank, world, stage, peer):
 
     torch.manual_seed(4321)
     model = models.TinyTransformer(128, 4, 2, 256, 1e-5, 2, 96, 32)
-    cls = zero1.Zero1Plugin if stage == 1 else zero1.Zero2Plugin
-    plugin = cls(bucket_mb_size=1, peer_memory=peer)
+    if stage == 3:
+        import torch.nn as nn
+
+        from maltos_b200.models.tiny_transformer import RmsNorm
+        from maltos_b200.runtime.plugins import zero3
+
+        plugin = zero3.Zero3Plugin(wrap_cls={nn.Linear, nn.Embedding, RmsNorm}, peer_memory=peer)
+    else:
+        cls = zero1.Zero1Plugin if stage == 1 else zero1.Zero2Plugin
+        plugin = cls(bucket_mb_size=1, peer_memory=peer)
     rt = RuntimeCore(model=model, mesh=MeshConfig(dp=world), plan=ParallelPlan(), plugins=[plugin], dtype=torch.bfloat16,
                      device=torch.device("cuda", rank), optimizer_factory=lambda ps: FusedAdamW(ps, lr=1e-2, weight_decay=0.01),
                      grad_accum_steps=2, grad_clip_max_norm=0.5)
     rt.setup()
-    assert (plugin.buckets[0].peer_grad_ptrs is not None) == peer and plugin._pushes == peer
+    if stage == 3:
+        assert all((b.peer_shard_ptrs is not None) == peer for b in plugin.buckets)
+    else:
+        assert (plugin.buckets[0].peer_grad_ptrs is not None) == peer and plugin._pushes == peer
     g = torch.Generator().manual_seed(99)
     losses = []
     for _ in range(3):
@@ -90,6 +113,8 @@ def _train(rank, world, stage, peer):
                 print(f"stage {stage} peer {peer}: micro-step loss {float(loss):.4f}", flush=True)
         rt.step_optimizer()
         losses.append(float(rt.collect_metrics()["loss"]))
+    if stage == 3:
+        plugin.materialize_model()
     params = torch.cat([p.detach().float().reshape(-1) for p in rt.model.parameters()]).cpu()
     norm = rt.state.metadata.get("grad_norm")
     rt.close()
@@ -107,7 +132,7 @@ def _worker(rank, world, port, queue):
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         out = {}
-        for stage in (1, 2):
+        for stage in (1, 2, 3):
             for peer in (False, True):
                 try:
                     out[(stage, peer)] = _train(rank, world, stage, peer)
@@ -147,7 +172,7 @@ def test_zero_peer_memory_mode_matches_nccl_mode_two_gpus():
                 p.kill()
     for rank, (out, status) in got.items():
         assert status[0] == 0, f"rank {rank} kernel status {status}"
-        for stage in (1, 2):
+        for stage in (1, 2, 3):
             (l0, p0, n0), (l1, p1, n1) = out[(stage, False)], out[(stage, True)]
             assert max(abs(a - b) for a, b in zip(l0, l1)) < 2e-2, (stage, l0, l1)
             assert (p0 - p1).abs().max().item() < 2e-2, stage
