@@ -108,6 +108,24 @@ def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
     return getattr(symm, "fused_scatter", True) and x2.dtype == torch.bfloat16 and x2.is_cuda and n_out % 8 == 0
 
 
+def _fused_gather_ok(symm, M: int, N: int, K: int) -> bool:
+    """Whether the all-gather should ride inside the GEMM launch. MALTOS_B200_FUSED_GATHER: "1" always, "0" never, unset =
+    measured rule: in groups larger than four a GEMM of less than ~1.5e11 FLOP is shorter than the push of this rank's
+    rows to seven peers, and NCCL all-gather + GEMM wins (q/k/v at TP=8: 206 vs 416 us; gate/up at TP=8 is a tie, every
+    shape at TP=2 and TP=4 is faster fused)."""
+    mode = os.environ.get("MALTOS_B200_FUSED_GATHER", "auto")
+    if mode in ("0", "1"):
+        return mode == "1"
+    return symm.world <= 4 or 2.0 * M * N * K >= 1.5e11
+
+
+def all_gather_gemm_unfused(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool):
+    """Same contract as :func:`all_gather_gemm` with an NCCL all-gather in front of a plain GEMM launch; ``gathered`` is an
+    ordinary tensor."""
+    x_full = _nccl_all_gather_rows(x2, symm, B, rows)
+    return gemm(x_full, w, b_mn=b_mn), x_full
+
+
 def all_gather_gemm(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool):
     """``(gather_over_ranks(x2) @ op(w), gathered)`` in one launch (see module docstring).
 
@@ -119,6 +137,8 @@ def all_gather_gemm(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, 
     T = symm.world
     K = x2.shape[1]
     N = w.shape[1] if b_mn else w.shape[0]
+    if not _fused_gather_ok(symm, B * rows * T, N, K):
+        return all_gather_gemm_unfused(x2, w, symm, B, rows, b_mn=b_mn)
     if x2.stride(1) != 1 or x2.stride(0) % 8:
         x2 = x2.contiguous()
     if w.stride(1) != 1 or w.stride(0) % 8:
@@ -158,7 +178,9 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         # checkpointing) replaces the all-gather the backward would otherwise launch.
         keep = any(ctx.needs_input_grad[2:]) and os.environ.get("MALTOS_B200_KEEP_GATHERED", "1") == "1"
         ctx.kept = keep
-        ctx.save_for_backward(x2, *weights, *([gathered.clone()] if keep else []))
+        if keep and _fused_gather_ok(symm, B * rows * T, N, K):
+            gathered = gathered.clone()          # the symmetric buffer is recycled two calls later
+        ctx.save_for_backward(x2, *weights, *([gathered] if keep else []))
         ctx.symm, ctx.layout, ctx.fused_ok = symm, layout, order is not None
         ctx.dims = (B, rows, K, N)
         return out.view(B, rows * T, N)

@@ -35,10 +35,12 @@ def _worker(rank, world, port, queue):
             ws = [torch.nn.Parameter((torch.randn(n, K, device="cuda") * 0.05).bfloat16()) for n in outs]
             fuse_parameters(ws)
             g = torch.Generator(device="cuda").manual_seed(100 + rank)
-            for rep in range(4):          # several calls: both buffer parities, the consumed handshake, both push modes
+            for rep in range(6):          # several calls: both buffer parities, the consumed handshake, both push modes
                 from maltos_b200.ops.fused_tp import set_push_mode
 
                 set_push_mode(rep >= 2)
+                # the last two calls take the NCCL all-gather + GEMM route that large groups use for short GEMMs
+                os.environ["MALTOS_B200_FUSED_GATHER"] = "0" if rep >= 4 else "1"
                 x = torch.randn(B, rows, K, device="cuda", generator=g).bfloat16().requires_grad_()
                 y, offs = all_gather_grouped_linear(x, ws, ctx)
                 full = torch.empty(world, B, rows, K, device="cuda", dtype=torch.bfloat16)
@@ -63,6 +65,7 @@ def _worker(rank, world, port, queue):
                 for w in ws:
                     w.grad = None
         set_push_mode(False)
+        os.environ.pop("MALTOS_B200_FUSED_GATHER", None)
         # the NCCL helpers of the non-fused paths keep the batch-major layout for B > 1 without a permuting copy
         from maltos_b200.ops.fused_tp import _nccl_all_gather_rows, _nccl_reduce_scatter_rows
 
