@@ -680,6 +680,17 @@ struct TailWorkspace {
   unsigned* counters;
 };
 constexpr size_t kTailPartialBytes = 74ull * 2 * 128 * 512 * sizeof(float);
+// Number of k slices for the tiles of the last wave (1 = no split): see GemmArgs::tail_split and the cost note in the
+// launcher. `total` tiles on `pairs` CTA pairs, `k_blocks` k-blocks per tile.
+static int tail_slices(int total, int pairs, int k_blocks) {
+  if (!g_tail_split || pairs <= 0) return 1;
+  const int rem = total % pairs;
+  int s = rem > 0 ? pairs / rem : 1;
+  if (s > 4) s = 4;
+  while (s > 1 && k_blocks / s < 8) --s;
+  if (s > 1 && k_blocks * 1080.0 * (1.0 - 1.0 / s) - 70000.0 <= 0.0) s = 1;
+  return s;
+}
 static TailWorkspace g_tail_ws[16];
 static int g_tail_ws_count = 0;
 static std::mutex g_tail_ws_mutex;
@@ -1153,11 +1164,8 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   int split_pairs = 0;
   if (WIDE && !g.enabled && !args.sc.enabled && g_tail_split && args.debug_mode == 0 && args.trace == nullptr) {
     const int rem = total % max_pairs;
-    int s = rem > 0 ? max_pairs / rem : 1;
-    if (s > 4) s = 4;
-    while (s > 1 && args.k_blocks / s < 8) --s;
-    const double gain = args.k_blocks * 1080.0 * (1.0 - 1.0 / (s > 1 ? s : 1)) - 70000.0;
-    TailWorkspace* ws = (s > 1 && gain > 0.0) ? tail_workspace(dev, stream) : nullptr;
+    const int s = tail_slices(total, max_pairs, args.k_blocks);
+    TailWorkspace* ws = s > 1 ? tail_workspace(dev, stream) : nullptr;
     if (ws) {
       args.tail_split = s;
       args.tail_ws = ws->partials;
@@ -1182,7 +1190,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 // wide tiles lose when the problem has too few of them to fill the 74 SM pairs.
 enum GemmKind { kKindSingle128 = 128, kKindSingle256 = 256, kKindPair = 512, kKindWide = 1024 };
 
-static GemmKind choose_gemm_kind(int M, int N, int K) {
+static GemmKind choose_gemm_kind(int M, int N, int K, bool plain = true) {   // plain: no fused collective in the launch
   // Estimated cycles = waves x cycles per tile. Per k-block of 64: 128x128 tiles ~640 cycles, 128x256 tiles ~850 (both
   // shared-memory bound, epilogue overlapped with the next tile's MMAs), 256x512 pair tiles ~1080 (tensor-pipe bound)
   // plus ~5000 cycles of epilogue that cannot overlap because the accumulator fills tensor memory. With few k-blocks
@@ -1198,7 +1206,13 @@ static GemmKind choose_gemm_kind(int M, int N, int K) {
   double best_cost = waves(128, 128, sms) * (kb * 640.0 > 1500.0 ? kb * 640.0 : 1500.0);
   const double c256 = waves(128, 256, sms) * (kb * 850.0 > 3000.0 ? kb * 850.0 : 3000.0);
   if (c256 < best_cost) best = kKindSingle256, best_cost = c256;
-  const double cwide = waves(256, 512, pairs) * (kb * 1080.0 + 5000.0);
+  double cwide = waves(256, 512, pairs) * (kb * 1080.0 + 5000.0);
+  {
+    // with the split tail the last wave costs 1/slices of a main loop plus the partial exchange
+    const int wide_tiles = ((M + 255) / 256) * ((N + 511) / 512);
+    const int s = plain ? tail_slices(wide_tiles, pairs, static_cast<int>(kb)) : 1;
+    if (s > 1) cwide = (wide_tiles / pairs) * (kb * 1080.0 + 5000.0) + kb * 1080.0 / s + 5000.0 + 70000.0;
+  }
   if (cwide < best_cost) best = kKindWide, best_cost = cwide;
   return best;
 }
@@ -1450,7 +1464,7 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
     g.pads[r] = r < world ? pads[r] : 0ull;
   }
   const __nv_bfloat16* a_base = reinterpret_cast<const __nv_bfloat16*>(gathered[rank]) + static_cast<long long>(seq & 1u) * buf_elems;
-  const int kind = choose_gemm_kind(args.M, N, K);
+  const int kind = choose_gemm_kind(args.M, N, K, false);
   const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
   const int bn = wide ? 256 : (pair ? 128 : kind);
   CUtensorMap tmA, tmB;
@@ -1515,7 +1529,7 @@ MB_API int mb_gemm_rs_bf16(const void* X, long long lda, const void* W, int b_mn
     sc.slot_base[r] = r < world ? stage[r] + static_cast<unsigned long long>((buf_off + rank * slot_elems) * 2) : 0ull;
     sc.pads[r] = r < world ? pads[r] : 0ull;
   }
-  int kind = choose_gemm_kind(args.M, N, K);
+  int kind = choose_gemm_kind(args.M, N, K, false);
   if (g_scatter_kind > 0) kind = g_scatter_kind;
   const bool wide = kind == kKindWide, pair = wide || kind == kKindPair;
   const int bn = wide ? 256 : (pair ? 128 : kind);
