@@ -199,6 +199,61 @@ adamw_push_kernel(float* __restrict__ master, const void* __restrict__ grad, int
   }
 }
 
+// In-place all-reduce of flat gradient buckets over peer memory: the owner of a slice reads it from every rank's bucket,
+// sums in fp32 in rank order, scales, and stores the result back into EVERY rank's bucket (16-byte peer loads and
+// stores). Owners' slices are disjoint, so nobody reads what another block writes. One kernel replaces the
+// all-reduce(AVG) of the data-parallel plugins (reference runtime/plugins/ddp.py:20-203); the callers bracket it with
+// stream-ordered group barriers. T = __nv_bfloat16 (8 per 16 bytes) or float (4 per 16 bytes).
+template <typename T>
+__global__ void __launch_bounds__(kZfThreads)
+peer_all_reduce_kernel(PeerDst bufs, int world, long long n, float scale) {
+  constexpr int kPer = 16 / sizeof(T);
+  const long long tid = static_cast<long long>(blockIdx.x) * kZfThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kZfThreads;
+  const long long nvec = n / kPer;
+  for (long long i = tid; i < nvec; i += nthreads) {
+    uint4 raw[kZfMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kZfMaxWorld; ++r)
+      if (r < world) raw[r] = reinterpret_cast<const uint4*>(bufs.p[r])[i];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kZfMaxWorld; ++r)
+      if (r < world) {
+        if constexpr (sizeof(T) == 2) {
+          float f[8];
+          bf16x8_to_float(raw[r], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        } else {
+          const float* f = reinterpret_cast<const float*>(&raw[r]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[j] += f[j];
+        }
+      }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= scale;
+    uint4 o;
+    if constexpr (sizeof(T) == 2) o = float_to_bf16x8(acc);
+    else o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+#pragma unroll
+    for (int r = 0; r < kZfMaxWorld; ++r)
+      if (r < world) reinterpret_cast<uint4*>(bufs.p[r])[i] = o;
+  }
+  for (long long i = nvec * kPer + tid; i < n; i += nthreads) {     // tail of fewer than 16 bytes
+    float a = 0.f;
+    for (int r = 0; r < world; ++r) {
+      if constexpr (sizeof(T) == 2) a += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bufs.p[r])[i]);
+      else a += reinterpret_cast<const float*>(bufs.p[r])[i];
+    }
+    a *= scale;
+    for (int r = 0; r < world; ++r) {
+      if constexpr (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(bufs.p[r])[i] = __float2bfloat16(a);
+      else reinterpret_cast<float*>(bufs.p[r])[i] = a;
+    }
+  }
+}
+
 static int zf_grid(long long n) {
   long long blocks = (n / 8 + kZfThreads - 1) / kZfThreads;
   const long long cap = static_cast<long long>(sm_count()) * 8;
@@ -254,6 +309,31 @@ MB_API int mb_adamw_push(float* master, const void* grad, int grad_bf16, float* 
   else
     adamw_push_kernel<false><<<zf_grid(n), kZfThreads, 0, stream>>>(master, grad, grad_bf16, m, v, n, dst, ndst, lr, beta1, beta2,
                                                                     eps, weight_decay, bias_corr1, bias_corr2_sqrt, grad_scale);
+  count_launch();
+  MB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// bufs[r]: device address of THIS rank's slice (first element) inside rank r's bucket; 16-byte aligned. n elements.
+MB_API int mb_peer_all_reduce(void* const* bufs, int world, long long n, int is_bf16, float scale, cudaStream_t stream) {
+  using namespace mb;
+  if (world < 1 || world > kZfMaxWorld) {
+    set_last_error("mb_peer_all_reduce: needs 1 <= world <= 16");
+    return -1;
+  }
+  if (n <= 0) return 0;
+  PeerDst b{};
+  for (int r = 0; r < world; ++r) {
+    if (!aligned16(bufs[r])) {
+      set_last_error("mb_peer_all_reduce: slices must start on a 16-byte boundary");
+      return -2;
+    }
+    b.p[r] = bufs[r];
+  }
+  if (is_bf16)
+    peer_all_reduce_kernel<__nv_bfloat16><<<zf_grid(n), kZfThreads, 0, stream>>>(b, world, n, scale);
+  else
+    peer_all_reduce_kernel<float><<<zf_grid(n / 2 + 1), kZfThreads, 0, stream>>>(b, world, n, scale);
   count_launch();
   MB_CHECK_CUDA(cudaGetLastError());
   return 0;

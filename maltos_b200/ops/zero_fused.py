@@ -87,3 +87,15 @@ def peer_gather(out: torch.Tensor, src_ptrs, bytes_each: int) -> None:
         raise ValueError("peer_gather: out must be contiguous and hold all pieces")
     _lib.check(_lib.lib().mb_peer_gather(_lib.ptr(out), _ptr_array(src_ptrs), _lib.c_int(len(src_ptrs)), _lib.c_ll(bytes_each),
                                          _lib.stream_ptr()), "mb_peer_gather")
+
+
+def peer_all_reduce(slice_ptrs, numel: int, dtype: torch.dtype, scale: float) -> None:
+    """In-place all-reduce of THIS rank's slice of a flat bucket that every rank keeps in symmetric memory:
+    ``slice_ptrs[r]`` = device address of the slice inside rank r's bucket (16-byte aligned), ``numel`` elements of
+    ``dtype`` (bf16 or fp32). The sum over ranks times ``scale`` is stored back into every rank's bucket
+    (reference ``runtime/plugins/ddp.py:20-203``: ``all_reduce(AVG)``)."""
+    if dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"peer_all_reduce: unsupported dtype {dtype}")
+    _lib.check(_lib.lib().mb_peer_all_reduce(_ptr_array(slice_ptrs), _lib.c_int(len(slice_ptrs)), _lib.c_ll(numel),
+                                             _lib.c_int(int(dtype == torch.bfloat16)), _lib.c_float(scale), _lib.stream_ptr()),
+               "mb_peer_all_reduce")

@@ -71,6 +71,23 @@ def test_peer_gather_concatenates_the_pieces(world, bytes_each):
     assert int(out[world * bytes_each:].sum()) == 0
 
 
+@pytest.mark.parametrize("world,n,dtype", [(2, 8 * 1000 + 5, torch.bfloat16), (4, 1 << 18, torch.bfloat16), (8, 4 * 777 + 3, torch.float32), (16, 4096, torch.float32)])
+def test_peer_all_reduce_writes_the_scaled_sum_into_every_bucket(world, n, dtype):
+    from maltos_b200.ops.zero_fused import peer_all_reduce
+
+    g = torch.Generator(device="cuda").manual_seed(n + world)
+    bufs = [torch.randn(n + 32, device="cuda", generator=g).to(dtype) for _ in range(world)]
+    want = sum(b[:n].float() for b in bufs) * (1.0 / world)
+    tails = [b[n:].clone() for b in bufs]
+    peer_all_reduce([b.data_ptr() for b in bufs], n, dtype, 1.0 / world)
+    torch.cuda.synchronize()
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-6
+    for b, t in zip(bufs, tails):
+        assert (b[:n].float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+        assert torch.equal(b[n:], t)                     # nothing beyond the slice is touched
+    assert all(torch.equal(bufs[0][:n], b[:n]) for b in bufs)
+
+
 # ------------------------------------------------------------------------------------------------ plugin path on 2 GPUs
 def _train(rank, world, stage, peer):
     import torch.distributed as dist
@@ -84,7 +101,11 @@ def _train(rank, world, stage, peer):
 
     torch.manual_seed(4321)
     model = models.TinyTransformer(128, 4, 2, 256, 1e-5, 2, 96, 32)
-    if stage == 3:
+    if stage == 0:
+        from maltos_b200.runtime.plugins import ddp
+
+        plugin = ddp.BucketDataParallelPlugin(bucket_mb_size=1, peer_memory=peer)
+    elif stage == 3:
         import torch.nn as nn
 
         from maltos_b200.models.tiny_transformer import RmsNorm
@@ -96,9 +117,11 @@ def _train(rank, world, stage, peer):
         plugin = cls(bucket_mb_size=1, peer_memory=peer)
     rt = RuntimeCore(model=model, mesh=MeshConfig(dp=world), plan=ParallelPlan(), plugins=[plugin], dtype=torch.bfloat16,
                      device=torch.device("cuda", rank), optimizer_factory=lambda ps: FusedAdamW(ps, lr=1e-2, weight_decay=0.01),
-                     grad_accum_steps=2, grad_clip_max_norm=0.5)
+                     grad_accum_steps=2, grad_clip_max_norm=None if stage == 0 else 0.5)
     rt.setup()
-    if stage == 3:
+    if stage == 0:
+        assert (plugin.buckets[0].peer_ptrs is not None) == peer
+    elif stage == 3:
         assert all((b.peer_shard_ptrs is not None) == peer for b in plugin.buckets)
     else:
         assert (plugin.buckets[0].peer_grad_ptrs is not None) == peer and plugin._pushes == peer
@@ -132,7 +155,7 @@ def _worker(rank, world, port, queue):
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         out = {}
-        for stage in (1, 2, 3):
+        for stage in (0, 1, 2, 3):      # 0 = bucketed data parallel, 1-3 = ZeRO stages
             for peer in (False, True):
                 try:
                     out[(stage, peer)] = _train(rank, world, stage, peer)
@@ -172,10 +195,11 @@ def test_zero_peer_memory_mode_matches_nccl_mode_two_gpus():
                 p.kill()
     for rank, (out, status) in got.items():
         assert status[0] == 0, f"rank {rank} kernel status {status}"
-        for stage in (1, 2, 3):
+        for stage in (0, 1, 2, 3):
             (l0, p0, n0), (l1, p1, n1) = out[(stage, False)], out[(stage, True)]
             assert max(abs(a - b) for a, b in zip(l0, l1)) < 2e-2, (stage, l0, l1)
             assert (p0 - p1).abs().max().item() < 2e-2, stage
-            assert abs(n0 - n1) < 2e-2 * max(1.0, abs(n0)), (stage, n0, n1)
+            if stage:
+                assert abs(n0 - n1) < 2e-2 * max(1.0, abs(n0)), (stage, n0, n1)
     # every rank holds the same parameters after the pushes
     assert torch.equal(got[0][0][(1, True)][1], got[1][0][(1, True)][1])
