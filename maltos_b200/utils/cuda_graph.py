@@ -1,0 +1,69 @@
+"""CUDA-graph capture of a launch-bound micro-step.
+
+Small models (and large ones sharded over many GPUs) spend a micro-step in hundreds of short kernels, and the host
+needs longer to launch them than the device needs to run them. ``GraphedMicroStep`` records the forward and backward
+of one micro-step - this library's kernels are ordinary launches on the current stream, so they are captured like any
+other - and replays the whole recording with one driver call. The reference has no counterpart (its answer to launch
+overhead is ``torch.compile``, ``runtime/plugins/compile.py:11-144``).
+
+Rules of the recording:
+
+* shapes are static: every call must bring tensors of the shapes of the example batch (they are copied into the
+  recording's input buffers);
+* gradients ACCUMULATE: parameters must own a gradient tensor before the capture (missing ones are created as zeros),
+  so the recorded backward adds into them in place; zero them with ``zero_grad(set_to_none=False)`` between steps;
+* the step must not read device values on the host (``.item()``, data-dependent shapes) and must not run collectives
+  whose arguments change from call to call (the fused tensor-parallel kernels carry a call sequence number);
+* activation checkpointing that saves and restores the random-number state cannot be recorded.
+"""
+from __future__ import annotations
+
+from typing import Callable, Mapping
+
+import torch
+
+
+class GraphedMicroStep:
+    def __init__(self, step_fn: Callable[[Mapping[str, torch.Tensor]], torch.Tensor], parameters, example_batch: Mapping[str, torch.Tensor],
+                 *, loss_scale: float = 1.0, warmup: int = 3) -> None:
+        """``step_fn(batch) -> scalar loss`` (forward only; the backward of ``loss * loss_scale`` is recorded here)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("GraphedMicroStep needs a CUDA device")
+        self.step_fn = step_fn
+        self.loss_scale = float(loss_scale)
+        self.params = [p for p in parameters if p.requires_grad]
+        self.static = {k: v.detach().clone() for k, v in example_batch.items() if torch.is_tensor(v)}
+        self.extra = {k: v for k, v in example_batch.items() if not torch.is_tensor(v)}
+        for p in self.params:
+            if p.grad is None:
+                p.grad = torch.zeros_like(p)
+        saved = [p.grad.detach().clone() for p in self.params]
+        # warm-up on a side stream (lazy initialisations, autotuning and workspace allocations happen here, not in the capture)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):
+                self._run()
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._run()
+        # warm-up and capture added to the gradients: restore what the caller had
+        with torch.no_grad():
+            for p, g in zip(self.params, saved):
+                p.grad.copy_(g)
+
+    def _run(self) -> torch.Tensor:
+        loss = self.step_fn({**self.static, **self.extra})
+        (loss * self.loss_scale).backward()
+        return loss.detach()
+
+    def __call__(self, batch: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        """Copies ``batch`` into the recorded inputs, replays forward + backward, returns the (recorded) loss tensor."""
+        for k, dst in self.static.items():
+            src = batch[k]
+            if src.shape != dst.shape or src.dtype != dst.dtype:
+                raise ValueError(f"GraphedMicroStep: '{k}' must keep shape {tuple(dst.shape)} and dtype {dst.dtype}, got {tuple(src.shape)} {src.dtype}")
+            dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        return self.loss
