@@ -10,8 +10,8 @@ Rules of the recording:
 
 * shapes are static: every call must bring tensors of the shapes of the example batch (they are copied into the
   recording's input buffers);
-* gradients ACCUMULATE: parameters must own a gradient tensor before the capture (missing ones are created as zeros),
-  so the recorded backward adds into them in place; zero them with ``zero_grad(set_to_none=False)`` between steps;
+* gradients ACCUMULATE like in eager execution: the recording owns one gradient tensor per parameter (allocated during
+  the capture, overwritten by every replay) and every call adds them to ``param.grad`` with one multi-tensor add;
 * the step must not read device values on the host (``.item()``, data-dependent shapes) and must not run collectives
   whose arguments change from call to call (the fused tensor-parallel kernels carry a call sequence number);
 * activation checkpointing that saves and restores the random-number state cannot be recorded.
@@ -34,24 +34,26 @@ class GraphedMicroStep:
         self.params = [p for p in parameters if p.requires_grad]
         self.static = {k: v.detach().clone() for k, v in example_batch.items() if torch.is_tensor(v)}
         self.extra = {k: v for k, v in example_batch.items() if not torch.is_tensor(v)}
-        for p in self.params:
-            if p.grad is None:
-                p.grad = torch.zeros_like(p)
-        saved = [p.grad.detach().clone() for p in self.params]
+        saved = [p.grad for p in self.params]
         # warm-up on a side stream (lazy initialisations, autotuning and workspace allocations happen here, not in the capture)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(max(1, warmup)):
+                for p in self.params:
+                    p.grad = None
                 self._run()
         torch.cuda.current_stream().wait_stream(side)
+        # gradients are None at capture time: the recorded backward then allocates them from the graph's own memory pool
+        # and every replay rewrites them (no in-place accumulation node runs inside the recording)
+        for p in self.params:
+            p.grad = None
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.loss = self._run()
-        # warm-up and capture added to the gradients: restore what the caller had
-        with torch.no_grad():
-            for p, g in zip(self.params, saved):
-                p.grad.copy_(g)
+        self.recorded = [(p, p.grad) for p in self.params if p.grad is not None]
+        for p, g in zip(self.params, saved):
+            p.grad = g                       # what the caller had before (possibly None)
 
     def _run(self) -> torch.Tensor:
         loss = self.step_fn({**self.static, **self.extra})
@@ -66,4 +68,10 @@ class GraphedMicroStep:
                 raise ValueError(f"GraphedMicroStep: '{k}' must keep shape {tuple(dst.shape)} and dtype {dst.dtype}, got {tuple(src.shape)} {src.dtype}")
             dst.copy_(src, non_blocking=True)
         self.graph.replay()
+        have = [(p.grad, g) for p, g in self.recorded if p.grad is not None]
+        if have:
+            torch._foreach_add_([a for a, _ in have], [g for _, g in have])
+        for p, g in self.recorded:
+            if p.grad is None:
+                p.grad = g.clone()
         return self.loss

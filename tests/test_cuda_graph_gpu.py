@@ -48,7 +48,7 @@ def test_graphed_micro_step_matches_eager_and_accumulates():
     for p in params:
         p.grad = None
     step = GraphedMicroStep(lambda batch: _loss(model, batch), params, b1, loss_scale=0.5)
-    assert all(float(p.grad.abs().max()) == 0.0 for p in params)        # warm-up and capture left no trace
+    assert all(p.grad is None for p in params)                          # warm-up and capture left no trace
     g1 = float(step(b1))
     g2 = float(step(b2))
     torch.cuda.synchronize()
