@@ -14,7 +14,10 @@ Rules of the recording:
   the capture, overwritten by every replay) and every call adds them to ``param.grad`` with one multi-tensor add;
 * the step must not read device values on the host (``.item()``, data-dependent shapes) and must not run collectives
   whose arguments change from call to call (the fused tensor-parallel kernels carry a call sequence number);
-* activation checkpointing that saves and restores the random-number state cannot be recorded.
+* activation checkpointing that saves and restores the random-number state cannot be recorded;
+* no autograd graph of an earlier eager step over the same parameters may still be alive (drop the old loss tensors
+  first): its gradient-accumulation nodes are bound to the stream they ran on, and the capture stream may not make the
+  default stream wait.
 """
 from __future__ import annotations
 

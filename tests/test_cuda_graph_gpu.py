@@ -44,7 +44,8 @@ def test_graphed_micro_step_matches_eager_and_accumulates():
     l2 = _loss(model, b2)
     (l2 * 0.5).backward()
     eager = [p.grad.detach().float().clone() for p in params]
-    eager_losses = (float(l1), float(l2))
+    eager_losses = (l1.item(), l2.item())
+    del l1, l2           # a live eager graph keeps its gradient-accumulation nodes bound to the stream they ran on
     for p in params:
         p.grad = None
     step = GraphedMicroStep(lambda batch: _loss(model, batch), params, b1, loss_scale=0.5)
