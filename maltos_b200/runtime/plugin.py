@@ -44,6 +44,7 @@ class PluginId(str, Enum):
     METRICS = "metrics"
     TORCH_PROFILER = "torch_profiler"
     COMPILE = "compile"
+    CUDA_GRAPH = "cuda_graph"     # not in the reference: micro-step recorded into a CUDA graph
 
 
 @runtime_checkable

@@ -245,6 +245,10 @@ def _build_runtime(args: argparse.Namespace, model: nn.Module, device: torch.dev
         plugins.append(Zero3Plugin(wrap_cls=_zero3_wrap_classes()))
     if args.compile:
         plugins.append(CompilePlugin(scope=args.compile_scope, mode=args.compile_mode))
+    if getattr(args, "cuda_graph", False):
+        from maltos_b200.runtime.plugins.cuda_graph import CudaGraphPlugin
+
+        plugins.append(CudaGraphPlugin())
     if dtype == torch.float16:
         plugins.append(Fp16Plugin())
     if not weights_only and args.grad_clip is not None:

@@ -103,6 +103,7 @@ FLAGS: tuple[Flag, ...] = (
     Flag("compile", BOOL, False, yaml=("compile.enabled",)),
     Flag("compile_scope", str, "mlp", yaml=("compile.scope",)),
     Flag("compile_mode", str, "default", yaml=("compile.mode",)),
+    Flag("cuda_graph", BOOL, False, yaml=("training.cuda_graph",)),   # record the micro-step into a CUDA graph (one process)
     # observability
     Flag("disable_metrics", BOOL, False, yaml=("training.disable_metrics",)),
     Flag("torch_profiler", BOOL, False, yaml=("profiling.torch_profiler",)),

@@ -75,3 +75,38 @@ def test_graphed_micro_step_matches_eager_and_accumulates():
     t_eager, t_graph = timed(eager_step), timed(lambda: step(b1))
     print(f"micro-step wall time: eager {t_eager:.2f} ms, graph replay {t_graph:.2f} ms")
     assert t_graph < t_eager * 1.2
+
+
+def test_cuda_graph_plugin_reproduces_eager_training():
+    """Same model, data and optimizer with and without the plugin: losses agree, and after the eager lead-in every
+    micro-step is a replay."""
+    import maltos_b200  # noqa: F401
+    from maltos_b200.models import LlamaConfig, LlamaForCausalLM
+    from maltos_b200.runtime import RuntimeCore
+    from maltos_b200.runtime.optim import FusedAdamW
+    from maltos_b200.runtime.plugins.cuda_graph import CudaGraphPlugin
+
+    def train(graphed):
+        torch.manual_seed(0)
+        cfg = LlamaConfig(vocab_size=2048, hidden_size=256, intermediate_size=704, num_hidden_layers=2, num_attention_heads=4,
+                          num_key_value_heads=2, max_position_embeddings=128, rms_norm_eps=1e-5)
+        plugin = CudaGraphPlugin(eager_steps=2) if graphed else None
+        rt = RuntimeCore(model=LlamaForCausalLM(cfg), device=torch.device("cuda", 0), dtype=torch.bfloat16, grad_accum_steps=2,
+                         plugins=[plugin] if plugin else [], optimizer_factory=lambda p: FusedAdamW(p, lr=1e-3, betas=(0.9, 0.95)))
+        rt.setup()
+        g = torch.Generator().manual_seed(5)
+        losses = []
+        for _ in range(4):
+            for _ in range(2):
+                ids = torch.randint(0, cfg.vocab_size, (2, 128), generator=g)
+                rt.run_step({"input_ids": ids, "labels": ids.roll(-1, 1)})
+            rt.step_optimizer()
+            losses.append(float(rt.collect_metrics()["loss"]))
+        replays = plugin.runner.replays if plugin else 0
+        rt.close()
+        return losses, replays
+
+    eager, _ = train(False)
+    graphed, replays = train(True)
+    assert replays == 6                                     # 8 micro-steps, the first two eager
+    assert max(abs(a - b) for a, b in zip(eager, graphed)) < 3e-2, (eager, graphed)
