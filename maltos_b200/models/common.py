@@ -84,7 +84,9 @@ def project_out(x: torch.Tensor, module: nn.Module) -> torch.Tensor:
 
 def run_layer(layer: nn.Module, x: torch.Tensor, *, use_checkpoint: bool, **kwargs) -> torch.Tensor:
     if use_checkpoint:
-        return checkpoint(lambda y: layer(y, **kwargs), x, use_reentrant=False, context_fn=activation_checkpoint_context_fn)
+        # no layer of these models draws random numbers (no dropout), so the generator state is neither saved nor restored
+        return checkpoint(lambda y: layer(y, **kwargs), x, use_reentrant=False, preserve_rng_state=False,
+                          context_fn=activation_checkpoint_context_fn)
     return layer(x, **kwargs)
 
 
