@@ -134,6 +134,33 @@ def bench_adamw(args) -> None:
     _report_bw(f"adamw multi-tensor {per * chunks:,} params", per * chunks * (12 + 2 + 12 + 2), ms, _peaks(args.peaks))
 
 
+def bench_shard_paths(args) -> None:
+    """The sharded-optimizer kernels with the ranks' buffers emulated as tensors of THIS GPU: what the kernels cost in
+    HBM traffic when NVLink is not the limit (the peers' buffers are ordinary device addresses to them)."""
+    from maltos_b200.ops.zero_fused import adamw_push, peer_all_reduce, peer_gather, peer_reduce_shard
+
+    world, n = args.world, args.numel // args.world * args.world
+    shard = n // world
+    peaks = _peaks(args.peaks)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    buckets = [torch.randn(shard, device="cuda").bfloat16() for _ in range(world)]      # this rank's slice in every rank's bucket
+    out = torch.empty(shard, device="cuda", dtype=torch.bfloat16)
+    sq = torch.zeros((), dtype=torch.float64, device="cuda")
+    ptrs = [b.data_ptr() for b in buckets]
+    ms = _time(lambda: peer_reduce_shard(ptrs, 0, shard, 1.0 / world, out, sumsq=sq), args.iters, flush=flush)
+    _report_bw(f"peer_reduce_shard world={world} shard={shard:,} bf16", shard * 2 * (world + 1), ms, peaks)
+    ms = _time(lambda: peer_all_reduce(ptrs, shard, torch.bfloat16, 1.0 / world), args.iters, flush=flush)
+    _report_bw(f"peer_all_reduce world={world} slice={shard:,} bf16", shard * 2 * 2 * world, ms, peaks)
+    master = torch.randn(shard, device="cuda")
+    m1, m2 = torch.zeros_like(master), torch.zeros_like(master)
+    ms = _time(lambda: adamw_push(master, out, m1, m2, ptrs, step=1.0, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1),
+               args.iters, flush=flush)
+    _report_bw(f"adamw_push world={world} shard={shard:,}", shard * (12 + 2 + 12 + 2 * world), ms, peaks)
+    full = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: peer_gather(full, ptrs, shard * 2), args.iters, flush=flush)
+    _report_bw(f"peer_gather world={world} total={n:,} bf16", n * 2 * 2, ms, peaks)
+
+
 def bench_attention(args) -> None:
     from maltos_b200.ops import _lib
     from maltos_b200.ops.flash_attn import _sdpa_cudnn, flash_forward
@@ -184,10 +211,14 @@ def main(argv=None) -> None:
     t.add_argument("--causal", action=argparse.BooleanOptionalAction, default=True)
     a = sub.add_parser("adamw")
     a.add_argument("--numel", type=int, default=500_000_000)
+    z = sub.add_parser("shard-paths")
+    z.add_argument("--numel", type=int, default=400_000_000, help="elements of the whole bucket")
+    z.add_argument("--world", type=int, default=8)
     args = p.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")
-    {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "attention": bench_attention}[args.what](args)
+    {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "adamw": bench_adamw, "attention": bench_attention,
+     "shard-paths": bench_shard_paths}[args.what](args)
 
 
 if __name__ == "__main__":
