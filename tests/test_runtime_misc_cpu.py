@@ -2,6 +2,7 @@
 import json
 
 import numpy as np
+import pytest
 import torch
 
 from maltos_b200.data.sft import PackedSFTDataset, SFTDataLoader
@@ -93,3 +94,27 @@ def test_metric_reduction_rules_across_ranks():
         assert out["memory/max_allocated_gb"] == 4.0   # max over ranks
         assert bool(out["fp16/overflow"]) is True      # any
     assert results[0][0].keys() == results[1][0].keys()
+
+
+def test_cuda_graph_plugin_refuses_communicating_plugins():
+    """The recorded micro-step cannot contain collectives: the plugin must say so at bind time, not fail in a capture."""
+    import maltos_b200  # noqa: F401
+    from maltos_b200 import models
+    from maltos_b200.runtime import RuntimeCore
+    from maltos_b200.runtime.plugins.cuda_graph import CudaGraphPlugin
+    from maltos_b200.runtime.plugins.grad_clip import GradClipPlugin
+    from maltos_b200.runtime.plugins.zero1 import Zero1Plugin
+
+    def model():
+        return models.TinyTransformer(32, 2, 2, 64, 1e-5, 1, 64, 16)
+
+    opt = lambda ps: torch.optim.AdamW(ps, lr=1e-3)   # noqa: E731
+    rt = RuntimeCore(model=model(), plugins=[CudaGraphPlugin(), GradClipPlugin(1.0)], optimizer_factory=opt)
+    rt.setup()                                        # local plugins are fine; on CPU batches simply run eagerly
+    ids = torch.randint(0, 64, (2, 16))
+    rt.run_step({"input_ids": ids, "labels": ids.roll(-1, 1)})
+    rt.step_optimizer()
+    assert rt.collect_metrics()["cuda_graph/replays"] == 0.0
+    rt.close()
+    with pytest.raises(ValueError, match="single-process"):
+        RuntimeCore(model=model(), plugins=[CudaGraphPlugin(), Zero1Plugin()], optimizer_factory=opt).setup()
