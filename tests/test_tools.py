@@ -59,3 +59,18 @@ def test_upload_plan_validation(tmp_path):
     plan = plan_uploads(root, [2, 4], "p", ["best"])
     assert [i["name"] for i in plan] == ["p-step-00000002", "p-step-00000004"]
     assert plan[0]["aliases"] == ["best", "step_2"] and plan[1]["aliases"] == ["best", "step_4", "latest"]
+
+
+def test_bench_micro_batch_defaults():
+    """The benchmark's micro-batch default: 2 for this framework on one GPU, 1 everywhere else; explicit values win."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("bench_module", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.parse_args([]).micro_batch == 2
+    assert bench.parse_args(["--gpus", "4"]).micro_batch == 1
+    assert bench.parse_args(["--impl", "reference"]).micro_batch == 1
+    assert bench.parse_args(["--small"]).micro_batch == 1
+    assert bench.parse_args(["--micro-batch", "4"]).micro_batch == 4
