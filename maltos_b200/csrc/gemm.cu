@@ -263,6 +263,16 @@ __device__ void gather_push_role_bulk(const GatherArgs& g, int K, int* status, i
   }
 }
 
+// The push as a launch of its own (same stream, in front of the GEMM launch): 256-thread blocks doing nothing but the
+// row copies reach the NVLink rate of a plain copy kernel (~680 GB/s measured with 64 blocks), which the push warps
+// inside a GEMM block do not (~190 GB/s: they share the SM with spinning producer / MMA / epilogue warps). The GEMM
+// launch that follows only waits for the peers' flags.
+constexpr int kPushKernelThreads = 256;
+__global__ void __launch_bounds__(kPushKernelThreads)
+ag_push_kernel(const __grid_constant__ GatherArgs g, int K, int* status) {
+  gather_push_role(g, K, status, static_cast<int>(gridDim.x), 0);
+}
+
 // First M block a rank visits: with a fused all-gather its own rows (already local), with a fused reduce-scatter the
 // rows of the next rank (remote partials leave first, the rank's own rows need no transfer and come last).
 __device__ __forceinline__ int tile_rotation(const GatherArgs& g, const ScatterArgs& sc, int tile_m) {
@@ -666,6 +676,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // tfull[a] exist in both CTAs and are signalled by one commit addressed to both; tempty[a] lives in the leader and
 // collects the epilogue warps of both CTAs.
 static int g_debug_max_pairs = 0;   // debug cap on the number of CTA pairs (0 = all)
+static int g_push_split = [] {       // 1: the all-gather push runs as its own launch in front of the GEMM
+  const char* e = getenv("MALTOS_B200_PUSH_SPLIT");
+  return e ? atoi(e) : 0;
+}();
 static int g_tail_split = [] {
   const char* e = getenv("MALTOS_B200_GEMM_TAIL_SPLIT");
   return e ? atoi(e) : 1;
@@ -1331,6 +1345,7 @@ MB_API void mb_gemm_set_tail_split(int on) { mb::g_tail_split = on ? 1 : 0; }
 MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
 MB_API void mb_gemm_set_push_bulk(int on) { mb::g_push_bulk = on ? 1 : 0; }
+MB_API void mb_gemm_set_push_split(int on) { mb::g_push_split = on ? 1 : 0; }
 // Debug: cap the number of CTA pairs of the pair kernel (0 = one pair per two SMs).
 MB_API void mb_gemm_set_debug_max_pairs(int pairs) { mb::g_debug_max_pairs = pairs; }
 
@@ -1472,6 +1487,16 @@ MB_API int mb_ag_gemm_bf16(const void* x_local, long long x_ld, int batches, int
   if (!(b_mn ? encode_tmap_2d(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBK, 2, true)
              : encode_tmap_2d(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, (uint32_t)bn, 2, true)))
     return -5;
+  if (g_push_split) {
+    const long long rows_local = static_cast<long long>(batches) * rows_per_chunk;
+    long long blocks = (rows_local + 3) / 4;
+    if (blocks > 128) blocks = 128;
+    ag_push_kernel<<<static_cast<unsigned>(blocks < 1 ? 1 : blocks), kPushKernelThreads, 0, stream>>>(g, K, status);
+    count_launch();
+    MB_CHECK_CUDA(cudaGetLastError());
+    g.push_ctas = 0;      // the GEMM launch below has no push warps: it only waits for the flags
+    g.bulk = 0;
+  }
   if (wide) return launch_gemm_pair<true>(tmA, tmB, args, stream, &g);
   if (pair) return launch_gemm_pair<false>(tmA, tmB, args, stream, &g);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, args, stream, &g);

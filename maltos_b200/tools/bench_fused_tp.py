@@ -77,11 +77,14 @@ def main(argv=None) -> None:
             w = torch.nn.Parameter((torch.randn(n, H, device="cuda") * 0.02).bfloat16())
             x = torch.randn(1, rows, H, device="cuda").bfloat16()
             fused = _time(lambda: all_gather_grouped_linear(x, [w], ctx), args.iters)
+            _lib.lib().mb_gemm_set_push_split(1)
+            split = _time(lambda: all_gather_grouped_linear(x, [w], ctx), args.iters)
+            _lib.lib().mb_gemm_set_push_split(0)
             nccl = _time(lambda: gemm(_nccl_all_gather_rows(x.view(-1, H), ctx, 1, rows), w), args.iters)
             xf = _nccl_all_gather_rows(x.view(-1, H), ctx, 1, rows)
             alone = _time(lambda: gemm(xf, w), args.iters)
             report(f"all-gather -> GEMM {name} N={n}", 2.0 * S * H * n, (world - 1) * rows * H * 2,
-                   {"fused": fused, "NCCL all-gather + GEMM": nccl, "GEMM alone": alone})
+                   {"fused": fused, "push launch + GEMM": split, "NCCL all-gather + GEMM": nccl, "GEMM alone": alone})
         for name, k_full in (("o_proj", H), ("down", args.ffn)):
             k = k_full // world
             w = torch.nn.Parameter((torch.randn(H, k, device="cuda") * 0.02).bfloat16())

@@ -35,12 +35,14 @@ def _worker(rank, world, port, queue):
             ws = [torch.nn.Parameter((torch.randn(n, K, device="cuda") * 0.05).bfloat16()) for n in outs]
             fuse_parameters(ws)
             g = torch.Generator(device="cuda").manual_seed(100 + rank)
-            for rep in range(6):          # several calls: both buffer parities, the consumed handshake, both push modes
+            for rep in range(8):          # several calls: both buffer parities, the consumed handshake, all push modes
                 from maltos_b200.ops.fused_tp import set_push_mode
 
                 set_push_mode(rep >= 2)
                 # the last two calls take the NCCL all-gather + GEMM route that large groups use for short GEMMs
-                os.environ["MALTOS_B200_FUSED_GATHER"] = "0" if rep >= 4 else "1"
+                os.environ["MALTOS_B200_FUSED_GATHER"] = "0" if rep in (4, 5) else "1"
+                # calls 6 and 7: the push as a launch of its own in front of the GEMM launch
+                _lib.lib().mb_gemm_set_push_split(1 if rep >= 6 else 0)
                 x = torch.randn(B, rows, K, device="cuda", generator=g).bfloat16().requires_grad_()
                 y, offs = all_gather_grouped_linear(x, ws, ctx)
                 full = torch.empty(world, B, rows, K, device="cuda", dtype=torch.bfloat16)
@@ -65,6 +67,7 @@ def _worker(rank, world, port, queue):
                 for w in ws:
                     w.grad = None
         set_push_mode(False)
+        _lib.lib().mb_gemm_set_push_split(0)
         os.environ.pop("MALTOS_B200_FUSED_GATHER", None)
         # the NCCL helpers of the non-fused paths keep the batch-major layout for B > 1 without a permuting copy
         from maltos_b200.ops.fused_tp import _nccl_all_gather_rows, _nccl_reduce_scatter_rows
