@@ -41,8 +41,8 @@ def parse_args(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--micro-batch", type=int, default=None,
-                    help="sequences per micro-step (global batch stays 32). Default: 2 on one GPU for this framework (127 GiB peak; "
-                         "16384-row GEMMs fill whole waves of 256x512 tiles: 16.0 k against 14.6-15.0 k tokens/s), otherwise 1")
+                    help="sequences per micro-step (global batch stays 32). Default for BOTH arms: 2 on one GPU, falling back to 1 "
+                         "when the first warm-up step runs out of device memory; 1 on several GPUs")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
     ap.add_argument("--small", action="store_true", help="tiny model/sequence: plumbing check only, NOT a benchmark number")
     ap.add_argument("--device", default=None, help="override device (cpu allowed only with --small)")
@@ -50,9 +50,25 @@ def parse_args(argv=None):
     ap.add_argument("--kernel-table", default=None, help="debugging: write rank 0's per-kernel device-time table of one extra step to this file")
     ap.add_argument("--layers", type=int, default=None, help="debugging only: fewer layers (the JSON line is then marked invalid)")
     args = ap.parse_args(argv)
+    args.micro_batch_auto = args.micro_batch is None
     if args.micro_batch is None:
-        args.micro_batch = 2 if (args.impl == "ours" and args.gpus == 1 and not args.small) else 1
+        args.micro_batch = 2 if (args.gpus == 1 and not args.small) else 1
     return args
+
+
+MICRO_BATCH_POLICY = "same for both arms: 2 on one GPU, 1 after an out-of-memory error in the first warm-up step; 1 on several GPUs"
+
+
+def retry_with_micro_batch_one(args) -> None:
+    """The automatically chosen micro-batch of 2 did not fit: start over with 1 in a fresh process image (single-process
+    runs only), so that nothing of the failed attempt stays allocated."""
+    import torch
+
+    torch.cuda.empty_cache()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    argv = [a for a in sys.argv[1:]]
+    os.execv(sys.executable, [sys.executable, str(Path(__file__).resolve()), *argv, "--micro-batch", "1"])
 
 
 # ---------------------------------------------------------------------------------------------- clocks
@@ -162,17 +178,23 @@ def barrier_sync(device) -> None:
         torch.cuda.synchronize(device)
 
 
-class HostBatches:
-    """Deterministic uniform token batches in pinned host memory (one fresh tensor pair per micro-step)."""
+POOL_STEPS = 8
 
-    def __init__(self, micro_batch: int, seq_len: int, vocab: int, seed: int, pin: bool, pool: int = 4) -> None:
+
+class HostBatches:
+    """Deterministic uniform token ids in pinned host memory: ``POOL_STEPS`` optimizer steps' worth of DISTINCT sequences
+    (``POOL_STEPS * global_batch`` rows), cut into micro-batches in row order, so both arms see the same sequences in the
+    same order whatever their micro-batch; after ``POOL_STEPS`` steps the pool repeats."""
+
+    def __init__(self, micro_batch: int, seq_len: int, vocab: int, seed: int, pin: bool, global_batch: int) -> None:
         import torch
 
         g = torch.Generator().manual_seed(seed)
+        rows = POOL_STEPS * global_batch
+        toks = torch.randint(0, vocab, (rows, seq_len + 1), generator=g, dtype=torch.long)
         self.items = []
-        for _ in range(pool):
-            toks = torch.randint(0, vocab, (micro_batch, seq_len + 1), generator=g, dtype=torch.long)
-            ids, labels = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
+        for r in range(0, rows, micro_batch):
+            ids, labels = toks[r:r + micro_batch, :-1].contiguous(), toks[r:r + micro_batch, 1:].contiguous()
             if pin:
                 ids, labels = ids.pin_memory(), labels.pin_memory()
             self.items.append({"input_ids": ids, "labels": labels})
@@ -183,6 +205,10 @@ class HostBatches:
         item = self.items[self.i % len(self.items)]
         self.i += 1
         return item
+
+
+DATA_NOTE = (f"synthetic uniform token ids, {POOL_STEPS} steps x global batch of distinct sequences (seed 0, same rows for both "
+             "arms), repeating after that")
 
 
 def emit(payload: dict) -> None:
@@ -255,12 +281,17 @@ def run_ours(args) -> None:
 
     seq = m["seq_len"]
     tokens_per_step = args.global_batch * seq
-    host = HostBatches(micro, seq, m["vocab"], seed=0, pin=use_cuda)
+    host = HostBatches(micro, seq, m["vocab"], seed=0, pin=use_cuda, global_batch=args.global_batch)
     dev_batches = [{k: v.to(device) for k, v in item.items()} for item in host.items]
+    dev_cursor = [0]
 
     def one_step(source, read_loss: bool):
         for i in range(accum):
-            batch = source.next_batch() if hasattr(source, "next_batch") else source[i % len(source)]
+            if hasattr(source, "next_batch"):
+                batch = source.next_batch()
+            else:
+                batch = source[dev_cursor[0] % len(source)]
+                dev_cursor[0] += 1
             loss, should = runtime.run_step(batch)
         assert should, "accumulation window did not close"
         runtime.step_optimizer()
@@ -268,8 +299,18 @@ def run_ours(args) -> None:
             return float(runtime.collect_metrics()["loss"])
         return None
 
-    for _ in range(args.warmup):
-        one_step(dev_batches, read_loss=False)
+    oom = False
+    for w in range(args.warmup):
+        try:
+            one_step(dev_batches, read_loss=False)
+        except torch.OutOfMemoryError:
+            if not (w == 0 and args.micro_batch_auto and micro > 1 and world == 1):
+                raise
+            oom = True
+            break
+    if oom:
+        del runtime, model, dev_batches
+        retry_with_micro_batch_one(args)
     barrier_sync(device)
 
     if args.kernel_table and use_cuda:
@@ -326,11 +367,12 @@ def run_ours(args) -> None:
             "metric": "LLaMA-8B train tokens/sec (max over ranks)" if not (args.small or args.layers) else "REDUCED MODEL plumbing check (not a benchmark)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16" if use_cuda else "fp32", "data": "synthetic uniform token ids, random-init weights",
+            "dtype": "bf16" if use_cuda else "fp32", "data": DATA_NOTE + "; random-init weights",
             "impl": "ours",
             "config": {"model": "llama3-8b" if not args.small else "small", "layers": m["layers"], "hidden": m["hidden"],
                        "ffn": m["ffn"], "heads": m["heads"], "kv_heads": m["kv_heads"], "vocab": m["vocab"],
                        "global_batch": args.global_batch, "seq_len": seq, "micro_batch": micro, "grad_accum": accum,
+                       "micro_batch_policy": MICRO_BATCH_POLICY,
                        "parallelism": f"tp{tp}+sp" if tp > 1 else "single-gpu", "activation_checkpointing": "per layer",
                        "optimizer": "fused AdamW, fp32 master weights",
                        "l2_policy": "working set (16 GB of bf16 weights + activations per micro-step) is far larger than the 126 MB L2; no explicit flush",
@@ -393,18 +435,33 @@ def run_reference(args) -> None:
 
         seq = m["seq_len"]
         tokens_per_step = args.global_batch * seq
-        host = HostBatches(micro, seq, m["vocab"], seed=0, pin=use_cuda)
+        host = HostBatches(micro, seq, m["vocab"], seed=0, pin=use_cuda, global_batch=args.global_batch)
         dev_batches = [{k: v.to(device) for k, v in item.items()} for item in host.items]
+        dev_cursor = [0]
 
         def one_step(source, read_loss):
             for i in range(accum):
-                batch = source.next_batch() if hasattr(source, "next_batch") else source[i % len(source)]
+                if hasattr(source, "next_batch"):
+                    batch = source.next_batch()
+                else:
+                    batch = source[dev_cursor[0] % len(source)]
+                    dev_cursor[0] += 1
                 loss, should = core.run_step(batch)
             core.step_optimizer()
             return float(loss.detach().float().item()) if read_loss else None
 
-        for _ in range(args.warmup):
-            one_step(dev_batches, False)
+        oom = False
+        for w in range(args.warmup):
+            try:
+                one_step(dev_batches, False)
+            except torch.OutOfMemoryError:
+                if not (w == 0 and args.micro_batch_auto and micro > 1 and world == 1):
+                    raise
+                oom = True
+                break
+        if oom:
+            del core, model, dev_batches
+            retry_with_micro_batch_one(args)
         barrier_sync(device)
         sampler = ClockSampler(device.index if use_cuda else 0)
         sampler.start()
@@ -439,9 +496,9 @@ def run_reference(args) -> None:
                   "value": tokens_per_step / (ms_per_step / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                   "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                   "vs_baseline": None, "dtype": "bf16" if use_cuda else "fp32",
-                  "data": "synthetic uniform token ids, reference default init", "impl": "reference",
+                  "data": DATA_NOTE + "; reference default init", "impl": "reference",
                   "config": {"model": "llama3-8b" if not args.small else "small", "global_batch": args.global_batch,
-                             "seq_len": seq, "micro_batch": micro, "grad_accum": accum,
+                             "seq_len": seq, "micro_batch": micro, "grad_accum": accum, "micro_batch_policy": MICRO_BATCH_POLICY,
                              "parallelism": f"tp{tp}+sp" if tp > 1 else "single-gpu", "attention_backend": ref_args.attention_backend,
                              "zero_stage": 0, "note": "reference CLI rejects ZeRO-1 with dp=1 and has no rope_theta flag"},
                   "clocks": clocks, "e2e": e2e, "gpu_launches": 0})

@@ -4,7 +4,9 @@
 // (so partial results of ring attention can be merged). Visibility rules:
 //   mode 0  every key is visible (blocks below the diagonal of ring attention);
 //   mode 1  causal with offset: key j visible to query i  <=>  j <= i + (Sk - Sq);
-//   mode 2  general: k_pos[j] <= q_pos[i] and k_seq[j] == q_seq[i] and k_seq[j] != -1 (packed documents, zigzag blocks).
+//   mode 2  general: k_pos[j] <= q_pos[i] and k_seq[j] == q_seq[i] and k_seq[j] != -1 (packed documents, zigzag blocks);
+//   mode 3  causal by index (as mode 1, so key blocks above the diagonal are skipped) and k_seq[j] == q_seq[i] != -1:
+//           packed documents inside one row.
 // One CTA handles 128 query rows of one (batch, head): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = softmax,
 // rescale and output (two threads per query row, each owning half of the key columns). The reference gets this op from the flash-attn 2 package (utils/attention_backend.py:42-135).
 #include "host.h"
@@ -80,7 +82,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   // number of key blocks this tile has to look at
   int n_blocks = (p.Sk + kFaBN - 1) / kFaBN;
-  if (p.mode == 1) {
+  if (p.mode == 1 || p.mode == 3) {
     const int last_key = min(q0 + kFaBM - 1, p.Sq - 1) + causal_off;      // last key visible to the tile's last row
     n_blocks = last_key < 0 ? 0 : min(n_blocks, last_key / kFaBN + 1);
   }
@@ -187,7 +189,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool row_valid = qi < p.Sq;
     const uint32_t t_lane = static_cast<uint32_t>(qw * 32) << 16;
     const int my_pos = (p.mode == 2 && row_valid) ? p.q_pos[static_cast<long long>(batch) * p.Sq + qi] : 0;
-    const int my_seq = (p.mode == 2 && row_valid && p.q_seq) ? p.q_seq[static_cast<long long>(batch) * p.Sq + qi] : 0;
+    const int my_seq = (p.mode >= 2 && row_valid && p.q_seq) ? p.q_seq[static_cast<long long>(batch) * p.Sq + qi] : 0;
     // Pairwise exchange between the two threads of a row through shared memory: value, then a monotonically increasing
     // tag; the reader polls the partner's tag with the usual bound (no block-wide barrier, so an aborting warp cannot
     // strand the others).
@@ -224,14 +226,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int key0 = j * kFaBN + half * HALF_N;  // first key of this thread's columns
       bool need_mask = j * kFaBN + kFaBN > p.Sk;
       if (p.mode == 1) need_mask = need_mask || (j * kFaBN + kFaBN - 1 > q0 + causal_off);
-      if (p.mode == 2) need_mask = true;
+      if (p.mode >= 2) need_mask = true;
       auto visible = [&](int c) -> bool {          // c = column inside this thread's half
         const int kj = key0 + c;
         if (kj >= p.Sk) return false;
         if (p.mode == 1) return kj <= qi + causal_off;
-        if (p.mode == 2) {
+        if (p.mode == 3 && kj > qi + causal_off) return false;
+        if (p.mode >= 2) {
           const long long at = static_cast<long long>(batch) * p.Sk + kj;
-          if (p.k_pos[at] > my_pos) return false;
+          if (p.mode == 2 && p.k_pos[at] > my_pos) return false;
           if (p.k_seq) {
             const int ks = p.k_seq[at];
             if (ks == -1 || ks != my_seq) return false;
@@ -403,7 +406,8 @@ MB_API int mb_flash_attn_fwd(const void* q, long long q_tstride, long long q_bst
     set_last_error("mb_flash_attn_fwd: head_dim must be 64 or 128, query heads a multiple of key/value heads");
     return -1;
   }
-  if (mode < 0 || mode > 2 || (mode == 2 && (!q_pos || !k_pos)) || ((q_seq == nullptr) != (k_seq == nullptr))) {
+  if (mode < 0 || mode > 3 || (mode == 2 && (!q_pos || !k_pos)) || ((q_seq == nullptr) != (k_seq == nullptr)) ||
+      (mode == 3 && !q_seq)) {
     set_last_error("mb_flash_attn_fwd: bad mask mode or missing position / sequence-id arrays");
     return -2;
   }

@@ -60,33 +60,32 @@ def _kernel_eligible(q, k, v) -> bool:
 
 
 def attention(q, k, v, *, q_positions=None, k_positions=None, q_sequence_ids=None, k_sequence_ids=None,
-              causal: bool = True, scale: float | None = None, return_lse: bool = False):
-    """General masked attention (see module docstring). Differentiable."""
+              causal: bool = True, scale: float | None = None, return_lse: bool = False, packed_causal: bool = False):
+    """General masked attention (see module docstring). Differentiable. ``packed_causal``: causality follows the index
+    inside the row (positions are ignored) and documents are separated by their sequence ids."""
     if _kernel_eligible(q, k, v):
         from .flash_attn import flash_attention
 
         return flash_attention(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
-                               k_sequence_ids=k_sequence_ids, causal=causal, scale=scale, return_lse=return_lse)
+                               k_sequence_ids=k_sequence_ids, causal=causal, scale=scale, return_lse=return_lse,
+                               packed_causal=packed_causal)
+    if packed_causal or (q_positions is None and q_sequence_ids is not None):
+        B, Sq, Sk = q.shape[0], q.shape[1], k.shape[1]
+        q_positions = torch.arange(Sk - Sq, Sk, device=q.device).unsqueeze(0).expand(B, Sq)
+        k_positions = torch.arange(Sk, device=q.device).unsqueeze(0).expand(B, Sk)
     return attention_reference(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
                                k_sequence_ids=k_sequence_ids, causal=causal, scale=scale, return_lse=return_lse)
 
 
 def causal_attention(q, k, v, *, position_ids=None, sequence_ids=None, scale: float | None = None):
-    """Self-attention over one local sequence: causal, and document-local when ``sequence_ids`` is given."""
+    """Self-attention over one local sequence: causal, and document-local when ``sequence_ids`` is given.
+
+    Inside a packed row positions restart per document, so the row index decides causality and the document id the block
+    structure; on the GPU that is ONE launch of the flash kernel over the padded rows (no compaction, no host sync)."""
     if sequence_ids is None:
         return attention(q, k, v, causal=True, scale=scale)
-    B, S = q.shape[:2]
-    if scale is None and _kernel_eligible(q, k, v):
-        # packed rows on the GPU: compact the valid tokens and run ONE variable-length fused attention over all documents
-        from maltos_b200.runtime.layers.flash_utils import flash_attn_fallback_reason, flash_attn_varlen
-
-        if flash_attn_fallback_reason(q) is None:
-            return flash_attn_varlen(q, k, v, sequence_ids)
-    # inside a packed row, positions restart per document; visibility needs an order that is monotone in the row,
-    # so the row index is used for causality and the document id for the block structure
-    order = torch.arange(S, device=q.device).unsqueeze(0).expand(B, S)
-    return attention(q, k, v, q_positions=order, k_positions=order, q_sequence_ids=sequence_ids, k_sequence_ids=sequence_ids,
-                     causal=True, scale=scale)
+    return attention(q, k, v, q_sequence_ids=sequence_ids, k_sequence_ids=sequence_ids, causal=True, scale=scale,
+                     packed_causal=True)
 
 
 # ------------------------------------------------------------------------------------------------ block primitives

@@ -1,12 +1,11 @@
 """Variable-length (packed-document) attention helpers in the ``[B, S, heads, D]`` layout.
 
 Packed rows hold several documents back to back plus tail padding; attention must stay inside a document. This module
-turns per-token ``sequence_ids`` into the flat layout that varlen attention kernels take (valid tokens compacted,
-``cu_seqlens`` boundaries), runs one varlen call for the whole batch, and scatters the result back. The layout depends
-only on ``sequence_ids``, so it is computed once per micro-batch and reused by every layer and by activation-checkpoint
-recomputation. Also the dense with-LSE block forward/backward used by ring attention. The import-guarded access to the
-flash-attn package mirrors the reference's ``runtime/layers/flash_utils.py:87-135,356-563``; where that package is
-missing everything falls back to the library's masked attention (same results).
+runs it as ONE launch of this library's flash kernel over the padded rows (mask rule "causal by row index and same
+sequence id": no compaction, no ``cu_seqlens``, no device->host read), and also offers the flat layout helpers
+(valid tokens compacted, ``cu_seqlens`` boundaries) that callers of the reference's interface expect. Also the dense
+with-LSE block forward/backward used by ring attention. The reference reaches the same results through the flash-attn
+package (``runtime/layers/flash_utils.py:87-135,356-563``); that package is not used here.
 """
 from __future__ import annotations
 
@@ -17,14 +16,6 @@ import torch
 from maltos_b200.ops.attention import attention, attention_block_backward, attention_block_forward
 from maltos_b200.utils.constants import PAD_SEQUENCE_ID
 
-try:   # optional dependency
-    from flash_attn import flash_attn_func as _flash_attn_func
-    from flash_attn import flash_attn_varlen_func as _flash_attn_varlen_func
-
-    _FLASH_ATTN_IMPORT_ERROR: Exception | None = None
-except Exception as exc:  # noqa: BLE001 - any import-time failure means "not available"
-    _flash_attn_func = _flash_attn_varlen_func = None
-    _FLASH_ATTN_IMPORT_ERROR = exc
 
 
 @dataclass(frozen=True)
@@ -57,22 +48,22 @@ class FlashAttnBlockOutput:
 
 # ------------------------------------------------------------------------------------------------ availability
 def flash_attn_import_error() -> Exception | None:
-    return _FLASH_ATTN_IMPORT_ERROR
+    """Kept for callers of the reference's interface: the kernels are part of this library, nothing is imported."""
+    return None
 
 
 def flash_attn_is_available() -> bool:
-    return _flash_attn_func is not None and _flash_attn_varlen_func is not None
+    return True
 
 
 def flash_attn_fallback_reason(q: torch.Tensor) -> str | None:
-    """None when the flash-attn package can take ``q``; otherwise why not."""
-    if not flash_attn_is_available():
-        err = flash_attn_import_error()
-        return "flash-attn package is unavailable" + ("" if err is None else f": {type(err).__name__}: {err}")
+    """None when the tcgen05 flash kernels take ``q``; otherwise why the fp32 restatement runs instead."""
     if not q.is_cuda:
-        return "flash-attn requires CUDA tensors"
-    if q.dtype not in (torch.float16, torch.bfloat16):
-        return f"flash-attn requires fp16/bf16 tensors, got {q.dtype}"
+        return "the flash kernels require CUDA tensors"
+    if q.dtype != torch.bfloat16:
+        return f"the flash kernels require bf16 tensors, got {q.dtype}"
+    if q.shape[-1] not in (64, 128):
+        return f"the flash kernels cover head_dim 64 and 128, got {q.shape[-1]}"
     return None
 
 
@@ -135,41 +126,26 @@ def unpack_varlen_output(out: torch.Tensor, token_mask: torch.Tensor) -> torch.T
                                            seq_len=token_mask.shape[1])
 
 
-def _varlen_call(q, k, v, cu_seqlens, max_seqlen):
-    return _flash_attn_varlen_func(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, dropout_p=0.0, causal=True)
-
-
 def flash_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sequence_ids: torch.Tensor) -> torch.Tensor:
     """Causal attention inside every document of a packed ``[B, S, h, D]`` batch; padding rows come back as zeros."""
-    if flash_attn_fallback_reason(q) is not None:
-        order = torch.arange(q.shape[1], device=q.device).unsqueeze(0).expand(q.shape[0], -1)
-        out = attention(q, k, v, q_positions=order, k_positions=order, q_sequence_ids=sequence_ids, k_sequence_ids=sequence_ids)
-        return out * (sequence_ids != PAD_SEQUENCE_ID).unsqueeze(-1).unsqueeze(-1).to(out.dtype)
-    packed = pack_varlen_qkv(q, k, v, sequence_ids)
-    if packed.max_seqlen == 0:
-        return q.new_zeros(q.shape)
-    out = _varlen_call(packed.q, packed.k, packed.v, packed.cu_seqlens, packed.max_seqlen)
-    return unpack_varlen_output_by_indices(out, packed.flat_indices, batch_size=q.shape[0], seq_len=q.shape[1])
+    out = attention(q, k, v, q_sequence_ids=sequence_ids, k_sequence_ids=sequence_ids, causal=True, packed_causal=True)
+    return out * (sequence_ids != PAD_SEQUENCE_ID).unsqueeze(-1).unsqueeze(-1).to(out.dtype)
 
 
 def flash_attn_varlen_segments(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, token_indices: torch.Tensor, cu_seqlens: torch.Tensor,
                                max_seqlen: int) -> torch.Tensor:
-    """One varlen call over independent contiguous documents given as flattened token indices (``[B*S]`` order) and
-    their boundaries - a layout-only interface, so callers can cache both per batch."""
+    """Attention over independent contiguous documents given as flattened token indices (``[B*S]`` order) and their
+    boundaries - a layout-only interface, so callers can cache both per batch. Runs as one masked launch over the rows."""
     if q.dim() != 4 or k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3] or q.shape[2] % k.shape[2]:
         raise ValueError("flash_attn_varlen_segments expects [batch, tokens, heads, dim] Q and native matching K/V")
     if token_indices.dtype != torch.long or cu_seqlens.dtype != torch.int32:
         raise ValueError("token_indices must be int64 and cu_seqlens int32")
     if max_seqlen < 1 or token_indices.numel() == 0:
         return q.new_zeros(q.shape)
-    if flash_attn_fallback_reason(q) is not None:
-        ids = torch.full((q.shape[0] * q.shape[1],), PAD_SEQUENCE_ID, dtype=torch.long, device=q.device)
-        doc = torch.bucketize(torch.arange(token_indices.numel(), device=q.device), cu_seqlens[1:].to(torch.long), right=True)
-        ids[token_indices] = doc
-        return flash_attn_varlen(q, k, v, ids.view(q.shape[0], q.shape[1]))
-    flat = lambda t: t.reshape(-1, t.shape[2], t.shape[3]).index_select(0, token_indices)   # noqa: E731
-    out = _varlen_call(flat(q), flat(k), flat(v), cu_seqlens, max_seqlen)
-    return unpack_varlen_output_by_indices(out, token_indices, batch_size=q.shape[0], seq_len=q.shape[1])
+    ids = torch.full((q.shape[0] * q.shape[1],), PAD_SEQUENCE_ID, dtype=torch.long, device=q.device)
+    doc = torch.bucketize(torch.arange(token_indices.numel(), device=q.device), cu_seqlens[1:].to(torch.long), right=True)
+    ids[token_indices] = doc
+    return flash_attn_varlen(q, k, v, ids.view(q.shape[0], q.shape[1]))
 
 
 # ------------------------------------------------------------------------------------------------ dense blocks with LSE

@@ -163,27 +163,45 @@ def bench_shard_paths(args) -> None:
 
 def bench_attention(args) -> None:
     from maltos_b200.ops import _lib
-    from maltos_b200.ops.flash_attn import _sdpa_cudnn, flash_forward
+    from maltos_b200.ops.flash_attn import _sdpa_cudnn, flash_backward, flash_forward
 
     B, S, Hq, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
     g = torch.Generator(device="cuda").manual_seed(0)
     q = torch.randn(B, S, Hq, D, device="cuda", generator=g).bfloat16()
     k = torch.randn(B, S, Hkv, D, device="cuda", generator=g).bfloat16()
     v = torch.randn(B, S, Hkv, D, device="cuda", generator=g).bfloat16()
+    dout = torch.randn(B, S, Hq, D, device="cuda", generator=g).bfloat16()
     flops = 4.0 * B * S * S * D * Hq / (2 if args.causal else 1)
-    rows = []
+    mode = 1 if args.causal else 0
+    rows, rows_bwd = [], []
     with torch.no_grad():
-        rows.append(("tcgen05 flash forward (this library)", _time(lambda: flash_forward(q, k, v, mode=1 if args.causal else 0), args.iters)))
+        rows.append(("tcgen05 flash forward (this library)", _time(lambda: flash_forward(q, k, v, mode=mode), args.iters)))
+        out, lse = flash_forward(q, k, v, mode=mode)
+        rows_bwd.append(("tcgen05 flash backward (this library)",
+                         _time(lambda: flash_backward(q, k, v, out, lse, dout, mode=mode), args.iters)))
         if _sdpa_cudnn(q, k, v, args.causal, None) is not None:
             rows.append(("cuDNN fused attention (library)", _time(lambda: _sdpa_cudnn(q, k, v, args.causal, None), args.iters)))
+    if args.libraries:
+        ql, kl, vl = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = _sdpa_cudnn(ql, kl, vl, args.causal, None)
+        if o is not None:
+            rows_bwd.append(("cuDNN fused attention backward (library)",
+                             _time(lambda: torch.autograd.grad(o, (ql, kl, vl), dout, retain_graph=True), args.iters)))
         try:
             from flash_attn import flash_attn_func
 
-            rows.append(("flash-attn 2 (library)", _time(lambda: flash_attn_func(q, k, v, causal=args.causal), args.iters)))
+            with torch.no_grad():
+                rows.append(("flash-attn 2 (library)", _time(lambda: flash_attn_func(q, k, v, causal=args.causal), args.iters)))
+            o2 = flash_attn_func(ql, kl, vl, causal=args.causal)
+            rows_bwd.append(("flash-attn 2 backward (library)",
+                             _time(lambda: torch.autograd.grad(o2, (ql, kl, vl), dout, retain_graph=True), args.iters)))
         except ImportError:
             pass
+    tag = f"B{B} S{S} h{Hq}/{Hkv} D{D} {'causal' if args.causal else 'full'}"
     for name, ms in rows:
-        print(f"attention fwd B{B} S{S} h{Hq}/{Hkv} D{D} {'causal' if args.causal else 'full'} {name:>38}: {ms * 1e3:8.1f} us  {flops / ms / 1e9:7.1f} TFLOP/s")
+        print(f"attention fwd {tag} {name:>42}: {ms * 1e3:8.1f} us  {flops / ms / 1e9:7.1f} TFLOP/s")
+    for name, ms in rows_bwd:
+        print(f"attention bwd {tag} {name:>42}: {ms * 1e3:8.1f} us  {2.5 * flops / ms / 1e9:7.1f} TFLOP/s")
     _lib.fetch_status()
 
 
@@ -209,6 +227,7 @@ def main(argv=None) -> None:
     t.add_argument("--kv-heads", type=int, default=8)
     t.add_argument("--head-dim", type=int, default=128)
     t.add_argument("--causal", action=argparse.BooleanOptionalAction, default=True)
+    t.add_argument("--libraries", action=argparse.BooleanOptionalAction, default=True, help="also time the library kernels")
     a = sub.add_parser("adamw")
     a.add_argument("--numel", type=int, default=500_000_000)
     z = sub.add_parser("shard-paths")
