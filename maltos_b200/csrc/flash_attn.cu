@@ -137,15 +137,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0 && n_blocks > 0) {
       const uint32_t idesc_qk = make_idesc_bf16(kFaBM, kFaBN, 0, 0);      // S[128 q, 128 keys]: A = Q, B = K, both K-major over d
       const uint32_t idesc_pv = make_idesc_bf16(kFaBM, D, 0, 1);          // O[128 q, D]: A = P (K-major over keys), B = V (MN-major)
+      constexpr uint32_t hi_k = smem_desc_hi_sw128(1024);
+      const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 16), p_lo = smem_desc_lo(smem_u32(sP), 16);
       auto issue_qk = [&](int j) {
         const int s = j & 1;
-        const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + s * TILE_BYTES);
+        const uint32_t k_lo = smem_desc_lo(smem_u32(sK + s * TILE_BYTES), 16);
         const uint32_t d_tmem = tmem_base + S_COL0 + static_cast<uint32_t>(s * kFaBN);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = static_cast<uint32_t>((kk >> 2) * (kFaBM * 128) + (kk & 3) * 32);
-          umma_bf16_ss(d_tmem, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                       idesc_qk, kk != 0 ? 1u : 0u);
+          const uint32_t off = static_cast<uint32_t>(((kk >> 2) * (kFaBM * 128) + (kk & 3) * 32) >> 4);
+          umma_bf16_ss_lh(d_tmem, q_lo + off, hi_k, k_lo + off, hi_k, idesc_qk, kk != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[s]);
       };
@@ -165,12 +166,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(p_full, j & 1, abort_flag)) break;
         tc_fence_after();
         const int s = j & 1;
-        const uint32_t p_addr = smem_u32(sP), v_addr = smem_u32(sV + s * TILE_BYTES);
+        const uint32_t v_lo = smem_desc_lo(smem_u32(sV + s * TILE_BYTES), kFaBN * 128);   // MN-major: atoms kFaBN * 128 bytes apart
+        const uint32_t acc0 = j != 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kFaBN / 16; ++kk) {
-          const uint64_t adesc = make_smem_desc_sw128(p_addr + (kk >> 2) * (kFaBM * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(v_addr + kk * 2048, kFaBN * 128, 1024);
-          umma_bf16_ss(tmem_base + O_COL, adesc, bdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+          const uint32_t off_p = static_cast<uint32_t>(((kk >> 2) * (kFaBM * 128) + (kk & 3) * 32) >> 4);
+          umma_bf16_ss_lh(tmem_base + O_COL, p_lo + off_p, hi_k, v_lo + static_cast<uint32_t>(kk * 128), hi_k, idesc_pv, kk != 0 ? 1u : acc0);
         }
         umma_commit(&kv_empty[s]);   // K and V of this stage are free
         umma_commit(o_full);         // O holds blocks 0..j; the P tile may be overwritten

@@ -18,13 +18,16 @@
 // forward (mode 0 all visible, 1 causal with offset, 2 positions + sequence ids, 3 causal by index + same sequence id).
 // Every wait is bounded (see ptx.cuh). The reference gets this op from the flash-attn 2 package
 // (runtime/layers/flash_utils.py:218-260) or from autograd through SDPA.
+#include <cstdlib>
+
 #include "host.h"
 #include "ptx.cuh"
 
 namespace mb {
 
-constexpr int kBwThreads = 320;      // warp 0 TMA producer, warp 1 UMMA issuer, warps 2..9 arithmetic / epilogue
-constexpr int kBwComputeWarps = 8;
+constexpr int kBwComputeWarps = 16;   // four warps per TMEM lane quarter: enough warps per scheduler to hide the latency of
+                                      // the dependent exp / multiply / pack chains
+constexpr int kBwThreads = 32 * (2 + kBwComputeWarps);   // warp 0 TMA producer, warp 1 UMMA issuer, warps 2..17 arithmetic
 constexpr float kBwLog2e = 1.4426950408889634f;
 
 struct FlashBwdArgs {
@@ -45,7 +48,25 @@ struct FlashBwdArgs {
   int accumulate;           // 1 (fp32 outputs only): add to what the output holds
   float scale, scale_log2;
   int* status;
+  int dbg;                  // probe builds only: bit 0 skip the S/dP UMMAs, bit 1 skip the accumulation UMMAs, bit 2 skip the arithmetic
 };
+
+#ifdef MB_FLASH_PROBE
+// Timing probe (never part of the default build): clock64() stamps of the first CTA's issuing thread and of one arithmetic
+// warp, 8 slots per iteration, read back with mb_flash_probe_read.
+__device__ long long g_flash_probe[16 * 256];
+#define MB_PROBE(cond, it, slot)                                                                  \
+  do {                                                                                            \
+    if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_flash_probe[(it) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define MB_PROBE(cond, it, slot) do { } while (0)
+#endif
+#ifdef MB_FLASH_PROBE
+#define MB_DBG(bit) ((p.dbg >> (bit)) & 1)
+#else
+#define MB_DBG(bit) 0
+#endif
 
 __device__ __forceinline__ float bw_exp2(float x) {
   float y;
@@ -100,13 +121,13 @@ __global__ void flash_bwd_pad_kernel(const int* __restrict__ src, int* __restric
   dst[i] = v;
 }
 
-__device__ __forceinline__ void store_row_chunk(void* base, long long elem_off, const uint32_t (&r)[32], float mul, bool fp32,
+// 16 consecutive output elements starting at elem_off
+__device__ __forceinline__ void store_row_chunk(void* base, long long elem_off, const uint32_t (&r)[16], float mul, bool fp32,
                                                 bool accumulate) {
-  // 32 consecutive output elements starting at elem_off
   if (fp32) {
     float* dst = static_cast<float*>(base) + elem_off;
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
+    for (int i = 0; i < 16; i += 4) {
       float4 v = make_float4(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul, __uint_as_float(r[i + 2]) * mul,
                              __uint_as_float(r[i + 3]) * mul);
       if (accumulate) {
@@ -118,7 +139,7 @@ __device__ __forceinline__ void store_row_chunk(void* base, long long elem_off, 
   } else {
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(base) + elem_off;
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
+    for (int i = 0; i < 16; i += 8) {
       uint4 v;
       v.x = pack_bf16x2(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
       v.y = pack_bf16x2(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
@@ -144,7 +165,7 @@ constexpr int kKvRows = 128;   // keys per CTA
 constexpr int kQSub = 64;      // query rows per iteration
 constexpr int kQStages = 4;
 
-template <int D>
+template <int D, int MODE>
 __global__ void __launch_bounds__(kBwThreads, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FlashBwdArgs p) {
@@ -177,7 +198,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int group = p.Hq / p.Hkv;
   const int k0 = static_cast<int>(blockIdx.x) * kKvRows;
   const int causal_off = p.Sk - p.Sq;
-  const bool causal = p.mode == 1 || p.mode == 3;
+  constexpr bool causal = MODE == 1 || MODE == 3;
 
   // query sub-blocks this key block has to visit
   const int n_qsub_all = (p.Sq + kQSub - 1) / kQSub;
@@ -226,7 +247,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tma_load_4d(sK + a * (kKvRows * 128), &tmK, kv_full, a * 64, kv_head, k0, batch);
         tma_load_4d(sV + a * (kKvRows * 128), &tmV, kv_full, a * 64, kv_head, k0, batch);
       }
-      const bool with_ids = p.mode >= 2;
+      constexpr bool with_ids = MODE >= 2;
       for (int it = 0; it < n_iter; ++it) {
         const int st = it % kQStages;
         if (!mbar_wait(&q_empty[st], ((it / kQStages) & 1) ^ 1, abort_flag)) break;
@@ -255,40 +276,42 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_s = make_idesc_bf16(kKvRows, kQSub, 0, 0);    // [128 keys, 64 q] = A(K-major over d) x B(K-major over d)
       const uint32_t idesc_acc = make_idesc_bf16(kKvRows, D, 0, 1);      // [128 keys, D]   = A(TMEM) x B(MN-major)
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      constexpr uint32_t hi_k = smem_desc_hi_sw128(1024);               // both operand kinds: 8-row groups 1024 bytes apart
+      const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
       auto issue_sdp = [&](int it) {
         const int st = it % kQStages;
-        const uint32_t slot = static_cast<uint32_t>(it & 1) * 128u;
-        const uint32_t q_addr = smem_u32(sQ + st * Q_BYTES), do_addr = smem_u32(sDO + st * Q_BYTES);
+        const uint32_t slot = tmem_base + static_cast<uint32_t>(it & 1) * 128u;
+        const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + st * Q_BYTES), 16), do_lo = smem_desc_lo(smem_u32(sDO + st * Q_BYTES), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off_a = static_cast<uint32_t>((kk >> 2) * (kKvRows * 128) + (kk & 3) * 32);
-          const uint32_t off_b = static_cast<uint32_t>((kk >> 2) * (kQSub * 128) + (kk & 3) * 32);
-          umma_bf16_ss(tmem_base + slot, make_smem_desc_sw128(k_addr + off_a, 16, 1024),
-                       make_smem_desc_sw128(q_addr + off_b, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          if (MB_DBG(0)) break;
+          const uint32_t off_a = static_cast<uint32_t>(((kk >> 2) * (kKvRows * 128) + (kk & 3) * 32) >> 4);
+          const uint32_t off_b = static_cast<uint32_t>(((kk >> 2) * (kQSub * 128) + (kk & 3) * 32) >> 4);
+          umma_bf16_ss_lh(slot, k_lo + off_a, hi_k, q_lo + off_b, hi_k, idesc_s, kk != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off_a = static_cast<uint32_t>((kk >> 2) * (kKvRows * 128) + (kk & 3) * 32);
-          const uint32_t off_b = static_cast<uint32_t>((kk >> 2) * (kQSub * 128) + (kk & 3) * 32);
-          umma_bf16_ss(tmem_base + slot + 64u, make_smem_desc_sw128(v_addr + off_a, 16, 1024),
-                       make_smem_desc_sw128(do_addr + off_b, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          if (MB_DBG(0)) break;
+          const uint32_t off_a = static_cast<uint32_t>(((kk >> 2) * (kKvRows * 128) + (kk & 3) * 32) >> 4);
+          const uint32_t off_b = static_cast<uint32_t>(((kk >> 2) * (kQSub * 128) + (kk & 3) * 32) >> 4);
+          umma_bf16_ss_lh(slot + 64u, v_lo + off_a, hi_k, do_lo + off_b, hi_k, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[it & 1]);
       };
       auto issue_acc = [&](int it) {
         const int st = it % kQStages;
-        const uint32_t slot = static_cast<uint32_t>(it & 1) * 128u;
-        const uint32_t q_addr = smem_u32(sQ + st * Q_BYTES), do_addr = smem_u32(sDO + st * Q_BYTES);
+        const uint32_t slot = tmem_base + static_cast<uint32_t>(it & 1) * 128u;
+        // MN-major B operands: 64-wide atoms of the head dimension are kQSub * 128 bytes apart
+        const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + st * Q_BYTES), kQSub * 128), do_lo = smem_desc_lo(smem_u32(sDO + st * Q_BYTES), kQSub * 128);
+        const uint32_t acc0 = it != 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kQSub / 16; ++kk) {
-          // packed bf16 pairs: query rows 0..31 of the sub-block sit in columns 0..15, rows 32..63 in columns 32..47
-          const uint32_t a_col = static_cast<uint32_t>(kk < 2 ? kk * 8 : 32 + (kk - 2) * 8);
-          const uint32_t acc_on = (it | kk) != 0 ? 1u : 0u;
-          umma_bf16_ts(tmem_base + DV_COL, tmem_base + slot + a_col,
-                       make_smem_desc_sw128(do_addr + kk * 2048, kQSub * 128, 1024), idesc_acc, acc_on);
-          umma_bf16_ts(tmem_base + DK_COL, tmem_base + slot + 64u + a_col,
-                       make_smem_desc_sw128(q_addr + kk * 2048, kQSub * 128, 1024), idesc_acc, acc_on);
+          if (MB_DBG(1)) break;
+          // packed bf16 pairs: the 16 query rows of k-step kk sit in the first 8 of the 16 columns their scores had
+          const uint32_t a_col = static_cast<uint32_t>(kk * 16);
+          const uint32_t acc_on = kk != 0 ? 1u : acc0;
+          umma_bf16_ts_lh(tmem_base + DV_COL, slot + a_col, do_lo + static_cast<uint32_t>(kk * 128), hi_k, idesc_acc, acc_on);
+          umma_bf16_ts_lh(tmem_base + DK_COL, slot + 64u + a_col, q_lo + static_cast<uint32_t>(kk * 128), hi_k, idesc_acc, acc_on);
         }
         umma_commit(&q_empty[st]);
       };
@@ -302,30 +325,35 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait(&q_full[(it + 1) % kQStages], ((it + 1) / kQStages) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          MB_PROBE(true, it, 0);
           issue_sdp(it + 1);     // its slot was last read by the accumulation UMMAs of it - 1, issued before
+          MB_PROBE(true, it, 1);
         }
         ok = mbar_wait(&p_full[it & 1], (it >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        MB_PROBE(true, it, 2);
         issue_acc(it);
+        MB_PROBE(true, it, 3);
       }
       if (ok) umma_commit(acc_full);
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ arithmetic: lane = key, 32 query columns per thread
-    const int qw = warp & 3;
-    const int half = (warp - 2) >> 2;
+    // ------------------------------------------------------------------ arithmetic: lane = key, 16 query columns per thread
+    const int qw = warp & 3;                      // TMEM lane quarter this warp may touch
+    const int grp = (warp - 2) >> 2;              // which 16 of the 64 query columns
     const int row = qw * 32 + lane;
     const int kj = k0 + row;
     const bool key_valid = kj < p.Sk;
     const uint32_t t_lane = static_cast<uint32_t>(qw * 32) << 16;
     int my_pos = 0, my_seq = 0;
-    if (p.mode >= 2) {
+    if (MODE >= 2) {
       const long long at = static_cast<long long>(batch) * p.Sk_pad + kj;   // padded: always in range
       my_pos = p.kpos[at];
       my_seq = p.kseq[at];
     }
+    const float scale_log2 = p.scale_log2;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int st = it % kQStages;
@@ -334,48 +362,78 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t_s = tmem_base + slot + static_cast<uint32_t>(half * 32) + t_lane;
-      uint32_t s[32], dp[32];
-      tmem_ld_32x32b_x32(t_s, s);
-      tmem_ld_32x32b_x32(t_s + 64u, dp);
-      tmem_ld_wait();
-      const float* aux = reinterpret_cast<const float*>(sAux + st * AUX_BYTES);
-      const float* a_lse = aux + half * 32;
-      const float* a_delta = aux + kQSub + half * 32;
-      const int* a_pos = reinterpret_cast<const int*>(aux) + 2 * kQSub + half * 32;
-      const int* a_seq = reinterpret_cast<const int*>(aux) + 3 * kQSub + half * 32;
-      const int q_first = (qb_start + it % n_sub) * kQSub + half * 32;   // query row of this thread's first column
-      // does this sub-block contain a masked pair?
-      bool need_mask = !key_valid || p.mode == 2;
-      if (causal) need_mask = need_mask || (k0 + kKvRows - 1 > (qb_start + it % n_sub) * kQSub + causal_off);
-      if (p.mode == 3) need_mask = true;
-      uint32_t pk[16], dk_[16];
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float pr[2], ds[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int cc = c + u;
-          float prob = bw_exp2(fmaf(__uint_as_float(s[cc]), p.scale_log2, -a_lse[cc]));
-          if (need_mask) {
-            bool vis = key_valid;
-            if (causal) vis = vis && (kj <= q_first + cc + causal_off);
-            if (p.mode == 2) vis = vis && (my_pos <= a_pos[cc]);
-            if (p.mode >= 2) vis = vis && (my_seq == a_seq[cc]) && (my_seq != -1);
-            prob = vis ? prob : 0.f;
-          }
-          pr[u] = prob;
-          ds[u] = prob * (__uint_as_float(dp[cc]) - a_delta[cc]);
-        }
-        pk[c >> 1] = pack_bf16x2(pr[0], pr[1]);
-        dk_[c >> 1] = pack_bf16x2(ds[0], ds[1]);
+      MB_PROBE(warp == 2 && lane == 0, it, 4);
+      if (MB_DBG(2)) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[it & 1]);
+        continue;
       }
-      tmem_st_32x32b_x16(t_s, pk);          // P^T over this thread's own score columns
-      tmem_st_32x32b_x16(t_s + 64u, dk_);   // dS^T over its dP columns
+      const uint32_t t_s = tmem_base + slot + static_cast<uint32_t>(grp * 16) + t_lane;
+      uint32_t s[16], dp[16];
+      if (!MB_DBG(3)) {
+        tmem_ld_32x32b_x16(t_s, s);
+        tmem_ld_32x32b_x16(t_s + 64u, dp);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) s[c] = dp[c] = static_cast<uint32_t>(it + c);
+      }
+      const uint8_t* aux = sAux + st * AUX_BYTES + grp * 64;
+      float lse[16], dl[16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(aux + i * 16);
+        const float4 d = *reinterpret_cast<const float4*>(aux + kQSub * 4 + i * 16);
+        lse[4 * i] = a.x, lse[4 * i + 1] = a.y, lse[4 * i + 2] = a.z, lse[4 * i + 3] = a.w;
+        dl[4 * i] = d.x, dl[4 * i + 1] = d.y, dl[4 * i + 2] = d.z, dl[4 * i + 3] = d.w;
+      }
+      tmem_ld_wait();
+      MB_PROBE(warp == 2 && lane == 0, it, 5);
+      const int qsub0 = (qb_start + it % n_sub) * kQSub;      // first query row of the sub-block
+      // does this sub-block contain a masked pair? (warp-uniform)
+      bool need_mask = (k0 + kKvRows > p.Sk) || MODE >= 2;
+      if (causal) need_mask = need_mask || (k0 + kKvRows - 1 > qsub0 + causal_off);
+      float pr[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) pr[c] = MB_DBG(5) ? __uint_as_float(s[c]) : bw_exp2(fmaf(__uint_as_float(s[c]), scale_log2, -lse[c]));
+      if (need_mask) {
+        int qp[16], qs[16];
+        if (MODE >= 2) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int4 a = *reinterpret_cast<const int4*>(aux + 2 * kQSub * 4 + i * 16);
+            const int4 d = *reinterpret_cast<const int4*>(aux + 3 * kQSub * 4 + i * 16);
+            qp[4 * i] = a.x, qp[4 * i + 1] = a.y, qp[4 * i + 2] = a.z, qp[4 * i + 3] = a.w;
+            qs[4 * i] = d.x, qs[4 * i + 1] = d.y, qs[4 * i + 2] = d.z, qs[4 * i + 3] = d.w;
+          }
+        }
+        const int q_first = qsub0 + grp * 16 + causal_off;     // key index visible up to (causal modes)
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          bool vis = key_valid;
+          if (causal) vis = vis && (kj <= q_first + c);
+          if (MODE == 2) vis = vis && (my_pos <= qp[c]);
+          if (MODE >= 2) vis = vis && (my_seq == qs[c]) && (my_seq != -1);
+          pr[c] = vis ? pr[c] : 0.f;
+        }
+      }
+      uint32_t pk[8], dsk[8];
+#pragma unroll
+      for (int c = 0; c < 16; c += 2) {
+        pk[c >> 1] = pack_bf16x2(pr[c], pr[c + 1]);
+        dsk[c >> 1] = pack_bf16x2(pr[c] * (__uint_as_float(dp[c]) - dl[c]), pr[c + 1] * (__uint_as_float(dp[c + 1]) - dl[c + 1]));
+      }
+      MB_PROBE(warp == 2 && lane == 0, it, 6);
+      if (!MB_DBG(4)) {
+      tmem_st_32x32b_x8(t_s, pk);           // P^T over the first half of this thread's own score columns
+      tmem_st_32x32b_x8(t_s + 64u, dsk);    // dS^T over its dP columns
       tmem_st_wait();
+      } else if (pk[0] == 0x12345678u && dsk[3] == 0x9abcdef0u) {
+        p.status[2] = 7;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[it & 1]);
+      MB_PROBE(warp == 2 && lane == 0, it, 7);
     }
     // ------------------------------------------------------------------ epilogue: dV, dK rows of this key
     if (ok && n_iter > 0) {
@@ -383,23 +441,23 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
-      constexpr int HALF_D = D / 2;
-      const long long off = (static_cast<long long>(batch) * p.Sk + kj) * p.dkv_tstride + static_cast<long long>(kv_head) * D + half * HALF_D;
+      constexpr int QUART_D = D / 4;                // columns of the head dimension per thread
+      const long long off = (static_cast<long long>(batch) * p.Sk + kj) * p.dkv_tstride + static_cast<long long>(kv_head) * D + grp * QUART_D;
       if (n_iter > 0) {
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < HALF_D; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + DV_COL + static_cast<uint32_t>(half * HALF_D + c0) + t_lane, r);
+        for (int c0 = 0; c0 < QUART_D; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(tmem_base + DV_COL + static_cast<uint32_t>(grp * QUART_D + c0) + t_lane, r);
           tmem_ld_wait();
           if (key_valid) store_row_chunk(p.dv, off + c0, r, 1.f, p.out_fp32 != 0, p.accumulate != 0);
-          tmem_ld_32x32b_x32(tmem_base + DK_COL + static_cast<uint32_t>(half * HALF_D + c0) + t_lane, r);
+          tmem_ld_32x32b_x16(tmem_base + DK_COL + static_cast<uint32_t>(grp * QUART_D + c0) + t_lane, r);
           tmem_ld_wait();
           if (key_valid) store_row_chunk(p.dk, off + c0, r, p.scale, p.out_fp32 != 0, p.accumulate != 0);
         }
       } else if (key_valid && !p.accumulate) {
-        store_row_zero(p.dv, off, HALF_D, p.out_fp32 != 0);
-        store_row_zero(p.dk, off, HALF_D, p.out_fp32 != 0);
+        store_row_zero(p.dv, off, QUART_D, p.out_fp32 != 0);
+        store_row_zero(p.dk, off, QUART_D, p.out_fp32 != 0);
       }
     }
   }
@@ -424,7 +482,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 constexpr int kDqRows = 128;   // query rows per CTA
 constexpr int kDqKeys = 128;   // keys per block
 
-template <int D>
+template <int D, int MODE>
 __global__ void __launch_bounds__(kBwThreads, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FlashBwdArgs p) {
@@ -434,23 +492,31 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t DP_COL = 256, DQ_COL = 384;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // K and V have rings of their own: a V tile is free as soon as dP of its block is done, a K tile only after dQ, and
+  // the tensor-map loads are slow enough (64 KB take ~1400 cycles) that K needs three stages to stay ahead. With Q and
+  // dO resident that fills the shared memory of the SM, so the dynamic window must start 1024-byte aligned (checked).
+  // (The masks that need per-key ids keep two K stages at head_dim 128: their id arrays take the remaining space.)
+  constexpr int K_STAGES = (D == 128) ? (MODE >= 2 ? 2 : 3) : 4;
+  constexpr int AUX_STAGES = MODE >= 2 ? K_STAGES : 0;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + TILE_BYTES;
-  uint8_t* sK = sDO + TILE_BYTES;                   // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;                // 2 stages
-  uint8_t* sAux = sV + 2 * TILE_BYTES;              // 2 x AUX_BYTES
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sAux + 2 * AUX_BYTES);
+  uint8_t* sK = sDO + TILE_BYTES;                   // K_STAGES stages
+  uint8_t* sV = sK + K_STAGES * TILE_BYTES;         // 2 stages
+  uint8_t* sAux = sV + 2 * TILE_BYTES;              // AUX_STAGES x AUX_BYTES
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sAux + AUX_STAGES * AUX_BYTES);
   uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // 2
-  uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // 2
-  uint64_t* dp_full = bars + 7;       // 1
-  uint64_t* dp_free = bars + 8;       // 1 (count = arithmetic warps)
-  uint64_t* ds_full = bars + 9;       // 1 (count = arithmetic warps)
-  uint64_t* dq_full = bars + 10;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 1;        // K_STAGES (<= 4)
+  uint64_t* k_empty = bars + 5;       // K_STAGES
+  uint64_t* v_full = bars + 9;        // 2
+  uint64_t* v_empty = bars + 11;      // 2
+  uint64_t* s_full = bars + 13;       // 2
+  uint64_t* dp_full = bars + 15;      // 1
+  uint64_t* dp_free = bars + 16;      // 1 (count = arithmetic warps)
+  uint64_t* ds_full = bars + 17;      // 1 (count = arithmetic warps)
+  uint64_t* dq_full = bars + 18;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -459,7 +525,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q0 = q_tile * kDqRows;
   const int causal_off = p.Sk - p.Sq;
-  const bool causal = p.mode == 1 || p.mode == 3;
+  constexpr bool causal = MODE == 1 || MODE == 3;
 
   int n_blocks = (p.Sk + kDqKeys - 1) / kDqKeys;
   if (causal) {
@@ -467,11 +533,22 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     n_blocks = last_key < 0 ? 0 : min(n_blocks, last_key / kDqKeys + 1);
   }
 
+  if (smem_u32(smem_raw) & 1023u) {   // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0) {
+      atomicOr(&p.status[0], MB_ERR_BAD_INDEX);
+      p.status[2] = 1003;
+    }
+    return;
+  }
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    for (int i = 0; i < K_STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
     mbar_init(dp_full, 1);
@@ -504,21 +581,24 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_4d(sQ + a * (kDqRows * 128), &tmQ, q_full, a * 64, head, q0, batch);
         tma_load_4d(sDO + a * (kDqRows * 128), &tmDO, q_full, a * 64, head, q0, batch);
       }
-      const bool with_ids = p.mode >= 2;
+      constexpr bool with_ids = MODE >= 2;
       for (int j = 0; j < n_blocks; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) break;
-        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES + (with_ids ? AUX_BYTES : 0));
+        const int ks = j % K_STAGES, vs = j & 1;
+        if (!mbar_wait(&k_empty[ks], ((j / K_STAGES) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&k_full[ks], TILE_BYTES + (with_ids ? AUX_BYTES : 0));
 #pragma unroll
-        for (int a = 0; a < ATOMS; ++a) {
-          tma_load_4d(sK + s * TILE_BYTES + a * (kDqKeys * 128), &tmK, &kv_full[s], a * 64, kv_head, j * kDqKeys, batch);
-          tma_load_4d(sV + s * TILE_BYTES + a * (kDqKeys * 128), &tmV, &kv_full[s], a * 64, kv_head, j * kDqKeys, batch);
-        }
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_4d(sK + ks * TILE_BYTES + a * (kDqKeys * 128), &tmK, &k_full[ks], a * 64, kv_head, j * kDqKeys, batch);
         if (with_ids) {
           const long long prow = static_cast<long long>(batch) * p.Sk_pad + j * kDqKeys;
-          bulk_load(sAux + s * AUX_BYTES, p.kpos + prow, kDqKeys * 4, &kv_full[s]);
-          bulk_load(sAux + s * AUX_BYTES + kDqKeys * 4, p.kseq + prow, kDqKeys * 4, &kv_full[s]);
+          bulk_load(sAux + ks * AUX_BYTES, p.kpos + prow, kDqKeys * 4, &k_full[ks]);
+          bulk_load(sAux + ks * AUX_BYTES + kDqKeys * 4, p.kseq + prow, kDqKeys * 4, &k_full[ks]);
         }
+        if (!mbar_wait(&v_empty[vs], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&v_full[vs], TILE_BYTES);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_4d(sV + vs * TILE_BYTES + a * (kDqKeys * 128), &tmV, &v_full[vs], a * 64, kv_head, j * kDqKeys, batch);
       }
     }
     __syncwarp();
@@ -527,65 +607,77 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0 && n_blocks > 0) {
       const uint32_t idesc_s = make_idesc_bf16(kDqRows, kDqKeys, 0, 0);   // [128 q, 128 keys]
       const uint32_t idesc_dq = make_idesc_bf16(kDqRows, D, 0, 1);         // [128 q, D] = A(TMEM) x B(K tile, MN-major)
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+      constexpr uint32_t hi_k = smem_desc_hi_sw128(1024);
+      const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 16), do_lo = smem_desc_lo(smem_u32(sDO), 16);
       auto issue_s = [&](int j) {
-        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
+        const uint32_t k_lo = smem_desc_lo(smem_u32(sK + (j % K_STAGES) * TILE_BYTES), 16);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j & 1) * 128u;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = static_cast<uint32_t>((kk >> 2) * (128 * 128) + (kk & 3) * 32);
-          umma_bf16_ss(tmem_base + static_cast<uint32_t>(j & 1) * 128u, make_smem_desc_sw128(q_addr + off, 16, 1024),
-                       make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          const uint32_t off = static_cast<uint32_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);
+          umma_bf16_ss_lh(d_tmem, q_lo + off, hi_k, k_lo + off, hi_k, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[j & 1]);
       };
       auto issue_dp = [&](int j) {
-        const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE_BYTES);
+        const uint32_t v_lo = smem_desc_lo(smem_u32(sV + (j & 1) * TILE_BYTES), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = static_cast<uint32_t>((kk >> 2) * (128 * 128) + (kk & 3) * 32);
-          umma_bf16_ss(tmem_base + DP_COL, make_smem_desc_sw128(do_addr + off, 16, 1024),
-                       make_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          const uint32_t off = static_cast<uint32_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);
+          umma_bf16_ss_lh(tmem_base + DP_COL, do_lo + off, hi_k, v_lo + off, hi_k, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(dp_full);
+        umma_commit(&v_empty[j & 1]);   // this V tile is not read again
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
       if (ok) {
         tc_fence_after();
         issue_s(0);
+        ok = mbar_wait(&v_full[0], 0, abort_flag);
+      }
+      if (ok) {
+        tc_fence_after();
         issue_dp(0);
       }
       for (int j = 0; ok && j < n_blocks; ++j) {
         if (j + 1 < n_blocks) {
-          ok = mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+          ok = mbar_wait(&k_full[(j + 1) % K_STAGES], ((j + 1) / K_STAGES) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          MB_PROBE(true, j, 0);
           issue_s(j + 1);           // its S buffer was last read by dQ of block j - 1, issued before
-          ok = mbar_wait(dp_free, j & 1, abort_flag);   // block j's dP has been read
+          MB_PROBE(true, j, 1);
+          ok = mbar_wait(dp_free, j & 1, abort_flag) &&   // block j's dP has been read
+               mbar_wait(&v_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          MB_PROBE(true, j, 2);
           issue_dp(j + 1);
+          MB_PROBE(true, j, 3);
         }
         ok = mbar_wait(ds_full, j & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
-        const uint32_t s_col = static_cast<uint32_t>(j & 1) * 128u;
+        MB_PROBE(true, j, 4);
+        const uint32_t k_lo = smem_desc_lo(smem_u32(sK + (j % K_STAGES) * TILE_BYTES), kDqKeys * 128);   // MN-major B: atoms kDqKeys * 128 bytes apart
+        const uint32_t s_col = tmem_base + static_cast<uint32_t>(j & 1) * 128u;
+        const uint32_t acc0 = j != 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kDqKeys / 16; ++kk) {
-          // packed bf16 pairs: keys 0..63 of the block sit in columns 0..31, keys 64..127 in columns 64..95
-          const uint32_t a_col = static_cast<uint32_t>(kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + s_col + a_col,
-                       make_smem_desc_sw128(k_addr + kk * 2048, kDqKeys * 128, 1024), idesc_dq, (j | kk) != 0 ? 1u : 0u);
+          // packed bf16 pairs: the 32 keys of column group g sit in the first 16 of the 32 columns their scores had
+          const uint32_t a_col = static_cast<uint32_t>((kk >> 1) * 32 + (kk & 1) * 8);
+          umma_bf16_ts_lh(tmem_base + DQ_COL, s_col + a_col, k_lo + static_cast<uint32_t>(kk * 128), hi_k, idesc_dq, kk != 0 ? 1u : acc0);
         }
-        umma_commit(&kv_empty[j & 1]);
+        umma_commit(&k_empty[j % K_STAGES]);
+        MB_PROBE(true, j, 5);
       }
       if (ok) umma_commit(dq_full);
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ arithmetic: lane = query row, 64 key columns per thread
+    // ------------------------------------------------------------------ arithmetic: lane = query row, 32 key columns per thread
     const int qw = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 2;              // which 32 of the 128 key columns
     const int row = qw * 32 + lane;
     const int qi = q0 + row;
     const bool row_valid = qi < p.Sq;
@@ -594,66 +686,70 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float my_lse = p.lse2[arow];
     const float my_delta = p.delta[arow];
     int my_pos = 0, my_seq = 0;
-    if (p.mode >= 2) {
+    if (MODE >= 2) {
       const long long at = static_cast<long long>(batch) * p.Sq_pad + qi;
       my_pos = p.qpos[at];
       my_seq = p.qseq[at];
     }
+    const float scale_log2 = p.scale_log2;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
       const int s = j & 1;
-      ok = mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag) && mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag) &&
+      ok = mbar_wait(&k_full[j % K_STAGES], (j / K_STAGES) & 1, abort_flag) && mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag) &&
            mbar_wait(dp_full, j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t_s = tmem_base + static_cast<uint32_t>(s * 128 + half * 64) + t_lane;
-      const uint32_t t_dp = tmem_base + DP_COL + static_cast<uint32_t>(half * 64) + t_lane;
-      const int key0 = j * kDqKeys + half * 64;
-      bool need_mask = j * kDqKeys + kDqKeys > p.Sk || p.mode >= 2;
+      MB_PROBE(warp == 2 && lane == 0, j, 8);
+      const uint32_t t_s = tmem_base + static_cast<uint32_t>(s * 128 + grp * 32) + t_lane;
+      const uint32_t t_dp = tmem_base + DP_COL + static_cast<uint32_t>(grp * 32) + t_lane;
+      uint32_t sc[32], dp[32];
+      tmem_ld_32x32b_x32(t_s, sc);
+      tmem_ld_32x32b_x32(t_dp, dp);
+      tmem_ld_wait();
+      MB_PROBE(warp == 2 && lane == 0, j, 9);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dp_free);        // this warp's dP columns are in registers: the next block's dP may be issued
+      const int key0 = j * kDqKeys + grp * 32;
+      bool need_mask = (j * kDqKeys + kDqKeys > p.Sk) || MODE >= 2;
       if (causal) need_mask = need_mask || (j * kDqKeys + kDqKeys - 1 > q0 + causal_off);
-      const int* a_pos = reinterpret_cast<const int*>(sAux + s * AUX_BYTES) + half * 64;
-      const int* a_seq = a_pos + kDqKeys;
-#pragma unroll 1
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t sc[32], dp[32];
-        tmem_ld_32x32b_x32(t_s + ch * 32, sc);
-        tmem_ld_32x32b_x32(t_dp + ch * 32, dp);
-        tmem_ld_wait();
-        if (ch == 1) {             // every dP column of this warp is in registers: the next block's dP may be issued
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(dp_free);
-        }
-        uint32_t dsp[16];
+      float pr[32];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float ds[2];
+      for (int c = 0; c < 32; ++c) pr[c] = bw_exp2(fmaf(__uint_as_float(sc[c]), scale_log2, -my_lse));
+      if (need_mask) {
+        const uint8_t* aux = sAux + (j % K_STAGES) * AUX_BYTES + grp * 128;
+        const int q_lim = qi + causal_off - key0;   // column c visible (causal modes) iff c <= q_lim
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cc = c + u;
-            float prob = bw_exp2(fmaf(__uint_as_float(sc[cc]), p.scale_log2, -my_lse));
-            if (need_mask) {
-              const int kj = key0 + ch * 32 + cc;
-              bool vis = kj < p.Sk;
-              if (causal) vis = vis && (kj <= qi + causal_off);
-              if (p.mode == 2) vis = vis && (a_pos[ch * 32 + cc] <= my_pos);
-              if (p.mode >= 2) {
-                const int ks = a_seq[ch * 32 + cc];
-                vis = vis && (ks == my_seq) && (ks != -1);
-              }
-              prob = vis ? prob : 0.f;
-            }
-            ds[u] = prob * (__uint_as_float(dp[cc]) - my_delta);
+        for (int i = 0; i < 8; ++i) {
+          int4 kp = make_int4(0, 0, 0, 0), ks = make_int4(0, 0, 0, 0);
+          if (MODE >= 2) {
+            kp = *reinterpret_cast<const int4*>(aux + i * 16);
+            ks = *reinterpret_cast<const int4*>(aux + kDqKeys * 4 + i * 16);
           }
-          dsp[c >> 1] = pack_bf16x2(ds[0], ds[1]);
+          const int kpv[4] = {kp.x, kp.y, kp.z, kp.w}, ksv[4] = {ks.x, ks.y, ks.z, ks.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = 4 * i + u;
+            bool vis = key0 + c < p.Sk;
+            if (causal) vis = vis && (c <= q_lim);
+            if (MODE == 2) vis = vis && (kpv[u] <= my_pos);
+            if (MODE >= 2) vis = vis && (ksv[u] == my_seq) && (ksv[u] != -1);
+            pr[c] = vis ? pr[c] : 0.f;
+          }
         }
-        tmem_st_32x32b_x16(t_s + ch * 16, dsp);   // dS over this thread's own score columns
       }
+      uint32_t dsp[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2)
+        dsp[c >> 1] = pack_bf16x2(pr[c] * (__uint_as_float(dp[c]) - my_delta), pr[c + 1] * (__uint_as_float(dp[c + 1]) - my_delta));
+      MB_PROBE(warp == 2 && lane == 0, j, 10);
+      tmem_st_32x32b_x16(t_s, dsp);               // dS over the first half of this thread's own score columns
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
+      MB_PROBE(warp == 2 && lane == 0, j, 11);
     }
     // ------------------------------------------------------------------ epilogue
     if (ok && n_blocks > 0) {
@@ -661,19 +757,19 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
-      constexpr int HALF_D = D / 2;
-      const long long off = (static_cast<long long>(batch) * p.Sq + qi) * p.dq_tstride + static_cast<long long>(head) * D + half * HALF_D;
+      constexpr int QUART_D = D / 4;
+      const long long off = (static_cast<long long>(batch) * p.Sq + qi) * p.dq_tstride + static_cast<long long>(head) * D + grp * QUART_D;
       if (n_blocks > 0) {
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < HALF_D; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + DQ_COL + static_cast<uint32_t>(half * HALF_D + c0) + t_lane, r);
+        for (int c0 = 0; c0 < QUART_D; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(tmem_base + DQ_COL + static_cast<uint32_t>(grp * QUART_D + c0) + t_lane, r);
           tmem_ld_wait();
           if (row_valid) store_row_chunk(p.dq, off + c0, r, p.scale, p.out_fp32 != 0, p.accumulate != 0);
         }
       } else if (row_valid && !p.accumulate) {
-        store_row_zero(p.dq, off, HALF_D, p.out_fp32 != 0);
+        store_row_zero(p.dq, off, QUART_D, p.out_fp32 != 0);
       }
     }
   }
@@ -694,7 +790,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-template <int D>
+template <int D, int MODE>
 static int launch_flash_bwd(const void* q, long long q_tstride, long long q_bstride, const void* k, const void* v,
                             long long kv_tstride, long long kv_bstride, const void* out, long long o_tstride, long long o_bstride,
                             const void* dout, long long do_tstride, long long do_bstride, const float* lse, const int* q_pos,
@@ -717,7 +813,7 @@ static int launch_flash_bwd(const void* q, long long q_tstride, long long q_bstr
         do_bstride, lse, lse2, delta, a.B, a.Sq, a.Hq, a.Sq_pad);
     count_launch();
   }
-  if (a.mode >= 2) {
+  if (MODE >= 2) {
     const int block = 256;
     const long long nq = static_cast<long long>(a.B) * a.Sq_pad, nk = static_cast<long long>(a.B) * a.Sk_pad;
     const unsigned gq = static_cast<unsigned>((nq + block - 1) / block), gk = static_cast<unsigned>((nk + block - 1) / block);
@@ -747,23 +843,24 @@ static int launch_flash_bwd(const void* q, long long q_tstride, long long q_bstr
       return -5;
   }
   constexpr size_t smem_dkdv = 1024 + 2 * (kKvRows * D * 2) + 2 * kQStages * (kQSub * D * 2) + kQStages * (4 * kQSub * 4) + 256;
-  constexpr size_t smem_dq = 1024 + 6 * (128 * D * 2) + 2 * (2 * kDqKeys * 4) + 256;
-  static bool configured[64] = {false};
+  constexpr int k_stages = (D == 128) ? (MODE >= 2 ? 2 : 3) : 4;
+  constexpr size_t smem_dq = (4 + k_stages) * (128 * D * 2) + (MODE >= 2 ? k_stages : 0) * (2 * kDqKeys * 4) + 256;
+  static bool configured[64] = {false};   // one flag set per (D, MODE) instantiation
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    MB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_dkdv)));
-    MB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_dq)));
+    MB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_dkdv)));
+    MB_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_dq_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_dq)));
     configured[dev & 63] = true;
   }
   {
     dim3 grid((a.Sk + kKvRows - 1) / kKvRows, a.Hkv, a.B);
-    flash_bwd_dkdv_kernel<D><<<grid, kBwThreads, smem_dkdv, stream>>>(tmQ64, tmDO64, tmK, tmV, a);
+    flash_bwd_dkdv_kernel<D, MODE><<<grid, kBwThreads, smem_dkdv, stream>>>(tmQ64, tmDO64, tmK, tmV, a);
     count_launch();
   }
   {
     dim3 grid((a.Sq + kDqRows - 1) / kDqRows, a.Hq, a.B);
-    flash_bwd_dq_kernel<D><<<grid, kBwThreads, smem_dq, stream>>>(tmQ128, tmDO128, tmK, tmV, a);
+    flash_bwd_dq_kernel<D, MODE><<<grid, kBwThreads, smem_dq, stream>>>(tmQ128, tmDO128, tmK, tmV, a);
     count_launch();
   }
   MB_CHECK_CUDA(cudaGetLastError());
@@ -771,6 +868,12 @@ static int launch_flash_bwd(const void* q, long long q_tstride, long long q_bstr
 }
 
 }  // namespace mb
+
+#ifdef MB_FLASH_PROBE
+MB_API int mb_flash_probe_read(long long* host_out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mb::g_flash_probe, sizeof(long long) * 16 * 256));
+}
+#endif
 
 // Number of 4-byte words of scratch memory mb_flash_attn_bwd needs for these sizes.
 MB_API long long mb_flash_attn_bwd_scratch_words(int B, int Sq, int Sk, int Hq) {
@@ -820,9 +923,24 @@ MB_API int mb_flash_attn_bwd(const void* q, long long q_tstride, long long q_bst
   a.mode = mode, a.out_fp32 = out_fp32, a.accumulate = accumulate;
   a.scale = scale, a.scale_log2 = scale * kBwLog2e;
   a.status = status;
-  if (D == 128)
-    return launch_flash_bwd<128>(q, q_tstride, q_bstride, k, v, kv_tstride, kv_bstride, out, o_tstride, o_bstride, dout, do_tstride,
-                                 do_bstride, lse, q_pos, k_pos, q_seq, k_seq, scratch, a, stream);
-  return launch_flash_bwd<64>(q, q_tstride, q_bstride, k, v, kv_tstride, kv_bstride, out, o_tstride, o_bstride, dout, do_tstride,
-                              do_bstride, lse, q_pos, k_pos, q_seq, k_seq, scratch, a, stream);
+#ifdef MB_FLASH_PROBE
+  a.dbg = getenv("MB_FLASH_DBG") ? atoi(getenv("MB_FLASH_DBG")) : 0;
+#endif
+#define MB_BWD_ARGS q, q_tstride, q_bstride, k, v, kv_tstride, kv_bstride, out, o_tstride, o_bstride, dout, do_tstride, do_bstride, \
+                    lse, q_pos, k_pos, q_seq, k_seq, scratch, a, stream
+  if (D == 128) {
+    switch (mode) {
+      case 0: return launch_flash_bwd<128, 0>(MB_BWD_ARGS);
+      case 1: return launch_flash_bwd<128, 1>(MB_BWD_ARGS);
+      case 2: return launch_flash_bwd<128, 2>(MB_BWD_ARGS);
+      default: return launch_flash_bwd<128, 3>(MB_BWD_ARGS);
+    }
+  }
+  switch (mode) {
+    case 0: return launch_flash_bwd<64, 0>(MB_BWD_ARGS);
+    case 1: return launch_flash_bwd<64, 1>(MB_BWD_ARGS);
+    case 2: return launch_flash_bwd<64, 2>(MB_BWD_ARGS);
+    default: return launch_flash_bwd<64, 3>(MB_BWD_ARGS);
+  }
+#undef MB_BWD_ARGS
 }

@@ -62,7 +62,8 @@ def test_upload_plan_validation(tmp_path):
 
 
 def test_bench_micro_batch_defaults():
-    """The benchmark's micro-batch default: 2 for this framework on one GPU, 1 everywhere else; explicit values win."""
+    """The benchmark's micro-batch default is the same for both arms: 2 on one GPU (with a fallback to 1 when it does not
+    fit), 1 on several GPUs; explicit values win and switch the fallback off."""
     import importlib.util
     from pathlib import Path
 
@@ -71,6 +72,9 @@ def test_bench_micro_batch_defaults():
     spec.loader.exec_module(bench)
     assert bench.parse_args([]).micro_batch == 2
     assert bench.parse_args(["--gpus", "4"]).micro_batch == 1
-    assert bench.parse_args(["--impl", "reference"]).micro_batch == 1
+    ref = bench.parse_args(["--impl", "reference"])
+    assert ref.micro_batch == 2 and ref.micro_batch_auto
+    assert bench.parse_args(["--impl", "reference", "--gpus", "8"]).micro_batch == 1
+    assert not bench.parse_args(["--micro-batch", "2"]).micro_batch_auto
     assert bench.parse_args(["--small"]).micro_batch == 1
     assert bench.parse_args(["--micro-batch", "4"]).micro_batch == 4
