@@ -41,13 +41,16 @@ __device__ __forceinline__ void st_logit<float>(float* p, long long i, float v) 
 
 // One block per row. loss_rows[row] = lse - logit[label] (0 for ignored rows); lse_out[row] = log-sum-exp.
 // If grad_out != nullptr: grad_out[row, :] = (softmax - onehot) * scale_row, where
-// scale_row = (label != ignore) * (*grad_scale_ptr), written in place when grad_out == logits.
+// scale_row = (label != ignore) * (*grad_scale_ptr). grad_out may BE logits (in place): every thread rewrites only the
+// columns it read itself, and the target logit needed for the loss is captured during the first pass, before any
+// column is overwritten. (logits is therefore not declared __restrict__.)
 template <typename T>
 __global__ void __launch_bounds__(kCeThreads)
-cross_entropy_kernel(const T* __restrict__ logits, long long row_stride, const long long* __restrict__ labels,
+cross_entropy_kernel(const T* logits, long long row_stride, const long long* __restrict__ labels,
                      float* __restrict__ loss_rows, float* __restrict__ lse_out, T* grad_out,
                      const float* __restrict__ grad_scale_ptr, int V, long long ignore_index, int* status) {
   __shared__ float red_m[kCeThreads / 32], red_s[kCeThreads / 32];
+  __shared__ float target_logit;
   const long long row = blockIdx.x;
   const T* lr = logits + row * row_stride;
   const long long label = labels[row];
@@ -62,6 +65,7 @@ cross_entropy_kernel(const T* __restrict__ logits, long long row_stride, const l
   float m = -INFINITY, s = 0.f;
   for (int c = threadIdx.x; c < V; c += kCeThreads) {
     const float v = ld_logit<T>(lr, c);
+    if (c == label) target_logit = v;      // exactly one thread of the block owns the target column
     if (v > m) {
       s = s * __expf(m - v) + 1.f;
       m = v;
@@ -92,7 +96,7 @@ cross_entropy_kernel(const T* __restrict__ logits, long long row_stride, const l
   if (threadIdx.x == 0) {
     if (lse_out) lse_out[row] = lse;
     float lrow = 0.f;
-    if (active && label >= 0 && label < V) lrow = lse - ld_logit<T>(lr, label);
+    if (active && label >= 0 && label < V) lrow = lse - target_logit;
     loss_rows[row] = lrow;
   }
   if (grad_out) {

@@ -68,7 +68,11 @@ class _LinearCrossEntropy(torch.autograd.Function):
         inv = (1.0 / count.clamp_min(1).to(torch.float32)).reshape(1)
         loss_rows = torch.empty(N, device=h.device, dtype=torch.float32)
         dh = torch.empty_like(h) if need_dh else None
-        dw = torch.zeros_like(weight) if need_dw else None
+        # several token chunks add into dW: the running sum stays in fp32 and is rounded to the weight's dtype once
+        n_chunks = (N + chunk_tokens - 1) // chunk_tokens
+        dw = None
+        if need_dw:
+            dw = torch.zeros(weight.shape, device=weight.device, dtype=torch.float32 if n_chunks > 1 else weight.dtype)
         want_grad = need_dh or need_dw
         logits_buf = torch.empty((min(chunk_tokens, N), V), device=h.device, dtype=h.dtype)
         for start in range(0, N, chunk_tokens):
@@ -81,6 +85,8 @@ class _LinearCrossEntropy(torch.autograd.Function):
                 gemm(lg, weight, b_mn=True, out=dh[start:start + n])          # dlogits[n,V] @ W[V,H]
             if need_dw:
                 gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)   # dlogits^T[V,n] @ h[n,H]
+        if dw is not None and dw.dtype != weight.dtype:
+            dw = dw.to(weight.dtype)
         ctx.save_for_backward(dh, dw)
         return _sum_over_group(loss_rows.sum() * inv.squeeze(0), group)
 

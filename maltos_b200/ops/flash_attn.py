@@ -30,8 +30,19 @@ class _FlashAttention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, mode, q_pos, k_pos, q_seq, k_seq, scale):
-        out, lse = flash_forward(q, k, v, mode=mode, q_positions=q_pos, k_positions=k_pos, q_sequence_ids=q_seq,
-                                 k_sequence_ids=k_seq, scale=scale)
+        # Under activation checkpointing the original forward keeps (out, lse) for the recompute: the backward needs
+        # exactly these two and nothing else of the forward, so the recompute pass launches no attention kernel.
+        from maltos_b200.utils.activation_checkpoint import current_checkpoint_stash
+
+        stash = current_checkpoint_stash()
+        kept = stash.replay() if stash is not None and stash.replaying else None
+        if kept is not None and kept[0].shape == q.shape:
+            out, lse = kept
+        else:
+            out, lse = flash_forward(q, k, v, mode=mode, q_positions=q_pos, k_positions=k_pos, q_sequence_ids=q_seq,
+                                     k_sequence_ids=k_seq, scale=scale)
+            if stash is not None and not stash.replaying:
+                stash.record((out, lse))
         ctx.save_for_backward(q, k, v, out, lse, *(t for t in (q_pos, k_pos, q_seq, k_seq) if t is not None))
         ctx.has = tuple(t is not None for t in (q_pos, k_pos, q_seq, k_seq))
         ctx.mode, ctx.scale = mode, scale

@@ -8,8 +8,13 @@ double-buffered by call parity and a "consumed" flag keeps a fast rank from over
 
 ``linear_reduce_scatter`` / the input gradient of ``all_gather_grouped_linear``: GEMM and reduce-scatter are one GEMM
 launch whose epilogue stores partial tiles into the owner rank's staging slots over NVLink, plus a small reduce kernel
-(:func:`gemm_reduce_scatter`). The remaining backward collectives (re-gather of ``x`` for the weight gradient, gather of
-``dy`` of row-parallel layers) use NCCL around the tcgen05 GEMMs.
+(:func:`gemm_reduce_scatter`).
+
+In groups above four ranks (two for the reduce-scatter) the in-kernel push does not pay: there the collectives are the
+one-sided PULL kernels of ``csrc/tp_pull.cu`` (:func:`gemm_reduce_scatter_pull`, :func:`all_gather_pull`): the GEMM
+writes its partial result into this rank's symmetric buffer and the owner of a sequence slice reads it from all ranks
+with the whole grid's loads in flight; the all-gather publishes the local rows and pulls the peers' rows the same way.
+NCCL is only the fallback for ranks without peer access (and ``MALTOS_B200_TP_PULL=0`` for A/B timing).
 """
 from __future__ import annotations
 
@@ -53,6 +58,72 @@ def _nccl_reduce_scatter_rows(y_full: torch.Tensor, ctx, B: int, rows: int) -> t
         if w is not None:
             w.wait()
     return out
+
+
+def _pull_ok(symm) -> bool:
+    return symm is not None and symm.world in (2, 4, 8) and os.environ.get("MALTOS_B200_TP_PULL", "1") != "0"
+
+
+def _peer_table(ptrs, offset_bytes: int = 0):
+    return (ctypes.c_ulonglong * 8)(*([p + offset_bytes for p in ptrs] + [0] * (8 - len(ptrs))))
+
+
+def gemm_reduce_scatter_pull(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool) -> torch.Tensor:
+    """``reduce_scatter_over_ranks(x2 @ op(w))`` along the sequence: the GEMM writes its bf16 partial ``[B*S, N]`` into this
+    rank's symmetric buffer, then ONE kernel (``csrc/tp_pull.cu``) exchanges the "partial complete" flags and lets the
+    owner of each sequence slice read it from every rank over NVLink and sum in fp32. Returns ``[B*rows, N]``."""
+    T = symm.world
+    N = w.shape[1] if b_mn else w.shape[0]
+    M = B * rows * T
+    stage = symm.ensure_buffer("sp_partial", 2 * M * N * 2)
+    half = stage.nbytes // 2 // 256 * 256
+    seq = symm.next_seq("pull_scatter")
+    off = (seq & 1) * half
+    partial = stage.local_tensor(torch.bfloat16, stage.nbytes // 2, x2.device)[off // 2: off // 2 + M * N].view(M, N)
+    gemm(x2, w, b_mn=b_mn, out=partial)
+    out = torch.empty((B * rows, N), dtype=torch.bfloat16, device=x2.device)
+    rc = _lib.lib().mb_pull_reduce_scatter_bf16(_peer_table(stage.peer_ptrs, off), _peer_table(symm.pad.peer_ptrs), _lib.ptr(out),
+                                                _lib.c_int(B), _lib.c_ll(rows), _lib.c_ll(N), _lib.c_int(symm.rank), _lib.c_int(T),
+                                                ctypes.c_uint(seq & 0xFFFFFFFF), _lib.stream_ptr())
+    _lib.check(rc, "mb_pull_reduce_scatter_bf16")
+    return out
+
+
+def all_gather_pull(x2: torch.Tensor, symm, B: int, rows: int) -> torch.Tensor:
+    """``[B*rows, K]`` local rows -> ``[B*rows*T, K]`` (batch-major, rank-minor) with ONE kernel: publish the local rows in
+    symmetric memory, exchange flags, pull the peers' rows over NVLink. The result is an ordinary tensor."""
+    T = symm.world
+    K = x2.shape[1]
+    x2 = x2.contiguous()
+    nbytes = B * rows * K * 2
+    pub = symm.ensure_buffer("sp_publish", 2 * nbytes)
+    half = pub.nbytes // 2 // 256 * 256
+    seq = symm.next_seq("pull_gather")
+    off = (seq & 1) * half
+    out = torch.empty((B * rows * T, K), dtype=torch.bfloat16, device=x2.device)
+    rc = _lib.lib().mb_pull_all_gather_bf16(_lib.ptr(x2), _peer_table(pub.peer_ptrs, off), _peer_table(symm.pad.peer_ptrs), _lib.ptr(out),
+                                            _lib.c_int(B), _lib.c_ll(rows), _lib.c_ll(K), _lib.c_int(symm.rank), _lib.c_int(T),
+                                            ctypes.c_uint(seq & 0xFFFFFFFF), _lib.stream_ptr())
+    _lib.check(rc, "mb_pull_all_gather_bf16")
+    return out
+
+
+def gather_rows(x2: torch.Tensor, symm, B: int, rows: int) -> torch.Tensor:
+    """Sequence all-gather of ``[B*rows, K]`` rows: the pull kernel over peer memory, NCCL only without it."""
+    if _pull_ok(symm) and x2.dtype == torch.bfloat16 and x2.is_cuda and (rows * x2.shape[1]) % 8 == 0:
+        return all_gather_pull(x2, symm, B, rows)
+    return _nccl_all_gather_rows(x2, symm, B, rows)
+
+
+def reduce_scatter_gemm(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool) -> torch.Tensor:
+    """``reduce_scatter(x2 @ op(w))`` by the best path for the group: GEMM epilogue push (two ranks), GEMM + pull kernel
+    (larger groups), GEMM + NCCL (no peer memory)."""
+    n_out = w.shape[1] if b_mn else w.shape[0]
+    if _fused_scatter_ok(symm, x2, n_out):
+        return gemm_reduce_scatter(x2, w, symm, B, rows, b_mn=b_mn)
+    if _pull_ok(symm) and x2.dtype == torch.bfloat16 and x2.is_cuda and (rows * n_out) % 8 == 0:
+        return gemm_reduce_scatter_pull(x2, w, symm, B, rows, b_mn=b_mn)
+    return _nccl_reduce_scatter_rows(gemm(x2, w, b_mn=b_mn), symm, B, rows)
 
 
 def gemm_reduce_scatter(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool) -> torch.Tensor:
@@ -120,9 +191,9 @@ def _fused_gather_ok(symm, M: int, N: int, K: int) -> bool:
 
 
 def all_gather_gemm_unfused(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool):
-    """Same contract as :func:`all_gather_gemm` with an NCCL all-gather in front of a plain GEMM launch; ``gathered`` is an
-    ordinary tensor."""
-    x_full = _nccl_all_gather_rows(x2, symm, B, rows)
+    """Same contract as :func:`all_gather_gemm` with the all-gather as a launch of its own (pull kernel over peer memory,
+    NCCL without it) in front of a plain GEMM launch; ``gathered`` is an ordinary tensor."""
+    x_full = gather_rows(x2, symm, B, rows)
     return gemm(x_full, w, b_mn=b_mn), x_full
 
 
@@ -198,13 +269,9 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         dx_local = None
         dws = [None] * len(weights)
         if ctx.needs_input_grad[0]:
-            if _fused_scatter_ok(symm, d2, K):
-                dx_local = gemm_reduce_scatter(d2, fused, symm, B, rows, b_mn=True).view(B, rows, K)
-            else:
-                dx_full = gemm(d2, fused, b_mn=True)                   # [B*S, K]
-                dx_local = _nccl_reduce_scatter_rows(dx_full, symm, B, rows).view(B, rows, K)
+            dx_local = reduce_scatter_gemm(d2, fused, symm, B, rows, b_mn=True).view(B, rows, K)
         if any(ctx.needs_input_grad[2:]):
-            x_full = x_kept if x_kept is not None else _nccl_all_gather_rows(x2, symm, B, rows)
+            x_full = x_kept if x_kept is not None else gather_rows(x2, symm, B, rows)
             dwf = gemm(d2, x_full, a_mn=True, b_mn=True)               # [N, K]
             at = 0
             for i in ctx.layout:
@@ -236,11 +303,7 @@ class _LinearReduceScatter(torch.autograd.Function):
         T = symm.world
         rows = S // T
         x2 = x.reshape(B * S, Kin)
-        if _fused_scatter_ok(symm, x2, weight.shape[0]):
-            y = gemm_reduce_scatter(x2, weight, symm, B, rows, b_mn=False)
-        else:
-            y_full = gemm(x2, weight)                                   # partial sums [B*S, H]
-            y = _nccl_reduce_scatter_rows(y_full, symm, B, rows)
+        y = reduce_scatter_gemm(x2, weight, symm, B, rows, b_mn=False)
         ctx.save_for_backward(x2, weight)
         ctx.symm, ctx.dims = symm, (B, S, rows, Kin)
         return y.view(B, rows, weight.shape[0])
@@ -257,7 +320,7 @@ class _LinearReduceScatter(torch.autograd.Function):
             dx_full, dy_full = all_gather_gemm(dy2, weight, ctx.symm, B, rows, b_mn=True)
             dx = dx_full.view(B, S, Kin)
         else:
-            dy_full = _nccl_all_gather_rows(dy2, ctx.symm, B, rows)   # [B*S, H]
+            dy_full = gather_rows(dy2, ctx.symm, B, rows)   # [B*S, H]
             dx = gemm(dy_full, weight, b_mn=True).view(B, S, Kin) if ctx.needs_input_grad[0] else None
         dw = gemm(dy_full, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
         return dx, dw, None

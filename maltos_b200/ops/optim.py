@@ -50,7 +50,7 @@ def adamw_multi_tensor(items, *, lr: float, beta1: float, beta2: float, eps: flo
             _adamw_reference(p.data, g, m, v, lowp.data if lowp is not None else None, step, lr, beta1, beta2, eps, weight_decay, grad_scale)
         return
     device = items[0][0].device
-    rows, corr = [], []
+    rows, corr, keep = [], [], []
     first = 0
     for p, g, m, v, lowp, step in items:
         if p.dtype != torch.float32 or m.dtype != torch.float32 or v.dtype != torch.float32:
@@ -60,7 +60,10 @@ def adamw_multi_tensor(items, *, lr: float, beta1: float, beta2: float, eps: flo
         if not (p.is_contiguous() and m.is_contiguous() and v.is_contiguous()):
             raise ValueError("adamw_multi_tensor: params and moments must be contiguous")
         if not g.is_contiguous():
+            # the copy's address goes into the table: it must stay allocated until the launch below has been queued,
+            # otherwise the next temporary of this loop could reuse its block and two rows would alias
             g = g.contiguous()
+            keep.append(g)
         if lowp is not None and (lowp.dtype != torch.bfloat16 or not lowp.is_contiguous()):
             raise TypeError("adamw_multi_tensor: low-precision params must be contiguous bf16")
         n = p.numel()
@@ -76,6 +79,8 @@ def adamw_multi_tensor(items, *, lr: float, beta1: float, beta2: float, eps: flo
     # the launch is asynchronous: keep the tables alive until the stream has consumed them
     table.record_stream(torch.cuda.current_stream())
     bias.record_stream(torch.cuda.current_stream())
+    for t in keep:
+        t.record_stream(torch.cuda.current_stream())
 
 
 def _vec_table(tensors, weights, device):

@@ -103,7 +103,10 @@ class MasterWeightsOptimizer(torch.optim.Optimizer):
         self._adopt_inner()
         self._master_grads_copied = False
         self._fused = isinstance(self._optimizer, FusedAdamW)
-        if self._fused:
+        # fp16 runs go through a GradScaler, which unscales and inf-checks `.grad` of the optimizer's own (master)
+        # parameters: there the fp32 master-gradient copies are kept and the fused kernel consumes those.
+        self._direct_grads = self._fused and self.model_params[0].dtype == torch.bfloat16
+        if self._direct_grads:
             self._optimizer.low_precision_params = {id(m): p for p, m in zip(self.model_params, self.master_params)}
 
     def _adopt_inner(self) -> None:
@@ -119,7 +122,7 @@ class MasterWeightsOptimizer(torch.optim.Optimizer):
         return self._model_by_master.get(id(param), param)
 
     def _fused_on_device(self) -> bool:
-        return self._fused and self.model_params[0].is_cuda
+        return self._direct_grads and self.model_params[0].is_cuda
 
     def copy_master_params(self) -> None:
         """Make the model gradients visible to the inner optimizer (fp32 copies, or by reference when fused)."""

@@ -164,3 +164,35 @@ def test_autograd_entry_point_strided_qkv_and_zigzag_positions():
     _close(dq, rq), _close(dk, rk), _close(dv, rv)
     assert float(dq[:, :chunk].abs().max()) == 0.0            # rows that see no key
     _lib.fetch_status()
+
+
+def test_checkpointed_layer_replays_attention_instead_of_recomputing_it():
+    """Under activation checkpointing the original forward keeps attention's output and log-sum-exp; the recompute pass
+    then launches no attention forward, and the gradients equal those of the plain (non-checkpointed) run."""
+    from torch.utils.checkpoint import checkpoint
+
+    from maltos_b200.utils.activation_checkpoint import activation_checkpoint_context_fn
+
+    B, S, Hq, Hkv, D = 1, 256, 4, 2, 128
+    q0, k0, v0 = _qkv(B, S, S, Hq, Hkv, D, seed=9)
+    w = torch.randn(D, D, device=DEV).bfloat16()
+
+    def layer(q, k, v):
+        return flash_attention(q @ w, k, v, causal=True).float().square().mean()
+
+    def run(use_ckpt):
+        q, k, v = (t.clone().requires_grad_(True) for t in (q0, k0, v0))
+        before = _lib.launch_count()
+        if use_ckpt:
+            loss = checkpoint(layer, q, k, v, use_reentrant=False, preserve_rng_state=False, context_fn=activation_checkpoint_context_fn)
+        else:
+            loss = layer(q, k, v)
+        loss.backward()
+        return _lib.launch_count() - before, q.grad, k.grad, v.grad
+
+    n_plain, *g_plain = run(False)
+    n_ckpt, *g_ckpt = run(True)
+    assert n_ckpt == n_plain                      # one forward + three backward launches in both runs
+    for a, b in zip(g_plain, g_ckpt):
+        assert torch.equal(a, b)
+    _lib.fetch_status()

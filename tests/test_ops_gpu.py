@@ -206,6 +206,25 @@ def test_adamw_and_norm_kernels():
     _lib.fetch_status()
 
 
+def test_adamw_takes_non_contiguous_gradients_of_equal_size():
+    """Two same-sized transposed gradients: their contiguous copies are temporaries whose addresses go into the launch
+    table, so both must stay allocated until the launch (a freed block would be reused by the second copy)."""
+    from maltos_b200.ops.optim import _adamw_reference
+
+    torch.manual_seed(11)
+    ps = [torch.randn(64, 48, device=DEV) for _ in range(3)]
+    gs = [torch.randn(48, 64, device=DEV).t() for _ in range(3)]
+    assert not gs[0].is_contiguous()
+    ms, vs = [torch.zeros_like(p) for p in ps], [torch.zeros_like(p) for p in ps]
+    ref = [(p.clone(), torch.zeros_like(p), torch.zeros_like(p)) for p in ps]
+    adamw_multi_tensor([(p, g, m, v, None, 1.0) for p, g, m, v in zip(ps, gs, ms, vs)], lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                       weight_decay=0.1)
+    for (rp, rm, rv), g, p in zip(ref, gs, ps):
+        _adamw_reference(rp, g.contiguous(), rm, rv, None, 1.0, 1e-2, 0.9, 0.95, 1e-8, 0.1, None)
+        assert (p - rp).abs().max().item() < 1e-5
+    _lib.fetch_status()
+
+
 @pytest.mark.parametrize("D,Hq,Hkv", [(64, 8, 2), (128, 4, 4)])
 def test_causal_attention_matches_fp32_reference(D, Hq, Hkv):
     from maltos_b200.ops.attention import attention_reference, causal_attention

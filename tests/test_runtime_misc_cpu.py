@@ -118,3 +118,23 @@ def test_cuda_graph_plugin_refuses_communicating_plugins():
     rt.close()
     with pytest.raises(ValueError, match="single-process"):
         RuntimeCore(model=model(), plugins=[CudaGraphPlugin(), Zero1Plugin()], optimizer_factory=opt).setup()
+
+
+def test_fp16_master_weights_with_fused_adamw_keeps_master_gradients():
+    """fp16 runs unscale and inf-check the optimizer's own gradients through a GradScaler, so with fp16 parameters the
+    fused AdamW consumes fp32 master-gradient copies instead of taking the model gradients by reference."""
+    from maltos_b200.runtime.optim import FusedAdamW, MasterWeightsOptimizer
+
+    torch.manual_seed(0)
+    for dtype, direct in ((torch.float16, False), (torch.bfloat16, True)):
+        w = torch.nn.Parameter(torch.randn(8, 4).to(dtype))
+        opt = MasterWeightsOptimizer([w], optimizer_factory=lambda ps: FusedAdamW(ps, lr=1e-2, weight_decay=0.0))
+        assert opt._direct_grads is direct
+        w.grad = torch.ones_like(w)
+        opt.copy_master_params()
+        master = opt.master_params[0]
+        assert master.grad is not None and master.grad.dtype == torch.float32      # CPU: copies in both cases
+        before = w.detach().clone()
+        opt.step()
+        assert not torch.equal(w.detach(), before) and w.dtype == dtype
+        assert torch.allclose(w.detach().float(), master.detach(), atol=1e-2)
