@@ -265,7 +265,9 @@ class _AllGatherGroupedLinear(torch.autograd.Function):
         d2 = dout.reshape(-1, N)
         if d2.stride(1) != 1 or d2.stride(0) % 8:
             d2 = d2.contiguous()
-        fused = _fused_view(weights, ctx.layout) if ctx.fused_ok else torch.cat(list(weights), dim=0)
+        # re-checked here: sharded parameters may have been re-materialised at other addresses since the forward
+        still_adjacent = ctx.fused_ok and _memory_order(weights) == ctx.layout
+        fused = _fused_view(weights, ctx.layout) if still_adjacent else torch.cat([weights[i] for i in ctx.layout], dim=0)
         dx_local = None
         dws = [None] * len(weights)
         if ctx.needs_input_grad[0]:

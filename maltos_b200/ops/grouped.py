@@ -100,7 +100,9 @@ class _GroupedLinear(torch.autograd.Function):
         dx = None
         dws: list = [None] * len(weights)
         if ctx.fused:
-            fused = _fused_view(weights, layout)
+            # the members may have been re-materialised elsewhere since the forward (sharded parameters): the zero-copy
+            # view is only valid if they still tile one region in the same order, otherwise pack a copy
+            fused = _fused_view(weights, layout) if _memory_order(weights) == layout else torch.cat([weights[i] for i in layout], dim=0)
             if need_x:
                 dx = gemm(d2, fused, b_mn=True).view(ctx.xshape)
             if need_w:

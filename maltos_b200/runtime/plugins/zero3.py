@@ -7,11 +7,15 @@ Buckets (this order is part of the checkpoint format, reference ``runtime/plugin
 Each bucket is a flat padded buffer whose ``1/N`` slice is this rank's ``local_param`` (what the optimizer updates and
 what ``zero3_bucket_{i}`` stores in a checkpoint).
 
-Execution: a forward-pre hook of the bucket's module all-gathers the slices into a pooled buffer and binds the
-parameters to views of it, the forward hook releases them; a backward-pre hook gathers again for the backward pass;
-when the last gradient of the bucket has been produced the flat gradient is reduce-scattered (AVG x correction) and
-added to the slice gradient, and the full parameters are released. Gradients accumulate on the slices, so the
-reduce-scatter runs every micro-step. Recompute under activation checkpointing re-enters the same hooks.
+Execution: a forward-pre hook of the bucket's module waits for the (asynchronous) all-gather of the slices into a
+pooled buffer, binds the parameters to views of it and starts the gather of the NEXT bucket in execution order, so that
+the transfer runs under this bucket's compute; the forward hook releases the parameters. A backward-pre hook does the
+same in reverse (prefetching the PREVIOUS bucket). The execution order is observed during the first forward. When the
+last gradient of a bucket has been produced the flat gradient is reduce-scattered asynchronously (AVG x correction); the
+results are added to the slice gradients at POST_BACKWARD, after the whole backward pass has been queued. Gradients
+accumulate on the slices, so the reduce-scatter runs every micro-step. Recompute under activation checkpointing
+re-enters the same hooks. Reference: ``runtime/plugins/zero3.py:384-450`` (prefetch), ``:452-490`` (asynchronous gather),
+``:505-544`` (asynchronous reduce-scatter). ``MALTOS_B200_ZERO3_PREFETCH=0`` makes every collective synchronous.
 """
 from __future__ import annotations
 
@@ -48,13 +52,16 @@ class ShardedBucket:
     padded: int
     local_param: nn.Parameter = None
     logical_names: list[str] = field(default_factory=list)
-    full_handle: object = None      # pooled buffer holding the gathered parameters while materialized
+    full_tensor: torch.Tensor | None = None   # flat gathered parameters; its storage has zero bytes while released
+    is_materialized: bool = False
     grad_flat: torch.Tensor | None = None
     grad_handle: object = None
     grads_pending: int = 0
     users: int = 0                  # nested materialisations (recompute inside backward)
     hook_module: nn.Module = None   # module whose forward/backward brackets the use of these parameters
     peer_shard_ptrs: list[int] | None = None   # peer-memory mode: address of every rank's shard of this bucket
+    gather_work: object = None      # handle of the all-gather in flight into full_handle (None once bound)
+    prefetched: bool = False        # gathered ahead of use and not yet claimed by a hook
 
     @property
     def shard_numel(self) -> int:
@@ -62,7 +69,7 @@ class ShardedBucket:
 
     @property
     def materialized(self) -> bool:
-        return self.full_handle is not None
+        return self.is_materialized
 
 
 class Zero3Plugin(ZeroPluginBase):
@@ -77,6 +84,12 @@ class Zero3Plugin(ZeroPluginBase):
         self._barrier_tokens: dict[int, torch.Tensor] = {}
         self._by_param: dict[int, ShardedBucket] = {}
         self._placeholder: dict[int, torch.Tensor] = {}
+        self.prefetch = os.environ.get("MALTOS_B200_ZERO3_PREFETCH", "1") != "0"
+        self._order: list[int] = []            # bucket indices in the order the first forward used them
+        self._order_pos: dict[int, int] = {}
+        self._order_final = False
+        self._unclaimed: list[ShardedBucket] = []     # prefetched buckets nobody has used yet (oldest first)
+        self._reduces: list[tuple] = []        # (bucket, work, piece, grad handle) of reduce-scatters in flight
 
     # ------------------------------------------------------------------ setup
     def bind(self, runtime) -> None:
@@ -197,14 +210,22 @@ class Zero3Plugin(ZeroPluginBase):
             dist.all_reduce(tok, group=group)
 
     # ------------------------------------------------------------------ gather / release
-    def _gather(self, b: ShardedBucket) -> None:
-        b.users += 1
+    def _start_gather(self, b: ShardedBucket) -> None:
+        """Launch the all-gather of the bucket into a pooled buffer without waiting for it."""
         if b.materialized:
             return
         gc = b.group_context
         lp = b.local_param
-        b.full_handle = acquire_buffer(shape=(b.padded,), dtype=lp.dtype, device=lp.device, policy=BufferPolicy.CACHEABLE)
-        full = b.full_handle.tensor
+        # The gathered parameters of a bucket always live in the SAME storage object, grown to full size here and shrunk
+        # to zero bytes on release: autograd may have saved a view of a weight (``weight.t()`` of a decomposed linear) in
+        # the forward pass, and such a view must see the re-gathered values in the backward pass wherever the allocator
+        # places them.
+        if b.full_tensor is None:
+            b.full_tensor = torch.empty(b.padded, dtype=lp.dtype, device=lp.device)
+        else:
+            b.full_tensor.untyped_storage().resize_(b.padded * lp.element_size())
+        b.is_materialized = True
+        full = b.full_tensor
         with torch.no_grad():
             if gc.group is None or gc.world_size == 1:
                 full.copy_(lp.data)
@@ -213,18 +234,64 @@ class Zero3Plugin(ZeroPluginBase):
 
                 peer_gather(full, b.peer_shard_ptrs, b.shard_numel * 2)
             else:
-                all_gather_single(full, lp.data.contiguous(), group=gc.group)
+                b.gather_work = all_gather_single(full, lp.data.contiguous(), group=gc.group, async_op=self.prefetch)
+
+    def _finish_gather(self, b: ShardedBucket) -> None:
+        """Wait for the gather in flight (the current stream waits, not the host, on NCCL) and bind the parameter views."""
+        if b.gather_work is not None:
+            b.gather_work.wait()
+            b.gather_work = None
+        full = b.full_tensor
         for p, off, n, shape in zip(b.params, b.offsets, b.param_numels, b.param_shapes):
             p.data = full[off:off + n].view(shape)
+
+    def _gather(self, b: ShardedBucket) -> None:
+        b.users += 1
+        if b.prefetched:
+            b.prefetched = False
+            if b in self._unclaimed:
+                self._unclaimed.remove(b)
+        if b.materialized and b.gather_work is None and b.params[0].data.numel() > 0:
+            return
+        self._start_gather(b)
+        self._finish_gather(b)
+
+    def _prefetch(self, b: ShardedBucket | None) -> None:
+        """Start gathering a bucket that the execution order says comes next. A prefetched bucket that is never claimed
+        (the order ran past the end of a recomputed block) is dropped once two newer ones are waiting."""
+        if b is None or not self.prefetch or b.materialized:
+            return
+        self._start_gather(b)
+        b.prefetched = True
+        self._unclaimed.append(b)
+        while len(self._unclaimed) > 2:
+            stale = self._unclaimed.pop(0)
+            if stale.users == 0 and stale.prefetched:
+                stale.prefetched = False
+                self._release(stale, force=True)
+
+    def _neighbour(self, b: ShardedBucket, step: int):
+        if not self._order_final:
+            return None
+        pos = self._order_pos.get(b.index)
+        if pos is None or not (0 <= pos + step < len(self._order)):
+            return None
+        return self.buckets[self._order[pos + step]]
 
     def _release(self, b: ShardedBucket, *, force: bool = False) -> None:
         b.users = 0 if force else max(b.users - 1, 0)
         if b.users > 0 or not b.materialized:
             return
+        if b.gather_work is not None:      # never hand a buffer back while a collective still writes it
+            b.gather_work.wait()
+            b.gather_work = None
+        b.prefetched = False
+        if b in self._unclaimed:
+            self._unclaimed.remove(b)
         for p in b.params:
             p.data = self._placeholder[id(p)]
-        release_buffer(b.full_handle)
-        b.full_handle = None
+        b.full_tensor.untyped_storage().resize_(0)
+        b.is_materialized = False
 
     def materialize_model(self) -> None:
         """Gather every bucket (tests / export). Pair with :meth:`reshard_model`."""
@@ -259,7 +326,11 @@ class Zero3Plugin(ZeroPluginBase):
     def _pre_forward(self, b: ShardedBucket):
         def hook(module, args):
             with span("maltos::zero3.materialize.forward"):
+                if not self._order_final and b.index not in self._order_pos:
+                    self._order_pos[b.index] = len(self._order)
+                    self._order.append(b.index)
                 self._gather(b)
+                self._prefetch(self._neighbour(b, +1))
 
         return hook
 
@@ -272,8 +343,9 @@ class Zero3Plugin(ZeroPluginBase):
     def _pre_backward(self, b: ShardedBucket):
         def hook(module, grad_output):
             with span("maltos::zero3.materialize.backward"):
-                if not b.materialized:
+                if not b.materialized or b.prefetched or b.gather_work is not None:
                     self._gather(b)
+                self._prefetch(self._neighbour(b, -1))
                 if b.grads_pending <= 0:
                     b.grads_pending = sum(1 for p in b.params if p.requires_grad)
 
@@ -300,27 +372,38 @@ class Zero3Plugin(ZeroPluginBase):
         return hook
 
     def _reduce(self, b: ShardedBucket) -> None:
+        """Launch the reduce-scatter of the bucket's flat gradient; :meth:`_finish_reduces` adds the result to the slice."""
         gc = b.group_context
-        lp = b.local_param
         flat = b.grad_flat
+        if gc.correction != 1.0:
+            flat.mul_(gc.correction)
         if gc.group is None or gc.world_size == 1:
-            if gc.correction != 1.0:
-                flat.mul_(gc.correction)
-            piece = flat[: b.shard_numel]
+            self._reduces.append((b, None, flat[: b.shard_numel], b.grad_handle))
         else:
-            if gc.correction != 1.0:
-                flat.mul_(gc.correction)
             piece = torch.empty(b.shard_numel, dtype=flat.dtype, device=flat.device)
-            reduce_scatter_single(piece, flat, op=dist.ReduceOp.AVG, group=gc.group)
-        if lp.grad is None:
-            lp.grad = piece.detach().clone()
-        else:
-            lp.grad.add_(piece)
-        release_buffer(b.grad_handle)
+            work = reduce_scatter_single(piece, flat, op=dist.ReduceOp.AVG, group=gc.group, async_op=self.prefetch)
+            self._reduces.append((b, work, piece, b.grad_handle))
         b.grad_flat, b.grad_handle = None, None
+        if not self.prefetch:
+            self._finish_reduces()
+
+    def _finish_reduces(self) -> None:
+        for b, work, piece, handle in self._reduces:
+            if work is not None:
+                work.wait()
+            lp = b.local_param
+            if lp.grad is None:
+                lp.grad = piece.detach().clone()
+            else:
+                lp.grad.add_(piece)
+            release_buffer(handle)
+        self._reduces.clear()
 
     def on_step_phase(self, phase: RuntimePhase) -> None:
-        if phase is RuntimePhase.POST_BACKWARD:
+        if phase is RuntimePhase.POST_FORWARD:
+            if not self._order_final and self._order:
+                self._order_final = True        # observed once; prefetching starts with the next pass
+        elif phase is RuntimePhase.POST_BACKWARD:
             with span("maltos::zero3.grad_sync.wait"):
                 for b in self.buckets:
                     if b.grad_flat is not None:      # some parameter produced no gradient: reduce what arrived
@@ -328,6 +411,7 @@ class Zero3Plugin(ZeroPluginBase):
                         self._reduce(b)
                     if b.materialized:
                         self._release(b, force=True)
+                self._finish_reduces()
         elif phase is RuntimePhase.PRE_STEP:
             self._maybe_clip_local_shards()
             self._peer_barrier()     # every pull of the old shards is done before any optimizer overwrites them

@@ -2,9 +2,10 @@
 
     torchrun --nproc-per-node 2 --master-addr 127.0.0.1 -m maltos_b200.tools.bench_fused_tp [--seq 8192 --hidden 4096]
 
-For the column-parallel projections of LLaMA-3 8B (q/k/v and gate/up) it times the fused all-gather -> GEMM, NCCL
-all-gather + GEMM, and the GEMM alone; for the row-parallel projections (o_proj, down) GEMM + NCCL reduce-scatter and
-the fused GEMM -> reduce-scatter. Device time (CUDA events), maximum over ranks, and the roofline target
+For the column-parallel projections of LLaMA-3 8B (q/k/v and gate/up) it times the all-gather pushed from inside the GEMM
+launch, the pull all-gather kernel + GEMM, NCCL all-gather + GEMM, and the GEMM alone; for the row-parallel projections
+(o_proj, down) the GEMM whose epilogue pushes the partial tiles, GEMM + pull reduce-scatter kernel, GEMM + NCCL
+reduce-scatter and the GEMM alone. The first column of every row is the path the library takes by default. Device time (CUDA events), maximum over ranks, and the roofline target
 ``max(FLOPs / measured GEMM peak, bytes leaving this GPU / NVLink bandwidth)`` with the achieved fraction.
 """
 from __future__ import annotations
@@ -50,8 +51,8 @@ def main(argv=None) -> None:
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     import maltos_b200  # noqa: F401
     from maltos_b200.ops import _lib, comm
-    from maltos_b200.ops.fused_tp import (_nccl_all_gather_rows, _nccl_reduce_scatter_rows, all_gather_grouped_linear,
-                                          gemm_reduce_scatter)
+    from maltos_b200.ops.fused_tp import (_nccl_all_gather_rows, _nccl_reduce_scatter_rows, all_gather_gemm, all_gather_pull,
+                                          gemm_reduce_scatter, gemm_reduce_scatter_pull, reduce_scatter_gemm)
     from maltos_b200.ops.gemm import gemm
 
     group = dist.new_group(list(range(world)))
@@ -69,31 +70,39 @@ def main(argv=None) -> None:
         if rank == 0:
             parts = " | ".join(f"{k} {v:.0f} us" for k, v in results.items())
             best = results[next(iter(results))]
-            print(f"{name} T={world}: {parts} | roofline target {target:.0f} us, fused achieves {target / best:.2f}", flush=True)
+            print(f"{name} T={world}: {parts} | roofline target {target:.0f} us, default path achieves {target / best:.2f}", flush=True)
 
     with torch.no_grad():
         for name, n_full in (("qkv", args.qkv), ("gate_up", 2 * args.ffn)):
             n = n_full // world
             w = torch.nn.Parameter((torch.randn(n, H, device="cuda") * 0.02).bfloat16())
             x = torch.randn(1, rows, H, device="cuda").bfloat16()
-            fused = _time(lambda: all_gather_grouped_linear(x, [w], ctx), args.iters)
-            _lib.lib().mb_gemm_set_push_split(1)
-            split = _time(lambda: all_gather_grouped_linear(x, [w], ctx), args.iters)
-            _lib.lib().mb_gemm_set_push_split(0)
-            nccl = _time(lambda: gemm(_nccl_all_gather_rows(x.view(-1, H), ctx, 1, rows), w), args.iters)
-            xf = _nccl_all_gather_rows(x.view(-1, H), ctx, 1, rows)
+            x2 = x.view(-1, H)
+            default = _time(lambda: all_gather_gemm(x2, w, ctx, 1, rows, b_mn=False), args.iters)
+            os.environ["MALTOS_B200_FUSED_GATHER"] = "1"
+            fused = _time(lambda: all_gather_gemm(x2, w, ctx, 1, rows, b_mn=False), args.iters)
+            os.environ.pop("MALTOS_B200_FUSED_GATHER")
+            pull = _time(lambda: gemm(all_gather_pull(x2, ctx, 1, rows), w), args.iters)
+            pull_only = _time(lambda: all_gather_pull(x2, ctx, 1, rows), args.iters)
+            nccl = _time(lambda: gemm(_nccl_all_gather_rows(x2, ctx, 1, rows), w), args.iters)
+            nccl_only = _time(lambda: _nccl_all_gather_rows(x2, ctx, 1, rows), args.iters)
+            xf = _nccl_all_gather_rows(x2, ctx, 1, rows)
             alone = _time(lambda: gemm(xf, w), args.iters)
             report(f"all-gather -> GEMM {name} N={n}", 2.0 * S * H * n, (world - 1) * rows * H * 2,
-                   {"fused": fused, "push launch + GEMM": split, "NCCL all-gather + GEMM": nccl, "GEMM alone": alone})
+                   {"default": default, "push inside GEMM": fused, "pull kernel + GEMM": pull, "NCCL all-gather + GEMM": nccl,
+                    "pull kernel alone": pull_only, "NCCL all-gather alone": nccl_only, "GEMM alone": alone})
         for name, k_full in (("o_proj", H), ("down", args.ffn)):
             k = k_full // world
             w = torch.nn.Parameter((torch.randn(H, k, device="cuda") * 0.02).bfloat16())
             x = torch.randn(S, k, device="cuda").bfloat16()
+            default = _time(lambda: reduce_scatter_gemm(x, w, ctx, 1, rows, b_mn=False), args.iters)
             fused = _time(lambda: gemm_reduce_scatter(x, w, ctx, 1, rows, b_mn=False), args.iters)
+            pull = _time(lambda: gemm_reduce_scatter_pull(x, w, ctx, 1, rows, b_mn=False), args.iters)
             nccl = _time(lambda: _nccl_reduce_scatter_rows(gemm(x, w), ctx, 1, rows), args.iters)
             alone = _time(lambda: gemm(x, w), args.iters)
             report(f"GEMM -> reduce-scatter {name} K={k}", 2.0 * S * H * k, (world - 1) * rows * H * 2,
-                   {"fused": fused, "GEMM + NCCL reduce-scatter": nccl, "GEMM alone": alone})
+                   {"default": default, "push from GEMM epilogue": fused, "GEMM + pull kernel": pull, "GEMM + NCCL reduce-scatter": nccl,
+                    "GEMM alone": alone})
     status = _lib.fetch_status(raise_on_error=False)
     if status[0]:
         print(f"rank {rank}: kernel status {status}", flush=True)

@@ -1,4 +1,5 @@
-"""Fused all-gather -> GEMM over NVLink peer memory against NCCL all-gather + fp32 matmul, on 2 GPUs."""
+"""Fused tensor-parallel collectives over NVLink peer memory (in-GEMM push, GEMM epilogue scatter, and the pull kernels)
+against NCCL collectives + fp32 matmul, on 2, 4 and 8 GPUs (the larger groups skip where fewer GPUs are present)."""
 import os
 
 import pytest
@@ -95,7 +96,9 @@ def _worker(rank, world, port, queue):
             w = torch.nn.Parameter((torch.randn(H, Kin, device="cuda", generator=torch.Generator(device="cuda").manual_seed(50 + rank)) * 0.05).bfloat16())
             g = torch.Generator(device="cuda").manual_seed(200 + rank)
             rows = S // world
-            for rep in range(3):
+            for rep in range(6):
+                # calls 0-2: partial tiles pushed by the GEMM epilogue; calls 3-5: GEMM into symmetric memory + pull kernel
+                os.environ["MALTOS_B200_FUSED_SCATTER"] = "1" if rep < 3 else "0"
                 x = torch.randn(B, S, Kin, device="cuda", generator=g).bfloat16().requires_grad_()
                 y = linear_reduce_scatter(x, w, ctx)
                 ref_full = x.detach().float() @ w.detach().float().t()
@@ -114,6 +117,24 @@ def _worker(rank, world, port, queue):
                 results.append((B, S, Kin, 10 + rep, err, gerr))
                 w.grad = None
         _lib.lib().mb_gemm_set_scatter_kind(ctypes.c_int(0))
+        # the pull kernels called directly, batch-major layout with B > 1, both buffer parities
+        from maltos_b200.ops.fused_tp import all_gather_pull, gemm_reduce_scatter_pull
+
+        B, rows, K, N = 2, 96, 256, 384
+        for rep in range(4):
+            gen = torch.Generator(device="cuda").manual_seed(500 + 10 * rep + rank)
+            xs = torch.randn(B * rows, K, device="cuda", generator=gen).bfloat16()
+            got = all_gather_pull(xs, ctx, B, rows)
+            allx = torch.empty(world, B, rows, K, device="cuda", dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(allx.view(-1, K), xs, group=group)
+            assert torch.equal(got, allx.permute(1, 0, 2, 3).reshape(B * world * rows, K)), ("all_gather_pull", rep)
+            xr = torch.randn(B * world * rows, K, device="cuda", generator=gen).bfloat16()
+            wr = (torch.randn(N, K, device="cuda", generator=gen) * 0.05).bfloat16()
+            got = gemm_reduce_scatter_pull(xr, wr, ctx, B, rows, b_mn=False)
+            tot = xr.float() @ wr.float().t()
+            dist.all_reduce(tot, group=group)
+            want = tot.view(B, world, rows, N)[:, rank].reshape(B * rows, N)
+            assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item(), ("gemm_reduce_scatter_pull", rep)
         status = _lib.fetch_status(raise_on_error=False)
         queue.put((rank, "ok", (results, status)))
         ctx.close()
@@ -124,8 +145,10 @@ def _worker(rank, world, port, queue):
             dist.destroy_process_group()
 
 
-def test_fused_all_gather_gemm_two_gpus():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_tensor_parallel_collectives(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
@@ -135,7 +158,7 @@ def test_fused_all_gather_gemm_two_gpus():
     out = {}
     try:
         for _ in range(world):
-            rank, status, payload = q.get(timeout=240)
+            rank, status, payload = q.get(timeout=400)
             assert status == "ok", payload
             out[rank] = payload
     finally:

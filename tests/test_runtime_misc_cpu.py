@@ -138,3 +138,53 @@ def test_fp16_master_weights_with_fused_adamw_keeps_master_gradients():
         opt.step()
         assert not torch.equal(w.detach(), before) and w.dtype == dtype
         assert torch.allclose(w.detach().float(), master.detach(), atol=1e-2)
+
+
+def _zero3_prefetch_worker(rank, world):
+    import torch.nn as nn
+
+    import maltos_b200  # noqa: F401
+    from maltos_b200 import models
+    from maltos_b200.models.tiny_transformer import RmsNorm
+    from maltos_b200.runtime import MeshConfig, RuntimeCore
+    from maltos_b200.runtime.plugins import zero3
+
+    torch.manual_seed(1)
+    model = models.TinyTransformer(32, 4, 2, 64, 1e-5, 2, 64, 16)
+    plug = zero3.Zero3Plugin(wrap_cls={nn.Linear, nn.Embedding, RmsNorm})
+    rt = RuntimeCore(model=model, mesh=MeshConfig(dp=world), plugins=[plug], grad_accum_steps=1,
+                     optimizer_factory=lambda ps: torch.optim.SGD(ps, lr=0.1))
+    rt.setup()
+    claimed_ahead, claimed_total = [0], [0]
+    inner = plug._gather
+
+    def counting_gather(b):
+        claimed_total[0] += 1
+        claimed_ahead[0] += int(b.prefetched)
+        return inner(b)
+
+    plug._gather = counting_gather
+    g = torch.Generator().manual_seed(5 + rank)
+    stats = []
+    for step in range(2):
+        ids = torch.randint(0, 64, (2, 16), generator=g)
+        rt.run_step({"input_ids": ids, "labels": ids.roll(-1, 1)})
+        stats.append((claimed_ahead[0], claimed_total[0], plug._order_final, len(plug._reduces),
+                      all(not b.materialized and b.full_tensor.untyped_storage().size() == 0 for b in plug.buckets)))
+        claimed_ahead[0] = claimed_total[0] = 0
+        rt.step_optimizer()
+    rt.close()
+    return stats, len(plug.buckets)
+
+
+def test_zero3_prefetches_in_observed_order_and_releases_everything():
+    """First pass: the bucket order is observed (the backward already prefetches). Second pass: every bucket but the
+    first of each direction is claimed from a gather that was started ahead of its use; after each micro-step no bucket
+    holds memory and no reduce-scatter is left in flight."""
+    results = run_distributed(_zero3_prefetch_worker, 2)
+    for stats, n_buckets in results:
+        (ahead0, total0, final0, pending0, clean0), (ahead1, total1, final1, pending1, clean1) = stats
+        assert final0 and final1 and pending0 == 0 and pending1 == 0 and clean0 and clean1
+        assert total0 == total1 == 2 * n_buckets
+        assert ahead0 >= n_buckets // 2            # backward of the first pass
+        assert ahead1 >= 2 * n_buckets - 6         # both directions of the second pass
