@@ -48,6 +48,9 @@ struct FlashBwdArgs {
   int accumulate;           // 1 (fp32 outputs only): add to what the output holds
   float scale, scale_log2;
   int* status;
+  int split;                // dK/dV kernel: the query heads of a group are divided over `split` CTAs (1 = no split)
+  float* dk_tmp;            // split > 1: fp32 [B, Sk, Hkv, D] sums the CTAs add their parts to
+  float* dv_tmp;
   int dbg;                  // probe builds only: bit 0 skip the S/dP UMMAs, bit 1 skip the accumulation UMMAs, bit 2 skip the arithmetic
 };
 
@@ -194,8 +197,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_head = blockIdx.y, batch = blockIdx.z;
+  // With few key/value heads per GPU (tensor parallelism) one CTA per (key block, key/value head) would leave most SMs
+  // idle: the query heads of the group are then divided over `split` CTAs, which add their parts into fp32 sums.
+  const int kv_head = static_cast<int>(blockIdx.y) / p.split, part = static_cast<int>(blockIdx.y) % p.split, batch = blockIdx.z;
   const int group = p.Hq / p.Hkv;
+  const int heads_here = group / p.split;
+  const int head0 = kv_head * group + part * heads_here;
   const int k0 = static_cast<int>(blockIdx.x) * kKvRows;
   const int causal_off = p.Sk - p.Sq;
   constexpr bool causal = MODE == 1 || MODE == 3;
@@ -208,7 +215,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     qb_start = first_q <= 0 ? 0 : first_q / kQSub;
   }
   const int n_sub = qb_start < n_qsub_all ? n_qsub_all - qb_start : 0;
-  const int n_iter = n_sub * group;
+  const int n_iter = n_sub * heads_here;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -251,7 +258,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       for (int it = 0; it < n_iter; ++it) {
         const int st = it % kQStages;
         if (!mbar_wait(&q_empty[st], ((it / kQStages) & 1) ^ 1, abort_flag)) break;
-        const int head = kv_head * group + it / n_sub;
+        const int head = head0 + it / n_sub;
         const int qrow0 = (qb_start + it % n_sub) * kQSub;
         mbar_arrive_expect_tx(&q_full[st], 2 * Q_BYTES + (with_ids ? 4 : 2) * kQSub * 4);
 #pragma unroll
@@ -443,6 +450,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (ok) {
       constexpr int QUART_D = D / 4;                // columns of the head dimension per thread
       const long long off = (static_cast<long long>(batch) * p.Sk + kj) * p.dkv_tstride + static_cast<long long>(kv_head) * D + grp * QUART_D;
+      const long long toff = ((static_cast<long long>(batch) * p.Sk + kj) * p.Hkv + kv_head) * D + grp * QUART_D;
       if (n_iter > 0) {
         tc_fence_after();
 #pragma unroll 1
@@ -450,12 +458,26 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           uint32_t r[16];
           tmem_ld_32x32b_x16(tmem_base + DV_COL + static_cast<uint32_t>(grp * QUART_D + c0) + t_lane, r);
           tmem_ld_wait();
-          if (key_valid) store_row_chunk(p.dv, off + c0, r, 1.f, p.out_fp32 != 0, p.accumulate != 0);
+          if (key_valid) {
+            if (p.split > 1) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) atomicAdd(p.dv_tmp + toff + c0 + i, __uint_as_float(r[i]));
+            } else {
+              store_row_chunk(p.dv, off + c0, r, 1.f, p.out_fp32 != 0, p.accumulate != 0);
+            }
+          }
           tmem_ld_32x32b_x16(tmem_base + DK_COL + static_cast<uint32_t>(grp * QUART_D + c0) + t_lane, r);
           tmem_ld_wait();
-          if (key_valid) store_row_chunk(p.dk, off + c0, r, p.scale, p.out_fp32 != 0, p.accumulate != 0);
+          if (key_valid) {
+            if (p.split > 1) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) atomicAdd(p.dk_tmp + toff + c0 + i, __uint_as_float(r[i]) * p.scale);
+            } else {
+              store_row_chunk(p.dk, off + c0, r, p.scale, p.out_fp32 != 0, p.accumulate != 0);
+            }
+          }
         }
-      } else if (key_valid && !p.accumulate) {
+      } else if (key_valid && !p.accumulate && p.split == 1) {
         store_row_zero(p.dv, off, QUART_D, p.out_fp32 != 0);
         store_row_zero(p.dk, off, QUART_D, p.out_fp32 != 0);
       }
@@ -476,6 +498,45 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// fp32 sums [tokens, hd] of a split dK/dV launch -> the caller's outputs (bf16 or fp32, token stride `tstride`).
+__global__ void flash_bwd_finish_split_kernel(const float* __restrict__ dk_tmp, const float* __restrict__ dv_tmp, void* dk, void* dv,
+                                              long long tokens, int hd, long long tstride, int out_fp32, int accumulate) {
+  const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= tokens * hd) return;
+  const long long t = i4 / hd;
+  const int c = static_cast<int>(i4 - t * hd);
+  const long long o = t * tstride + c;
+  const float4 a = *reinterpret_cast<const float4*>(dk_tmp + i4), b = *reinterpret_cast<const float4*>(dv_tmp + i4);
+  if (out_fp32) {
+    float4* pk = reinterpret_cast<float4*>(static_cast<float*>(dk) + o);
+    float4* pv = reinterpret_cast<float4*>(static_cast<float*>(dv) + o);
+    float4 k = a, v = b;
+    if (accumulate) {
+      const float4 ok = *pk, ov = *pv;
+      k.x += ok.x, k.y += ok.y, k.z += ok.z, k.w += ok.w;
+      v.x += ov.x, v.y += ov.y, v.z += ov.z, v.w += ov.w;
+    }
+    *pk = k;
+    *pv = v;
+  } else {
+    uint2 k, v;
+    k.x = pack_bf16x2(a.x, a.y), k.y = pack_bf16x2(a.z, a.w);
+    v.x = pack_bf16x2(b.x, b.y), v.y = pack_bf16x2(b.z, b.w);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(dk) + o) = k;
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(dv) + o) = v;
+  }
+}
+
+// How many CTAs share the query heads of one key/value head in the dK/dV kernel: the smallest power of two that fills
+// the GPU (or uses up the group).
+static int dkdv_split(int B, int Sk, int Hq, int Hkv) {
+  const long long ctas = static_cast<long long>((Sk + kKvRows - 1) / kKvRows) * Hkv * B;
+  const int group = Hq / Hkv;
+  int split = 1;
+  while (split * 2 <= group && group % (split * 2) == 0 && ctas * split < sm_count()) split *= 2;
+  return split;
 }
 
 // ---------------------------------------------------------------------------------------------- dQ
@@ -805,6 +866,13 @@ static int launch_flash_bwd(const void* q, long long q_tstride, long long q_bstr
   int* kpos = qseq + static_cast<long long>(a.B) * a.Sq_pad;
   int* kseq = kpos + static_cast<long long>(a.B) * a.Sk_pad;
   a.lse2 = lse2, a.delta = delta, a.qpos = qpos, a.qseq = qseq, a.kpos = kpos, a.kseq = kseq;
+  a.split = dkdv_split(a.B, a.Sk, a.Hq, a.Hkv);
+  const long long kv_elems = static_cast<long long>(a.B) * a.Sk * a.Hkv * D;
+  if (a.split > 1) {
+    a.dk_tmp = reinterpret_cast<float*>(kseq + static_cast<long long>(a.B) * a.Sk_pad);
+    a.dv_tmp = a.dk_tmp + kv_elems;
+    MB_CHECK_CUDA(cudaMemsetAsync(a.dk_tmp, 0, sizeof(float) * 2 * kv_elems, stream));
+  }
   {
     const long long threads = n_rows * 32;
     const int block = 256;
@@ -854,9 +922,15 @@ static int launch_flash_bwd(const void* q, long long q_tstride, long long q_bstr
     configured[dev & 63] = true;
   }
   {
-    dim3 grid((a.Sk + kKvRows - 1) / kKvRows, a.Hkv, a.B);
+    dim3 grid((a.Sk + kKvRows - 1) / kKvRows, a.Hkv * a.split, a.B);
     flash_bwd_dkdv_kernel<D, MODE><<<grid, kBwThreads, smem_dkdv, stream>>>(tmQ64, tmDO64, tmK, tmV, a);
     count_launch();
+    if (a.split > 1) {
+      const long long quads = kv_elems / 4;
+      flash_bwd_finish_split_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, stream>>>(
+          a.dk_tmp, a.dv_tmp, a.dk, a.dv, static_cast<long long>(a.B) * a.Sk, a.Hkv * D, a.dkv_tstride, a.out_fp32, a.accumulate);
+      count_launch();
+    }
   }
   {
     dim3 grid((a.Sq + kDqRows - 1) / kDqRows, a.Hq, a.B);
@@ -876,9 +950,11 @@ MB_API int mb_flash_probe_read(long long* host_out) {
 #endif
 
 // Number of 4-byte words of scratch memory mb_flash_attn_bwd needs for these sizes.
-MB_API long long mb_flash_attn_bwd_scratch_words(int B, int Sq, int Sk, int Hq) {
+MB_API long long mb_flash_attn_bwd_scratch_words(int B, int Sq, int Sk, int Hq, int Hkv, int D) {
   const long long sq_pad = (static_cast<long long>(Sq) + 127) / 128 * 128, sk_pad = (static_cast<long long>(Sk) + 127) / 128 * 128;
-  return 2 * B * Hq * sq_pad + 2 * B * sq_pad + 2 * B * sk_pad;
+  long long words = 2 * B * Hq * sq_pad + 2 * B * sq_pad + 2 * B * sk_pad;
+  if (Hkv >= 1 && Hq % Hkv == 0 && mb::dkdv_split(B, Sk, Hq, Hkv) > 1) words += 2ll * B * Sk * Hkv * D;   // fp32 dK / dV sums
+  return words;
 }
 
 // q, out, dout [B, Sq, Hq, D]; k, v [B, Sk, Hkv, D] bf16 (heads contiguous inside a token; token / batch strides in

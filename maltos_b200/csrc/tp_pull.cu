@@ -9,7 +9,7 @@
 //    Replaces NCCL reduce-scatter after the row-parallel GEMMs (reference runtime/layers/functional.py:273-366).
 //  * pull_all_gather_kernel: every rank copies its [B, S/T, K] rows into its symmetric buffer (and into its own slot of
 //    the gathered tensor), the last block to finish publishes the flag, then every block pulls the peers' rows, peers
-//    visited in ring order starting at rank + 1 so that at any moment every NVSwitch port serves one reader.
+//    visited in ring order starting at rank + 1, one load per peer in flight per thread.
 //    Replaces NCCL all-gather in front of the column-parallel GEMMs (reference runtime/layers/functional.py:369-486).
 //
 // Both buffers are double-buffered by call parity. That is enough for safe reuse without a second flag: a rank passes
@@ -23,6 +23,13 @@
 #include "ptx.cuh"
 
 namespace mb {
+
+#ifdef MB_FLASH_PROBE
+__device__ unsigned long long g_pull_probe[16];
+#define MB_PULL_STAMP(cond, slot) do { if (cond) g_pull_probe[slot] = globaltimer_ns(); } while (0)
+#else
+#define MB_PULL_STAMP(cond, slot) do { } while (0)
+#endif
 
 constexpr int kPullThreads = 256;
 constexpr int kPullMaxWorld = 8;
@@ -93,12 +100,8 @@ pull_reduce_scatter_kernel(PullPtrs pp, int rank, unsigned seq, int batches, lon
   if (!pull_wait_all(my_flags, WORLD, rank, seq, status)) return;
   const long long total = static_cast<long long>(batches) * vec_per_slice;
   const long long stride = static_cast<long long>(gridDim.x) * kPullThreads;
-  for (long long v = static_cast<long long>(blockIdx.x) * kPullThreads + threadIdx.x; v < total; v += stride) {
-    const long long b = v / vec_per_slice, off = v - b * vec_per_slice;
-    const long long src_off = (b * WORLD + rank) * vec_per_slice + off;   // this rank's slice inside batch b
-    uint4 raw[WORLD];
-#pragma unroll
-    for (int r = 0; r < WORLD; ++r) raw[r] = reinterpret_cast<const uint4*>(pp.data[r])[src_off];
+  constexpr int UNROLL = WORLD >= 8 ? 1 : (WORLD == 4 ? 2 : 4);     // loads in flight per thread: UNROLL x WORLD
+  auto reduce_store = [&](const uint4 (&raw)[WORLD], long long v) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < WORLD; ++r) bf16x8_accumulate(raw[r], acc);     // rank order: the same bits on every owner
@@ -106,6 +109,29 @@ pull_reduce_scatter_kernel(PullPtrs pp, int rank, unsigned seq, int batches, lon
     o.x = pack_bf16x2(acc[0], acc[1]), o.y = pack_bf16x2(acc[2], acc[3]);
     o.z = pack_bf16x2(acc[4], acc[5]), o.w = pack_bf16x2(acc[6], acc[7]);
     out[v] = o;
+  };
+  auto src_of = [&](long long v) {
+    const long long b = v / vec_per_slice, off = v - b * vec_per_slice;
+    return (b * WORLD + rank) * vec_per_slice + off;                      // this rank's slice inside batch b
+  };
+  long long v = static_cast<long long>(blockIdx.x) * kPullThreads + threadIdx.x;
+  for (; v + (UNROLL - 1) * stride < total; v += UNROLL * stride) {
+    uint4 raw[UNROLL][WORLD];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long so = src_of(v + u * stride);
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) raw[u][r] = reinterpret_cast<const uint4*>(pp.data[r])[so];
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) reduce_store(raw[u], v + u * stride);
+  }
+  for (; v < total; v += stride) {
+    const long long so = src_of(v);
+    uint4 raw[WORLD];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) raw[r] = reinterpret_cast<const uint4*>(pp.data[r])[so];
+    reduce_store(raw, v);
   }
 }
 
@@ -120,6 +146,7 @@ pull_all_gather_kernel(PullPtrs pp, int rank, unsigned seq, int batches, long lo
   const long long stride = static_cast<long long>(gridDim.x) * kPullThreads;
   const long long tid = static_cast<long long>(blockIdx.x) * kPullThreads + threadIdx.x;
   unsigned* my_pad = reinterpret_cast<unsigned*>(pp.pads[rank]);
+  MB_PULL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 0);
   // phase A: publish this rank's rows (no waiting here, so every block always gets through it)
   {
     uint4* pub = reinterpret_cast<uint4*>(pp.data[rank]);
@@ -133,39 +160,50 @@ pull_all_gather_kernel(PullPtrs pp, int rank, unsigned seq, int batches, long lo
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
+    MB_PULL_STAMP(blockIdx.x == 0, 1);
     const unsigned done = atomicAdd(my_pad + 288, 1u);
     if (done == gridDim.x - 1) {
       atomicExch(my_pad + 288, 0u);
       __threadfence_system();
+      MB_PULL_STAMP(true, 2);
       for (int r = 0; r < WORLD; ++r)
         if (r != rank) pull_st_release_sys(reinterpret_cast<unsigned*>(pp.pads[r]) + 272 + buf * 8 + rank, seq);
+      MB_PULL_STAMP(true, 3);
     }
   }
   // phase B: pull the peers' rows; the grid is no larger than what is resident at once, so the blocks that spin here
   // never keep a phase-A block of this GPU from running
   if (!pull_wait_all(my_pad + 272 + buf * 8, WORLD, rank, seq, status)) return;
-  constexpr int UNROLL = 4;
-#pragma unroll 1
-  for (int step = 1; step < WORLD; ++step) {
-    const int r = (rank + step) % WORLD;
-    const uint4* src = reinterpret_cast<const uint4*>(pp.data[r]);
-    long long v = tid;
-    for (; v + (UNROLL - 1) * stride < total; v += UNROLL * stride) {
-      uint4 q[UNROLL];
+  MB_PULL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 4);
+  // Remote loads need many requests in flight to fill the link (8 per thread reach ~735 GB/s, 3 only ~390): every thread
+  // keeps UNROLL vectors x (WORLD - 1) peers outstanding, peers taken in ring order from rank + 1 so that the readers of
+  // one source are spread over time.
+  constexpr int UNROLL = WORLD >= 8 ? 2 : (WORLD == 4 ? 3 : 8);
+  long long v = tid;
+  for (; v + (UNROLL - 1) * stride < total; v += UNROLL * stride) {
+    uint4 q[UNROLL][WORLD - 1];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) q[u] = src[v + u * stride];
+    for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const long long vv = v + u * stride;
-        const long long b = vv / vec_per_slice, off = vv - b * vec_per_slice;
-        gathered[(b * WORLD + r) * vec_per_slice + off] = q[u];
-      }
-    }
-    for (; v < total; v += stride) {
-      const long long b = v / vec_per_slice, off = v - b * vec_per_slice;
-      gathered[(b * WORLD + r) * vec_per_slice + off] = src[v];
+      for (int step = 1; step < WORLD; ++step) q[u][step - 1] = reinterpret_cast<const uint4*>(pp.data[(rank + step) % WORLD])[v + u * stride];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long vv = v + u * stride;
+      const long long b = vv / vec_per_slice, off = vv - b * vec_per_slice;
+#pragma unroll
+      for (int step = 1; step < WORLD; ++step) gathered[(b * WORLD + (rank + step) % WORLD) * vec_per_slice + off] = q[u][step - 1];
     }
   }
+  for (; v < total; v += stride) {
+    const long long b = v / vec_per_slice, off = v - b * vec_per_slice;
+#pragma unroll
+    for (int step = 1; step < WORLD; ++step) {
+      const int r = (rank + step) % WORLD;
+      gathered[(b * WORLD + r) * vec_per_slice + off] = reinterpret_cast<const uint4*>(pp.data[r])[v];
+    }
+  }
+  MB_PULL_STAMP(blockIdx.x == 0 && threadIdx.x == 0, 5);
+  MB_PULL_STAMP(blockIdx.x == gridDim.x - 1 && threadIdx.x == 0, 6);
 }
 
 static int fill_ptrs(PullPtrs* pp, const unsigned long long* data, const unsigned long long* pads, int world, const char* what) {
@@ -185,6 +223,12 @@ static int fill_ptrs(PullPtrs* pp, const unsigned long long* data, const unsigne
 }
 
 }  // namespace mb
+
+#ifdef MB_FLASH_PROBE
+MB_API int mb_pull_probe_read(unsigned long long* host_out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mb::g_pull_probe, sizeof(unsigned long long) * 16));
+}
+#endif
 
 // out[B, rows, N] = sum over ranks of partial_r[B, rank-th slice of T * rows, N]. `partials[r]`: address, as mapped in
 // this process, of the buffer half of rank r that holds its partial of this call; `pads[r]`: its signal pad. `seq`
@@ -237,7 +281,15 @@ MB_API int mb_pull_all_gather_bf16(const void* x_local, const unsigned long long
   const long long vec_per_slice = rows * k_cols / 8;
   const long long total = vec_per_slice * batches;
   long long blocks = (total + kPullThreads - 1) / kPullThreads;
-  const long long cap = static_cast<long long>(sm_count()) * 2;   // all resident at once (256 threads, few registers)
+  // the blocks that spin in phase B must never keep a phase-A block of the same launch from running: the grid is capped at
+  // what the occupancy calculator says is resident at once for this instance
+  int per_sm = 0;
+  cudaError_t occ = world == 2   ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pull_all_gather_kernel<2>, kPullThreads, 0)
+                    : world == 4 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pull_all_gather_kernel<4>, kPullThreads, 0)
+                                 : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pull_all_gather_kernel<8>, kPullThreads, 0);
+  if (occ != cudaSuccess || per_sm < 1) per_sm = 1;
+  if (per_sm > 4) per_sm = 4;
+  const long long cap = static_cast<long long>(sm_count()) * per_sm;
   if (blocks > cap) blocks = cap;
   const unsigned g = static_cast<unsigned>(blocks);
   const uint4* x = static_cast<const uint4*>(x_local);

@@ -181,7 +181,7 @@ def flash_backward(q, k, v, out, lse, dout, *, mode: int, q_positions=None, k_po
         dv = torch.empty((B, Sk, Hkv, D), dtype=dt, device=q.device)
     L = _lib.lib()
     L.mb_flash_attn_bwd_scratch_words.restype = ctypes.c_longlong
-    words = int(L.mb_flash_attn_bwd_scratch_words(_lib.c_int(B), _lib.c_int(Sq), _lib.c_int(Sk), _lib.c_int(Hq)))
+    words = int(L.mb_flash_attn_bwd_scratch_words(_lib.c_int(B), _lib.c_int(Sq), _lib.c_int(Sk), _lib.c_int(Hq), _lib.c_int(Hkv), _lib.c_int(D)))
     scratch = torch.empty((words,), dtype=torch.float32, device=q.device)
     to_i32 = lambda t: None if t is None else t.to(torch.int32).contiguous()   # noqa: E731
     qp, kp, qs, ks = (to_i32(t) for t in (q_positions, k_positions, q_sequence_ids, k_sequence_ids))

@@ -81,6 +81,9 @@ def main(argv=None) -> None:
             default = _time(lambda: all_gather_gemm(x2, w, ctx, 1, rows, b_mn=False), args.iters)
             os.environ["MALTOS_B200_FUSED_GATHER"] = "1"
             fused = _time(lambda: all_gather_gemm(x2, w, ctx, 1, rows, b_mn=False), args.iters)
+            _lib.lib().mb_gemm_set_push_split(1)
+            split = _time(lambda: all_gather_gemm(x2, w, ctx, 1, rows, b_mn=False), args.iters)
+            _lib.lib().mb_gemm_set_push_split(0)
             os.environ.pop("MALTOS_B200_FUSED_GATHER")
             pull = _time(lambda: gemm(all_gather_pull(x2, ctx, 1, rows), w), args.iters)
             pull_only = _time(lambda: all_gather_pull(x2, ctx, 1, rows), args.iters)
@@ -89,7 +92,7 @@ def main(argv=None) -> None:
             xf = _nccl_all_gather_rows(x2, ctx, 1, rows)
             alone = _time(lambda: gemm(xf, w), args.iters)
             report(f"all-gather -> GEMM {name} N={n}", 2.0 * S * H * n, (world - 1) * rows * H * 2,
-                   {"default": default, "push inside GEMM": fused, "pull kernel + GEMM": pull, "NCCL all-gather + GEMM": nccl,
+                   {"default": default, "push inside GEMM": fused, "push launch + GEMM": split, "pull kernel + GEMM": pull, "NCCL all-gather + GEMM": nccl,
                     "pull kernel alone": pull_only, "NCCL all-gather alone": nccl_only, "GEMM alone": alone})
         for name, k_full in (("o_proj", H), ("down", args.ffn)):
             k = k_full // world

@@ -147,7 +147,8 @@ def test_autograd_entry_point_strided_qkv_and_zigzag_positions():
     before = _lib.launch_count()
     out = flash_attention(q, k, v, causal=True)
     out.backward(dout)
-    assert _lib.launch_count() - before == 4      # forward, preprocessing, dK/dV, dQ: no library kernel in between
+    # forward, preprocessing, dK/dV (+ the pass that folds the per-head-group partial sums of a small grid), dQ
+    assert _lib.launch_count() - before in (4, 5)
     rq, rk, rv = _reference_grads(q.detach(), k.detach(), v.detach(), dout, causal=True)
     g = packed.grad
     _close(g[..., :Hq * D].view(B, S, Hq, D), rq)
