@@ -38,3 +38,109 @@ def moe_experts_forward(flat: torch.Tensor, expert_idx: torch.Tensor, gate: torc
     if pieces:
         out = out.index_add(0, sorted_tokens[:at], torch.cat(pieces, dim=0))
     return out
+
+
+# ------------------------------------------------------------------------------------------------ grouped expert GEMMs
+def _ptr_array(tensors):
+    import ctypes
+
+    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def grouped_gemm(mode: int, a: torch.Tensor, bs, counts: torch.Tensor, cap: int, *, out_dtype=None):
+    """All local experts' GEMMs in ONE launch with the per-expert row counts read on the device (``csrc/grouped_gemm.cu``).
+
+    ``a [G*cap, .]`` holds expert ``g``'s rows at ``[g*cap, g*cap + counts[g])``; ``counts`` is an int32 device tensor.
+      mode 0: ``bs[g]`` is ``[N, K]``, returns ``[G*cap, N]`` with ``out[rows of g] = a[rows of g] @ bs[g].T``;
+      mode 1: ``bs[g]`` is ``[K, N]``, returns ``[G*cap, N]`` with ``out[rows of g] = a[rows of g] @ bs[g]``;
+      mode 2: ``bs = [b]`` with ``b [G*cap, N]``, returns ``[G, M, N]`` with ``out[g] = a[rows of g].T @ b[rows of g]``.
+    Rows beyond ``counts[g]`` of the outputs of modes 0/1 are left as they were allocated (zeros). For mode 2 the rows of
+    ``a`` between ``counts[g]`` and the next multiple of 64 must be zero. CPU tensors take a plain loop (test oracle)."""
+    from . import _lib
+
+    G = counts.numel()
+    out_dtype = out_dtype or a.dtype
+    if mode == 2:
+        M, N = a.shape[1], bs[0].shape[1]
+    else:
+        N = bs[0].shape[0] if mode == 0 else bs[0].shape[1]
+    if not _lib.use_kernels(a):
+        cnt = counts.tolist()
+        if mode == 2:
+            out = torch.zeros((G, M, N), dtype=out_dtype, device=a.device)
+            for g, n in enumerate(cnt):
+                out[g] = (a[g * cap:g * cap + n].float().t() @ bs[0][g * cap:g * cap + n].float()).to(out_dtype)
+            return out
+        out = torch.zeros((G * cap, N), dtype=out_dtype, device=a.device)
+        for g, n in enumerate(cnt):
+            w = bs[g].float()
+            out[g * cap:g * cap + n] = (a[g * cap:g * cap + n].float() @ (w.t() if mode == 0 else w)).to(out_dtype)
+        return out
+    if a.dtype != torch.bfloat16 or any(b.dtype != torch.bfloat16 for b in bs):
+        raise TypeError("grouped_gemm kernel takes bf16 operands")
+    if cap % 64 or counts.dtype != torch.int32 or not counts.is_cuda:
+        raise ValueError("grouped_gemm: cap must be a multiple of 64 and counts an int32 device tensor")
+    a = a if (a.stride(1) == 1 and a.stride(0) % 8 == 0) else a.contiguous()
+    bs = [b if (b.stride(1) == 1 and b.stride(0) % 8 == 0) else b.contiguous() for b in bs]
+    if len({b.stride(0) for b in bs}) != 1:
+        raise ValueError("grouped_gemm: all group operands must share one row stride")
+    if mode == 2:
+        out = torch.empty((G, M, N), dtype=out_dtype, device=a.device)
+        c_list = [out[g] for g in range(G)]
+        K = cap
+    else:
+        out = torch.zeros((G * cap, N), dtype=out_dtype, device=a.device)
+        c_list = [out]
+        M, K = cap, a.shape[1]
+    rc = _lib.lib().mb_grouped_gemm_bf16(_lib.c_int(mode), _lib.ptr(a), _lib.c_ll(a.stride(0)), _ptr_array(bs), _lib.c_ll(bs[0].stride(0)),
+                                         _ptr_array(c_list), _lib.c_ll(N), _lib.ptr(counts), _lib.c_int(G), _lib.c_int(cap),
+                                         _lib.c_int(M), _lib.c_int(N), _lib.c_int(K), _lib.c_int(int(out_dtype == torch.float32)),
+                                         _lib.stream_ptr())
+    _lib.check(rc, "mb_grouped_gemm_bf16")
+    return out
+
+
+class _GroupedSwiGLUExperts(torch.autograd.Function):
+    """``y[rows of g] = down_g(silu(gate_g(x)) * up_g(x))`` for all local experts with device-side row counts: seven grouped
+    launches forward + backward per layer instead of nine GEMM calls per expert, and no host read of the counts."""
+
+    @staticmethod
+    def forward(ctx, x, counts, cap, n_experts, *weights):
+        from .swiglu import swiglu
+
+        gates, ups, downs = weights[:n_experts], weights[n_experts:2 * n_experts], weights[2 * n_experts:]
+        with torch.no_grad():
+            hg = grouped_gemm(0, x, list(gates), counts, cap)
+            hu = grouped_gemm(0, x, list(ups), counts, cap)
+            act = swiglu(hg, hu)
+            y = grouped_gemm(0, act, list(downs), counts, cap)
+        ctx.save_for_backward(x, counts, hg, hu, *weights)
+        ctx.cap, ctx.n = cap, n_experts
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .swiglu import swiglu
+
+        x, counts, hg, hu, *weights = ctx.saved_tensors
+        n, cap = ctx.n, ctx.cap
+        gates, ups, downs = weights[:n], weights[n:2 * n], weights[2 * n:]
+        dy = dy.contiguous()
+        dact = grouped_gemm(1, dy, list(downs), counts, cap)                    # [rows, F]   (down_g is [H, F] = [K, N])
+        with torch.enable_grad():
+            g_, u_ = hg.detach().requires_grad_(True), hu.detach().requires_grad_(True)
+            act = swiglu(g_, u_)
+        dg, du = torch.autograd.grad(act, (g_, u_), dact)
+        d_down = grouped_gemm(2, dy, [act.detach()], counts, cap)               # [G, H, F]
+        dx = grouped_gemm(1, dg, list(gates), counts, cap)                      # gate_g is [F, H] = [K, N]
+        dx = dx + grouped_gemm(1, du, list(ups), counts, cap)
+        d_gate = grouped_gemm(2, dg, [x], counts, cap)                          # [G, F, H]
+        d_up = grouped_gemm(2, du, [x], counts, cap)
+        grads = [d_gate[g] for g in range(n)] + [d_up[g] for g in range(n)] + [d_down[g] for g in range(n)]
+        return (dx, None, None, None, *grads)
+
+
+def grouped_swiglu_experts(x: torch.Tensor, counts: torch.Tensor, cap: int, gates, ups, downs) -> torch.Tensor:
+    """SwiGLU expert MLPs over a capacity-bounded, expert-major row buffer ``x [G*cap, H]`` (see :func:`grouped_gemm`).
+    Rows beyond ``counts[g]`` must hold finite values (zeros); their outputs are zeros."""
+    return _GroupedSwiGLUExperts.apply(x, counts, cap, len(gates), *gates, *ups, *downs)
