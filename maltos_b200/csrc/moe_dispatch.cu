@@ -8,6 +8,8 @@
 // one-sided row copies; gates and expert ids never travel because rows arrive sorted by expert and the gate is applied
 // on the source side.
 //
+// A destination rank of -1 marks an assignment dropped by the capacity limit (skipped by a push, zeros from a pull), so
+// the row count of a transfer is static and no host ever reads how many assignments survived.
 // One warp moves one row with 16-byte accesses, four in flight per lane. The kernels never wait on another GPU; the
 // callers separate them from the peers' reads and writes with stream-ordered group barriers.
 #include "host.h"
@@ -32,6 +34,14 @@ peer_rows_kernel(unsigned char* __restrict__ local, long long local_stride, cons
     const int r = peer_rank[j];
     const long long pr = peer_row[j];
     const long long lr = local_row ? local_row[j] : j;
+    if (r == -1) {
+      // an assignment that was dropped by the capacity limit: nothing is sent; a pull delivers a row of zeros
+      if (!kPush && lr >= 0 && lr < local_rows_cap) {
+        uint4* mine = reinterpret_cast<uint4*>(local + lr * local_stride);
+        for (int c = lane; c < chunks; c += 32) mine[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      continue;
+    }
     if (r < 0 || r >= world || pr < 0 || pr >= peer_rows_cap || lr < 0 || lr >= local_rows_cap) {
       // a bad index is recorded and the row skipped: nothing is read or written outside the buffers
       if (lane == 0) atomicOr(status, MB_ERR_BAD_INDEX);

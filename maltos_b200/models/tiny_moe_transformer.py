@@ -87,11 +87,11 @@ class TopKMoE(nn.Module):
         flat = x.reshape(-1, H)
         logits = self.router(flat)
         idx, gate, aux = route_and_balance(logits, self.top_k, need_aux=return_aux_loss)
-        keep = None
+        keep, cap = None, None
         if self.capacity_factor is not None:
             cap = max(1, int(self.capacity_factor * flat.shape[0] * self.top_k / self._num_experts + 0.999999))
             keep = capacity_keep_mask(idx, self._num_experts, cap)
-        out = moe_experts_forward(flat, idx, gate, keep, list(self.experts)).view(B, S, H)
+        out = moe_experts_forward(flat, idx, gate, keep, list(self.experts), capacity=cap).view(B, S, H)
         if not return_aux_loss:
             return out
         return out, aux

@@ -10,9 +10,59 @@ from __future__ import annotations
 import torch
 
 
+def swiglu_expert_weights(experts, like: torch.Tensor):
+    """``(gates, ups, downs)`` weight lists when every expert is a bias-free SwiGLU MLP (``gate``/``up``/``down`` linear
+    layers) whose bf16 weights are materialised on ``like``'s CUDA device - the case the grouped expert GEMM covers -
+    else None."""
+    from . import _lib
+
+    if not (_lib.use_kernels(like) and like.dtype == torch.bfloat16 and len(experts) <= 16):
+        return None
+    gates, ups, downs = [], [], []
+    for e in experts:
+        parts = [getattr(e, n, None) for n in ("gate", "up", "down")]
+        if any(p is None or getattr(p, "bias", None) is not None or not hasattr(p, "weight") for p in parts):
+            return None
+        ws = [p.weight for p in parts]
+        if any(w.dtype != torch.bfloat16 or w.numel() == 0 or w.dim() != 2 or not w.is_cuda or w.shape[1] % 8 for w in ws):
+            return None
+        gates.append(ws[0]), ups.append(ws[1]), downs.append(ws[2])
+    return gates, ups, downs
+
+
+def _moe_experts_forward_static(flat, expert_idx, gate, keep, weights, capacity: int) -> torch.Tensor:
+    """Single-device capacity-limited experts with static shapes: kept assignments are copied into fixed expert slots,
+    the experts run as grouped GEMMs with device-side counts, dropped assignments read a row of zeros."""
+    N, H = flat.shape
+    k = expert_idx.shape[1]
+    gates, ups, downs = weights
+    E = len(gates)
+    slot = (capacity + 127) // 128 * 128
+    a_expert = torch.where(keep.reshape(-1), expert_idx.reshape(-1), torch.full_like(expert_idx.reshape(-1), E))
+    token_of = torch.arange(N, device=flat.device).repeat_interleave(k)
+    order = torch.argsort(a_expert, stable=True)
+    sorted_e = a_expert[order]
+    counts = torch.bincount(a_expert, minlength=E + 1)
+    start = counts.cumsum(0) - counts
+    pos = torch.arange(sorted_e.numel(), device=flat.device) - start[sorted_e]
+    trash = E * slot                                                # one extra block of rows that nothing reads
+    row = torch.where(sorted_e < E, sorted_e * slot + pos, torch.full_like(pos, trash))
+    tokens_sorted = token_of[order]
+    buf = torch.zeros((E * slot + 64, H), dtype=flat.dtype, device=flat.device).index_copy(0, row, flat.index_select(0, tokens_sorted))
+    y = grouped_swiglu_experts(buf[:E * slot], counts[:E].to(torch.int32), slot, gates, ups, downs)
+    y = torch.cat([y, y.new_zeros((64, H))], dim=0)
+    gated = y.index_select(0, row) * gate.reshape(-1)[order].unsqueeze(1).to(flat.dtype)
+    return torch.zeros_like(flat).index_add(0, tokens_sorted, gated)
+
+
 def moe_experts_forward(flat: torch.Tensor, expert_idx: torch.Tensor, gate: torch.Tensor, keep: torch.Tensor | None,
-                        experts: list) -> torch.Tensor:
-    """``flat [N,H]``, ``expert_idx/gate [N,k]``, ``keep [N,k]`` bool or None, ``experts``: callables ``[n,H]->[n,H]``."""
+                        experts: list, capacity: int | None = None) -> torch.Tensor:
+    """``flat [N,H]``, ``expert_idx/gate [N,k]``, ``keep [N,k]`` bool or None, ``experts``: callables ``[n,H]->[n,H]``.
+    With a capacity limit on CUDA the grouped, host-sync-free path runs (``capacity`` = rows an expert may take)."""
+    if keep is not None and capacity is not None:
+        weights = swiglu_expert_weights(experts, flat)
+        if weights is not None:
+            return _moe_experts_forward_static(flat, expert_idx, gate, keep, weights, capacity)
     N, H = flat.shape
     k = expert_idx.shape[1]
     E = len(experts)
@@ -125,7 +175,11 @@ class _GroupedSwiGLUExperts(torch.autograd.Function):
         x, counts, hg, hu, *weights = ctx.saved_tensors
         n, cap = ctx.n, ctx.cap
         gates, ups, downs = weights[:n], weights[n:2 * n], weights[2 * n:]
-        dy = dy.contiguous()
+        # rows beyond an expert's count may hold anything in the incoming gradient buffer: they must be zero for the
+        # weight-gradient reductions, which run over whole 64-row blocks
+        r = torch.arange(dy.shape[0], device=dy.device)
+        valid = torch.remainder(r, cap) < counts.to(torch.long)[torch.div(r, cap, rounding_mode="floor")]
+        dy = torch.where(valid.unsqueeze(1), dy, torch.zeros((), dtype=dy.dtype, device=dy.device)).contiguous()
         dact = grouped_gemm(1, dy, list(downs), counts, cap)                    # [rows, F]   (down_g is [H, F] = [K, N])
         with torch.enable_grad():
             g_, u_ = hg.detach().requires_grad_(True), hu.detach().requires_grad_(True)

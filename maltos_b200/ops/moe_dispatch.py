@@ -45,14 +45,23 @@ class DispatchPlan:
     peer_row: torch.Tensor           # [M] int64 row in the destination's buffer
     recv_rows: int                   # rows this rank receives
     capacity: int                    # rows of the symmetric buffers (same on every rank)
-    local_counts: list[int]          # received rows per local expert, expert order
+    local_counts: list[int] | None   # received rows per local expert, expert order (host copy; None for a static plan)
+    recv_counts: torch.Tensor | None = None   # static plan: int32 device tensor, valid rows of every local expert's slot
+    slot_rows: int = 0               # static plan: rows of one local expert's slot
 
     @property
     def row_bytes(self) -> int:
         return self.hidden * torch.empty((), dtype=self.dtype).element_size()
 
     def buffer(self, name: str):
-        return self.ctx.ensure_buffer(f"moe_{name}", self.capacity * self.row_bytes)
+        sb = self.ctx.ensure_buffer(f"moe_{name}", self.capacity * self.row_bytes)
+        if not getattr(sb, "_cleared", False):
+            # a fresh allocation may hold any bit pattern; rows nobody writes must at least be finite numbers
+            sb.local_tensor(torch.uint8, sb.nbytes, self.order.device).zero_()
+            torch.cuda.current_stream().synchronize()
+            dist.barrier(group=self.group)
+            sb._cleared = True
+        return sb
 
     def local_rows(self, name: str) -> torch.Tensor:
         sb = self.buffer(name)
@@ -116,6 +125,39 @@ def build_plan(ctx, group, expert_of_assignment: torch.Tensor, num_experts: int,
     capacity = max(1024, 1 << (need - 1).bit_length())               # grows in powers of two: few collective re-allocations
     return DispatchPlan(ctx=ctx, group=group, hidden=hidden, dtype=dtype, order=order, peer_rank=peer_rank, peer_row=peer_row,
                         recv_rows=int(recv_rows[rank]), capacity=capacity, local_counts=[int(c) for c in local_counts])
+
+
+def static_slot_rows(world: int, per_source_capacity: int) -> int:
+    """Rows of one local expert's slot when every source sends at most ``per_source_capacity`` rows to it."""
+    return (world * per_source_capacity + 127) // 128 * 128
+
+
+def build_static_plan(ctx, group, expert_of_assignment: torch.Tensor, num_experts: int, hidden: int, dtype: torch.dtype,
+                      per_source_capacity: int) -> DispatchPlan:
+    """Plan with STATIC shapes and no host read. ``expert_of_assignment [M]`` holds the expert of every (token, choice) or
+    ``num_experts`` for an assignment the capacity limit dropped; every source sends at most ``per_source_capacity`` rows
+    to one expert, so a local expert's slot of ``static_slot_rows`` rows always suffices. Collective over ``group`` (one
+    all-gather of the counts, which stay on the device); the valid rows per local expert come back as a device tensor
+    for the grouped expert GEMM."""
+    rank, world = ctx.rank, ctx.world
+    per = num_experts // world
+    dev = expert_of_assignment.device
+    slot = static_slot_rows(world, per_source_capacity)
+    counts = torch.bincount(expert_of_assignment, minlength=num_experts + 1)              # [E + 1], last = dropped
+    all_counts = torch.empty(world, num_experts + 1, dtype=counts.dtype, device=dev)
+    dist.all_gather_into_tensor(all_counts.view(-1), counts, group=group)
+    order = torch.argsort(expert_of_assignment, stable=True)
+    sorted_e = expert_of_assignment[order]
+    group_start = counts.cumsum(0) - counts
+    pos = torch.arange(sorted_e.numel(), device=dev) - group_start[sorted_e]
+    before_me = all_counts[:rank].sum(0) if rank > 0 else torch.zeros_like(counts)       # rows of lower ranks per expert
+    valid = sorted_e < num_experts
+    local_e = torch.remainder(sorted_e, per)
+    peer_row = torch.where(valid, local_e * slot + before_me[sorted_e] + pos, torch.zeros_like(pos)).to(torch.int64)
+    peer_rank = torch.where(valid, torch.div(sorted_e, per, rounding_mode="floor"), torch.full_like(sorted_e, -1)).to(torch.int32)
+    recv_counts = all_counts[:, rank * per:(rank + 1) * per].sum(0).to(torch.int32)
+    return DispatchPlan(ctx=ctx, group=group, hidden=hidden, dtype=dtype, order=order, peer_rank=peer_rank, peer_row=peer_row,
+                        recv_rows=per * slot, capacity=per * slot, local_counts=None, recv_counts=recv_counts, slot_rows=slot)
 
 
 class _PeerDispatch(torch.autograd.Function):

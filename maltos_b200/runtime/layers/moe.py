@@ -105,12 +105,18 @@ class ExpertParallelMoE(nn.Module):
         a_expert = idx.reshape(-1)
         a_gate = gate.reshape(-1)
         a_token = torch.arange(N, device=x.device).repeat_interleave(self.top_k)
+        from maltos_b200.ops import moe_dispatch
+        from maltos_b200.ops.moe import swiglu_expert_weights
+
+        peer = moe_dispatch.peer_context(self.ep_group, flat)
+        weights = swiglu_expert_weights(self.local_experts, flat) if (peer is not None and keep is not None) else None
+        if weights is not None:
+            # capacity-bounded product path: static shapes end to end, counts stay on the device (no host read)
+            out = self._forward_peer_static(peer, flat, a_expert, a_gate, a_token, keep.reshape(-1), cap, weights).view(B, S, H)
+            return (out, aux) if return_aux_loss else out
         if keep is not None:                                              # dropped assignments are not sent at all
             sel = keep.reshape(-1).nonzero(as_tuple=False).flatten()
             a_expert, a_gate, a_token = a_expert[sel], a_gate[sel], a_token[sel]
-        from maltos_b200.ops import moe_dispatch
-
-        peer = moe_dispatch.peer_context(self.ep_group, flat)
         if peer is not None:
             out = self._forward_peer(peer, flat, a_expert, a_gate, a_token).view(B, S, H)
             return (out, aux) if return_aux_loss else out
@@ -144,6 +150,24 @@ class ExpertParallelMoE(nn.Module):
         if not return_aux_loss:
             return out
         return out, aux
+
+    def _forward_peer_static(self, peer, flat, a_expert, a_gate, a_token, keep, cap, weights):
+        """Capacity-limited routing with static shapes: dropped assignments keep their place in the (token, choice) list
+        with the sentinel expert ``num_experts``; rows travel one-sided into fixed expert slots of the owners' symmetric
+        buffers; ALL local experts run in one grouped tcgen05 GEMM launch per projection that reads the valid row counts
+        from device memory. Nothing in this path waits for the host."""
+        from maltos_b200.ops import moe_dispatch
+        from maltos_b200.ops.moe import grouped_swiglu_experts
+
+        a_expert = torch.where(keep, a_expert, torch.full_like(a_expert, self.num_experts))
+        plan = moe_dispatch.build_static_plan(peer, self.ep_group, a_expert, self.num_experts, flat.shape[1], flat.dtype, cap)
+        token_of_row = a_token[plan.order]
+        received = moe_dispatch.dispatch(flat, token_of_row, plan)          # [experts_here * slot_rows, H]
+        gates, ups, downs = weights
+        processed = grouped_swiglu_experts(received, plan.recv_counts, plan.slot_rows, gates, ups, downs)
+        back = moe_dispatch.combine(processed, plan)                        # [N * k, H]; zeros for dropped assignments
+        gated = back * a_gate[plan.order].unsqueeze(1).to(back.dtype)
+        return torch.zeros_like(flat).index_add(0, token_of_row, gated)
 
     def _forward_peer(self, peer, flat, a_expert, a_gate, a_token):
         """Dispatch / combine as one-sided row transfers through the peers' symmetric buffers."""

@@ -64,7 +64,7 @@ def test_push_and_pull_rows_between_emulated_ranks(hidden, dtype):
 
 
 # ------------------------------------------------------------------------------------------------ layer on 2 GPUs
-def _layer_run(rank, world, group, peer_mode, top_k, capacity):
+def _layer_run(rank, world, group, peer_mode, top_k, capacity, swiglu=False):
     import torch.distributed as dist
     import torch.nn as nn
 
@@ -74,7 +74,12 @@ def _layer_run(rank, world, group, peer_mode, top_k, capacity):
     H, E, N = 128, 4, 96
     torch.manual_seed(11)
     router = nn.Linear(H, E, bias=False).cuda().bfloat16()
-    experts = nn.ModuleList([nn.Sequential(nn.Linear(H, 2 * H, bias=False), nn.GELU(), nn.Linear(2 * H, H, bias=False)) for _ in range(E)]).cuda().bfloat16()
+    if swiglu:   # SwiGLU experts + a capacity limit: the peer path is then the static one with the grouped expert GEMM
+        from maltos_b200.models.tiny_transformer import MLP
+
+        experts = nn.ModuleList([MLP(H, 2 * H) for _ in range(E)]).cuda().bfloat16()
+    else:
+        experts = nn.ModuleList([nn.Sequential(nn.Linear(H, 2 * H, bias=False), nn.GELU(), nn.Linear(2 * H, H, bias=False)) for _ in range(E)]).cuda().bfloat16()
     per = E // world
     ids = list(range(rank * per, (rank + 1) * per))
     layer = ExpertParallelMoE(router=router, local_experts=nn.ModuleList([experts[i] for i in ids]), local_expert_ids=ids, dim=H,
@@ -109,6 +114,10 @@ def _worker(rank, world, port, queue):
         res = {}
         for top_k, capacity in ((1, None), (2, None), (2, 1.0)):
             res[(top_k, capacity)] = (_layer_run(rank, world, group, False, top_k, capacity), _layer_run(rank, world, group, True, top_k, capacity))
+        before = _lib.launch_count()
+        res[("swiglu", 2, 1.0)] = (_layer_run(rank, world, group, False, 2, 1.0, True), _layer_run(rank, world, group, True, 2, 1.0, True))
+        res[("swiglu", 1, 1.25)] = (_layer_run(rank, world, group, False, 1, 1.25, True), _layer_run(rank, world, group, True, 1, 1.25, True))
+        assert _lib.launch_count() > before
         queue.put((rank, "ok", (res, _lib.fetch_status(raise_on_error=False))))
     except BaseException:  # noqa: BLE001
         queue.put((rank, "error", traceback.format_exc()))

@@ -72,3 +72,30 @@ def test_grouped_swiglu_experts_match_per_expert_autograd():
         _close(ups[g].grad, wu.grad if n else torch.zeros_like(wu), 3e-2)
         _close(downs[g].grad, wd.grad if n else torch.zeros_like(wd), 3e-2)
     _lib.fetch_status()
+
+
+def test_single_device_capacity_path_is_static_and_matches_the_per_expert_loop():
+    from maltos_b200.models.tiny_moe_transformer import TopKMoE
+    from maltos_b200.ops import moe as moe_ops
+
+    torch.manual_seed(2)
+    layer = TopKMoE(128, 256, 8, top_k=2, capacity_factor=1.0).to(DEV).bfloat16()
+    x = torch.randn(2, 96, 128, device=DEV).bfloat16()
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, aux = layer(xa, return_aux_loss=True)                       # grouped path (capacity set, SwiGLU experts, CUDA bf16)
+    ya.float().pow(2).mean().backward()
+    ga = [p.grad.clone() for p in layer.parameters()]
+    for p in layer.parameters():
+        p.grad = None
+    orig = moe_ops.swiglu_expert_weights
+    moe_ops.swiglu_expert_weights = lambda *a, **k: None           # force the per-expert loop with host-read counts
+    try:
+        yb = layer(xb)
+    finally:
+        moe_ops.swiglu_expert_weights = orig
+    yb.float().pow(2).mean().backward()
+    _close(ya, yb.float(), 3e-2)
+    _close(xa.grad, xb.grad.float(), 3e-2)
+    for a, p in zip(ga, layer.parameters()):
+        _close(a, p.grad.float(), 4e-2)
+    _lib.fetch_status()
