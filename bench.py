@@ -34,6 +34,37 @@ SMALL = dict(layers=2, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=1024, seq
 GLOBAL_BATCH = 32
 
 
+# Other configurations of the baseline's list: (recipe both frameworks ship, training-flag overrides, GPUs, synthetic layout).
+_LLAMA8B = ["--model", "llama", "--dim", "4096", "--n-heads", "32", "--n-kv-heads", "8", "--hidden-size", "14336", "--n-layers", "32",
+            "--vocab-size", "128256", "--seq-len", "8192", "--eps", "1e-5", "--precision", "bf16", "--activation-checkpointing", "--fused-adamw"]
+_MOE = ["--model", "tiny_moe", "--dim", "1024", "--n-heads", "16", "--n-kv-heads", "16", "--hidden-size", "2816", "--n-layers", "12",
+        "--num-experts", "64", "--moe-aux-loss-coef", "0.01", "--vocab-size", "32000", "--seq-len", "4096", "--micro-batch-size", "1",
+        "--grad-accum-steps", "8", "--dp-size", "8", "--tp-size", "1", "--ep-size", "8", "--no-use-sp", "--zero-stage", "2", "--precision", "bf16",
+        "--fused-adamw", "--grad-clip", "1.0"]
+CONFIGS = {
+    "llama8b": None,
+    "llama50m": dict(gpus=8, layout="dense", what="LLaMA ~50M, DP4 x TP2 + SP + ZeRO-3, seq 2048, global batch 64",
+                     overrides=["--model", "llama", "--dim", "512", "--n-heads", "8", "--n-kv-heads", "8", "--hidden-size", "1408", "--n-layers", "8",
+                                "--vocab-size", "32000", "--seq-len", "2048", "--micro-batch-size", "4", "--grad-accum-steps", "4", "--dp-size", "4",
+                                "--tp-size", "2", "--use-sp", "--zero-stage", "3", "--precision", "bf16", "--fused-adamw", "--grad-clip", "1.0"]),
+    "llama8b_zero3": dict(gpus=8, layout="dense", what="LLaMA-3 8B, DP2 x TP4 + SP + ZeRO-3, seq 8192, global batch 32",
+                          overrides=_LLAMA8B + ["--micro-batch-size", "1", "--grad-accum-steps", "16", "--dp-size", "2", "--tp-size", "4", "--use-sp",
+                                                "--zero-stage", "3"]),
+    "moe64e": dict(gpus=8, layout="dense", what="64-expert MoE (12 L, d 1024, expert FFN 2816), EP8 + ZeRO-2, seq 4096, global batch 64, top-1 router",
+                   overrides=_MOE),
+    "moe64e_top2": dict(gpus=8, layout="dense", ours_only="the reference has no top-2 / capacity-factor router",
+                        what="the same MoE with the top-2 router and capacity factor 1.25 (static shapes, grouped expert GEMMs)",
+                        overrides=_MOE + ["--moe-top-k", "2", "--moe-capacity-factor", "1.25"]),
+    "olmo13b": dict(gpus=8, layout="packed", what="OLMo-2 13B packed rows, TP2 x CP2 (zigzag ring) x PP2, 8 micro-batches, seq 4096",
+                    overrides=["--model", "olmo2", "--dim", "5120", "--n-heads", "40", "--n-kv-heads", "40", "--hidden-size", "13824", "--n-layers", "40",
+                               "--vocab-size", "100352", "--seq-len", "4096", "--micro-batch-size", "8", "--grad-accum-steps", "1", "--dp-size", "1",
+                               "--tp-size", "2", "--use-sp", "--cp-size", "2", "--pp-size", "2", "--pp-microbatches", "8", "--cp-attn-core", "ring",
+                               "--cp-token-planner", "fixed_zigzag", "--attention-backend", "flash_attn", "--zero-stage", "0", "--precision", "bf16",
+                               "--activation-checkpointing", "--fused-adamw"],
+                    ours_extra=["--pp-schedule", "1f1b"], note="the reference CLI cannot select 1F1B: its arm runs its default schedule (AFAB)"),
+}
+
+
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -49,6 +80,12 @@ def parse_args(argv=None):
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
     ap.add_argument("--kernel-table", default=None, help="debugging: write rank 0's per-kernel device-time table of one extra step to this file")
     ap.add_argument("--layers", type=int, default=None, help="debugging only: fewer layers (the JSON line is then marked invalid)")
+    ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS),
+                    help="llama8b (default): the headline LLaMA-3 8B run, TP = N. The others are fixed multi-GPU recipes of the "
+                         "baseline's config list, run through each framework's own synthetic-throughput harness")
+    ap.add_argument("--exposed-comm", action=argparse.BooleanOptionalAction, default=None,
+                    help="profile ONE extra step after the timed regions and report the communication time no compute kernel covers "
+                         "(default: on for N > 1)")
     args = ap.parse_args(argv)
     args.micro_batch_auto = args.micro_batch is None
     if args.micro_batch is None:
@@ -211,6 +248,28 @@ DATA_NOTE = (f"synthetic uniform token ids, {POOL_STEPS} steps x global batch of
              "arms), repeating after that")
 
 
+def measure_exposed_comm(step_fn, device) -> dict | None:
+    """Profile ONE extra optimizer step (outside every timed region) on every rank and report, as the maximum over ranks,
+    the communication time that no compute kernel covers: |union(comm kernels) - union(compute kernels)|."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    sys.path.insert(0, str(ROOT))
+    from maltos_b200.utils.profiling import exposed_comm_us, kernels_of_profile
+
+    if device.type != "cuda":
+        return None
+    barrier_sync(device)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn()
+        torch.cuda.synchronize(device)
+    exposed, comm, busy = exposed_comm_us(kernels_of_profile(prof))
+    del prof
+    return {"exposed_ms_per_step": max_over_ranks(exposed / 1e3, device), "comm_ms_per_step": max_over_ranks(comm / 1e3, device),
+            "busy_ms_per_step": max_over_ranks(busy / 1e3, device),
+            "rule": "one profiled step; union of communication-kernel intervals not covered by any compute kernel; max over ranks"}
+
+
 def emit(payload: dict) -> None:
     print(json.dumps(payload), flush=True)
 
@@ -360,6 +419,9 @@ def run_ours(args) -> None:
         e2e = {"value": tokens_per_step / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": host.bytes_per_batch * accum,
                "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "loss": last_loss}
 
+    exposed = None
+    if (args.exposed_comm if args.exposed_comm is not None else world > 1) and use_cuda:
+        exposed = measure_exposed_comm(lambda: one_step(dev_batches, read_loss=False), device)
     status = _lib.fetch_status(raise_on_error=False) if use_cuda else (0, 0, 0, 0)
     peak_gib = torch.cuda.max_memory_allocated(device) / 2**30 if use_cuda else 0.0
     if rank == 0:
@@ -377,7 +439,7 @@ def run_ours(args) -> None:
                        "optimizer": "fused AdamW, fp32 master weights",
                        "l2_policy": "working set (16 GB of bf16 weights + activations per micro-step) is far larger than the 126 MB L2; no explicit flush",
                        "baseline_note": "no published number exists for this config; the same-box reference arm is the bar"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "kernel_status": list(status),
+            "clocks": clocks, "e2e": e2e, "exposed_comm": exposed, "gpu_launches": int(launches), "kernel_status": list(status),
             "peak_mem_gib": round(peak_gib, 1),
         })
     runtime.close()
@@ -491,6 +553,9 @@ def run_reference(args) -> None:
             e2e_s = max_over_ranks(time.perf_counter() - t0, device) / args.steps
             e2e = {"value": tokens_per_step / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": host.bytes_per_batch * accum,
                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "loss": last}
+        exposed = None
+        if (args.exposed_comm if args.exposed_comm is not None else world > 1) and use_cuda:
+            exposed = measure_exposed_comm(lambda: one_step(dev_batches, False), device)
         if rank == 0:
             emit({"metric": "LLaMA-8B train tokens/sec (max over ranks)" if not args.small else "SMALL plumbing check (not a benchmark)",
                   "value": tokens_per_step / (ms_per_step / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -501,7 +566,7 @@ def run_reference(args) -> None:
                              "seq_len": seq, "micro_batch": micro, "grad_accum": accum, "micro_batch_policy": MICRO_BATCH_POLICY,
                              "parallelism": f"tp{tp}+sp" if tp > 1 else "single-gpu", "attention_backend": ref_args.attention_backend,
                              "zero_stage": 0, "note": "reference CLI rejects ZeRO-1 with dp=1 and has no rope_theta flag"},
-                  "clocks": clocks, "e2e": e2e, "gpu_launches": 0})
+                  "clocks": clocks, "e2e": e2e, "exposed_comm": exposed, "gpu_launches": 0})
         core.close()
         import torch.distributed as dist
 
@@ -522,8 +587,76 @@ def run_reference(args) -> None:
             pass
 
 
+def run_recipe(args) -> None:
+    """One of the fixed multi-GPU configurations, through the framework's own synthetic-throughput harness
+    (``tools/profile_train_perf.py`` of either tree: same flags, per-step maximum over ranks, lr = 0)."""
+    import tempfile
+
+    spec = CONFIGS[args.config]
+    rank, local, world = dist_env()
+    ref = args.impl == "reference"
+
+    def unavailable(reason: str) -> None:
+        if rank == 0:
+            emit({"impl": args.impl, "config": {"name": args.config}, "unavailable": reason})
+
+    if world != spec["gpus"] or args.gpus != spec["gpus"]:
+        return unavailable(f"config {args.config} is defined on {spec['gpus']} GPUs (launch with torchrun and --gpus {spec['gpus']})")
+    if ref and spec.get("ours_only"):
+        return unavailable(spec["ours_only"])
+    root = (ROOT / "baseline" / "_ref") if ref else ROOT
+    if ref and not (root / "tools" / "profile_train_perf.py").exists():
+        return unavailable("baseline/_ref is not installed")
+    sys.path.insert(0, str(root))
+    if ref:
+        import tools.profile_train_perf as harness
+    else:
+        import maltos_b200  # noqa: F401
+        from maltos_b200.tools import profile_train_perf as harness
+    out_dir = Path(tempfile.mkdtemp(prefix=f"bench_{args.config}_")) if rank == 0 else Path(tempfile.gettempdir()) / f"bench_{args.config}_rank{rank}"
+    overrides = list(spec["overrides"]) + ([] if ref else list(spec.get("ours_extra", [])))
+    want_comm = args.exposed_comm if args.exposed_comm is not None else False
+    argv = ["--recipe", str(root / "configs" / "llama_50m.yaml"), "--warmup", str(args.warmup), "--steps", str(args.steps), "--seed", "0",
+            "--synthetic-layout", spec["layout"], "--output-dir", str(out_dir)] + (["--profile"] if want_comm else []) + ["--", *overrides]
+    try:
+        if ref:      # the reference's harness reads the process arguments
+            sys.argv = [str(root / "tools" / "profile_train_perf.py"), *argv]
+            harness.main()
+        else:
+            harness.main(argv)
+    except BaseException as exc:  # noqa: BLE001 - always answer with one JSON line
+        if isinstance(exc, KeyboardInterrupt):
+            raise
+        return unavailable(f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300])
+    if rank != 0:
+        return
+    summary = json.loads((out_dir / "summary.json").read_text())
+    exposed = None
+    traces = sorted(out_dir.rglob("*.json"))
+    traces = [t for t in traces if t.name != "summary.json"]
+    if want_comm and traces:
+        sys.path.insert(0, str(ROOT))
+        from maltos_b200.utils.profiling import exposed_comm_us, kernels_of_chrome_trace
+
+        e, c, b = exposed_comm_us(kernels_of_chrome_trace(traces[0]))
+        exposed = {"exposed_ms_per_step": e / 1e3 / args.steps, "comm_ms_per_step": c / 1e3 / args.steps, "busy_ms_per_step": b / 1e3 / args.steps,
+                   "source": "rank 0 trace of the timed steps"}
+    tok_s = summary.get("tokens_per_second", summary.get("throughput_tokens_per_second"))
+    mean_s = summary.get("mean_step_seconds", (summary.get("timing_seconds") or {}).get("mean"))
+    emit({"metric": f"{args.config} train tokens/sec (max over ranks)", "value": tok_s, "unit": "tokens/s",
+          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3,
+          "higher_is_better": True, "scaling": "fixed configuration", "vs_baseline": None, "dtype": "bf16", "impl": args.impl,
+          "data": "synthetic token ids from the harness's seeded generator (seed 0), lr 0",
+          "config": {"name": args.config, "what": spec["what"], "flags": overrides, "note": spec.get("note"),
+                     "timing": "host timer around device synchronisation per step, maximum over ranks (the harness's own rule)"},
+          "exposed_comm": exposed, "peak_mem_gib": summary.get("peak_memory_gib", summary.get("peak_allocated_gib"))})
+
+
 def main(argv=None) -> int:
     args = parse_args(argv)
+    if args.config != "llama8b":
+        run_recipe(args)
+        return 0
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -700,26 +700,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
         issue_dp(0);
       }
-      for (int j = 0; ok && j < n_blocks; ++j) {
-        if (j + 1 < n_blocks) {
-          ok = mbar_wait(&k_full[(j + 1) % K_STAGES], ((j + 1) / K_STAGES) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          MB_PROBE(true, j, 0);
-          issue_s(j + 1);           // its S buffer was last read by dQ of block j - 1, issued before
-          MB_PROBE(true, j, 1);
-          ok = mbar_wait(dp_free, j & 1, abort_flag) &&   // block j's dP has been read
-               mbar_wait(&v_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          MB_PROBE(true, j, 2);
-          issue_dp(j + 1);
-          MB_PROBE(true, j, 3);
-        }
-        ok = mbar_wait(ds_full, j & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        MB_PROBE(true, j, 4);
+      // Issue order per block j: dQ of block j - 1 first (its dS has just been finished by the arithmetic warps, which
+      // now start on block j), then dP and S of block j + 1. The only wait that can really block is the one on dS; the
+      // loads and the "dP consumed" signal it waits for next arrive while dQ(j - 1) is being issued, so the tensor pipe
+      // never idles behind this thread.
+      auto issue_dq = [&](int j) {
         const uint32_t k_lo = smem_desc_lo(smem_u32(sK + (j % K_STAGES) * TILE_BYTES), kDqKeys * 128);   // MN-major B: atoms kDqKeys * 128 bytes apart
         const uint32_t s_col = tmem_base + static_cast<uint32_t>(j & 1) * 128u;
         const uint32_t acc0 = j != 0 ? 1u : 0u;
@@ -730,7 +715,38 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           umma_bf16_ts_lh(tmem_base + DQ_COL, s_col + a_col, k_lo + static_cast<uint32_t>(kk * 128), hi_k, idesc_dq, kk != 0 ? 1u : acc0);
         }
         umma_commit(&k_empty[j % K_STAGES]);
-        MB_PROBE(true, j, 5);
+      };
+      for (int j = 0; ok && j < n_blocks; ++j) {
+        if (j > 0) {
+          ok = mbar_wait(ds_full, (j - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          MB_PROBE(true, j, 4);
+          issue_dq(j - 1);
+          MB_PROBE(true, j, 5);
+        }
+        if (j + 1 < n_blocks) {
+          ok = mbar_wait(dp_free, j & 1, abort_flag) &&   // block j's dP has been read
+               mbar_wait(&v_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          MB_PROBE(true, j, 2);
+          issue_dp(j + 1);
+          MB_PROBE(true, j, 3);
+          ok = mbar_wait(&k_full[(j + 1) % K_STAGES], ((j + 1) / K_STAGES) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          MB_PROBE(true, j, 0);
+          issue_s(j + 1);           // its S buffer was last read by dQ of block j - 1, issued above
+          MB_PROBE(true, j, 1);
+        }
+      }
+      if (ok) {
+        ok = mbar_wait(ds_full, (n_blocks - 1) & 1, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          issue_dq(n_blocks - 1);
+        }
       }
       if (ok) umma_commit(dq_full);
     }

@@ -16,7 +16,7 @@ from maltos_b200.ops.cross_entropy import linear_cross_entropy
 from maltos_b200.ops.gemm import linear
 from maltos_b200.ops.grouped import grouped_linear
 from maltos_b200.utils.activation_checkpoint import activation_checkpoint_context_fn
-from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
+from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
                                          POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 from maltos_b200.utils.losses import causal_cross_entropy
 
@@ -118,8 +118,19 @@ def lm_loss(hidden: torch.Tensor, lm_head: nn.Module, labels: torch.Tensor, loss
         labels = _local_sequence_slice(labels, group, hidden.shape[1])
     if isinstance(lm_head, nn.Linear) and lm_head.bias is None and not lm_head._forward_pre_hooks and not lm_head._forward_hooks:
         loss = linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), lm_head.weight, labels.reshape(-1), group=group)
-    else:
+    elif group is None:
         loss = causal_cross_entropy(lm_head(hidden), labels)
+    else:
+        # The head runs through its own forward (another plugin hooked it, e.g. ZeRO-3 gathers its weight there). Each
+        # rank scores its own tokens; the mean must still be taken over the targets of the WHOLE sequence, which the
+        # ranks' slices share unevenly in packed rows: local mean x local / global target count, summed over the group.
+        from maltos_b200.ops.cross_entropy import _global_count, _GroupSum
+
+        local = causal_cross_entropy(lm_head(hidden), labels)
+        flat = labels.reshape(-1)
+        local_count = (flat != IGNORE_INDEX).sum()
+        global_count = _global_count(flat, IGNORE_INDEX, group).clamp_min(1)
+        loss = _GroupSum.apply(local * (local_count.to(local.dtype) / global_count.to(local.dtype)), group)
     if loss_weight is not None:
         loss = loss * float(loss_weight)
     return loss

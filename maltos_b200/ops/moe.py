@@ -81,8 +81,8 @@ def moe_experts_forward(flat: torch.Tensor, expert_idx: torch.Tensor, gate: torc
     at = 0
     pieces = []
     for e, n in enumerate(counts):
-        if n == 0:
-            continue
+        # every expert is entered, also with zero rows: under sharded parameters (ZeRO-3) each call gathers the
+        # expert's weights collectively, so all ranks must make the same sequence of calls
         pieces.append(experts[e](gathered[at:at + n]) * gates_sorted[at:at + n])
         at += n
     if pieces:

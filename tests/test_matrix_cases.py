@@ -1,0 +1,349 @@
+"""Equivalence and resume matrix on 8 gloo ranks (CPU, fp32).
+
+The idea of the reference's matrix (``tests/full_stack_matrix_cases.py:209-629``, 144 cases run by
+``tests/tiny_transformer_full_stack_matrix_runner.py`` in long-lived "merged" workers) with this framework's own case
+list: every case is a set of ordinary training flags; ONE group of 8 worker processes builds model and runtime for case
+after case through the CLI's own builders (``train.cli._build_model`` / ``_build_runtime``, i.e. the plugin selection a
+user gets), trains two optimizer steps on a fixed global batch and reports the loss of every rank. The parent turns the
+per-rank losses into the global loss and compares it with single-process full-batch training of the same model.
+
+Covered: DP (sync / bucketed), ZeRO 0-3, TP, TP+SP, PP (AFAB / 1F1B), CP (all-gather K/V / zigzag ring), EP with 2 / 4 /
+8-way expert groups, gradient accumulation, activation checkpointing, packed batches, LLaMA / OLMo-2 / tiny / MoE models.
+The resume half (``tests/tiny_transformer_full_stack_resume.py:189-357`` in the reference) saves a sharded checkpoint
+at a step boundary or in the middle of an accumulation window, rebuilds the runtime, loads and continues; the
+continued losses must equal those of the uninterrupted run.
+"""
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+
+WORLD = 8
+VOCAB, SEQ, GLOBAL_ROWS, STEPS = 128, 32, 8, 2
+
+MODELS = {
+    "llama": ["--model", "llama", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "4", "--hidden-size", "128", "--n-layers", "4"],
+    "olmo": ["--model", "olmo2", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "4", "--hidden-size", "128", "--n-layers", "4"],
+    "tiny": ["--model", "tiny", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "128", "--n-layers", "4"],
+    "moe": ["--model", "tiny_moe", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "96", "--n-layers", "2", "--num-experts", "8",
+            "--moe-aux-loss-coef", "0"],
+}
+COMMON = ["--vocab-size", str(VOCAB), "--seq-len", str(SEQ), "--lr", "1e-3", "--weight-decay", "0.01", "--grad-clip", "1.0", "--seed", "5",
+          "--precision", "fp32", "--disable-metrics"]
+
+
+def C(model, flags, *, accum=1, packed=False, pp_mb=None):
+    return dict(model=model, flags=flags.split(), accum=accum, packed=packed, pp_mb=pp_mb)
+
+
+CASES = {
+    # ---- data parallel and the ZeRO stages
+    "dp8_sync": C("llama", "--dp-size 8 --ddp-mode sync"),
+    "dp8_async": C("llama", "--dp-size 8 --ddp-mode async"),
+    "dp8_bucket_accum2": C("llama", "--dp-size 8 --ddp-mode bucket", accum=1),
+    "dp4_bucket_tp2": C("llama", "--dp-size 4 --tp-size 2 --ddp-mode bucket", accum=2),
+    "dp8_zero1": C("llama", "--dp-size 8 --zero-stage 1"),
+    "dp4_zero2_tp2_accum2": C("llama", "--dp-size 4 --tp-size 2 --zero-stage 2", accum=2),
+    "dp8_zero3": C("llama", "--dp-size 8 --zero-stage 3"),
+    "dp4_zero3_tp2_accum2": C("llama", "--dp-size 4 --tp-size 2 --zero-stage 3", accum=2),
+    # ---- tensor / sequence parallel
+    "dp4_tp2": C("llama", "--dp-size 4 --tp-size 2"),
+    "dp4_tp2_sp": C("llama", "--dp-size 4 --tp-size 2 --use-sp"),
+    "dp4_tp2_sp_zero1": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 1"),
+    "dp4_tp2_sp_zero2": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 2"),
+    "dp4_tp2_sp_zero3_accum2": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3", accum=2),
+    "dp2_tp4_sp_zero3": C("llama", "--dp-size 2 --tp-size 4 --use-sp --zero-stage 3"),
+    "tp4_dp2_sp_ckpt": C("llama", "--dp-size 2 --tp-size 4 --use-sp --activation-checkpointing"),
+    "dp4_tp2_sp_zero3_ckpt": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3 --activation-checkpointing"),
+    # ---- pipeline parallel
+    "dp2_pp2_tp2_afab": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --pp-schedule afab", pp_mb=2),
+    "dp2_pp2_tp2_1f1b_zero1": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --pp-schedule 1f1b --zero-stage 1", pp_mb=2),
+    "dp2_pp2_tp2_sp_1f1b_zero2": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --use-sp --pp-schedule 1f1b --zero-stage 2", pp_mb=2),
+    "dp2_pp2_tp2_sp_afab_zero3": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --use-sp --pp-schedule afab --zero-stage 3", pp_mb=2),
+    "dp2_pp4_1f1b": C("llama", "--dp-size 2 --pp-size 4 --pp-schedule 1f1b", pp_mb=4),
+    "dp4_pp2_afab_accum2": C("llama", "--dp-size 4 --pp-size 2 --pp-schedule afab", accum=2, pp_mb=1),
+    # ---- context parallel
+    "dp2_pp2_cp2_allgather_afab": C("llama", "--dp-size 2 --pp-size 2 --cp-size 2 --cp-attn-core all_gather_kv --pp-schedule afab", pp_mb=2),
+    "dp2_pp2_cp2_ring_1f1b_zero1": C("llama", "--dp-size 2 --pp-size 2 --cp-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag "
+                                              "--pp-schedule 1f1b --zero-stage 1", pp_mb=2),
+    "dp2_cp2_tp2_sp_ring_zero3": C("llama", "--dp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 3"),
+    "dp2_cp2_tp2_allgather_zero2": C("llama", "--dp-size 2 --cp-size 2 --tp-size 2 --cp-attn-core all_gather_kv --zero-stage 2"),
+    "pp2_cp2_tp2_sp_ring_1f1b": C("llama", "--pp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core ring --cp-token-planner fixed_zigzag --pp-schedule 1f1b",
+                                  pp_mb=2),
+    "pp2_cp2_tp2_allgather_afab": C("llama", "--pp-size 2 --cp-size 2 --tp-size 2 --cp-attn-core all_gather_kv --pp-schedule afab", pp_mb=4),
+    "dp2_cp4_ring_zero1": C("llama", "--dp-size 2 --cp-size 4 --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 1"),
+    "dp4_cp2_ring_contiguous": C("llama", "--dp-size 4 --cp-size 2 --cp-attn-core ring --cp-token-planner fixed_contiguous"),
+    # ---- packed rows (several documents per row, padding at the end)
+    "packed_dp4_tp2_sp_zero3": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3", packed=True),
+    "packed_dp4_tp2_sp": C("llama", "--dp-size 4 --tp-size 2 --use-sp", packed=True),
+    "packed_dp4_tp2_zero3": C("llama", "--dp-size 4 --tp-size 2 --zero-stage 3", packed=True),
+    "packed_dp8_zero1": C("llama", "--dp-size 8 --zero-stage 1", packed=True),
+    "packed_dp2_cp2_tp2_ring": C("llama", "--dp-size 2 --cp-size 2 --tp-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag", packed=True),
+    "packed_dp4_pp2_1f1b": C("llama", "--dp-size 4 --pp-size 2 --pp-schedule 1f1b", packed=True, pp_mb=2),
+    "packed_dp4_cp2_allgather_zero2": C("llama", "--dp-size 4 --cp-size 2 --cp-attn-core all_gather_kv --zero-stage 2", packed=True),
+    # ---- OLMo-2 (post-norm, QK-norm over the sharded projection width)
+    "olmo_dp4_tp2": C("olmo", "--dp-size 4 --tp-size 2"),
+    "olmo_dp4_tp2_sp_zero3": C("olmo", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3"),
+    "olmo_dp4_tp2_sp_zero3_ckpt": C("olmo", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3 --activation-checkpointing", accum=2),
+    "olmo_dp2_pp2_tp2_1f1b": C("olmo", "--dp-size 2 --pp-size 2 --tp-size 2 --pp-schedule 1f1b", pp_mb=2),
+    "olmo_packed_dp2_cp2_tp2_ring": C("olmo", "--dp-size 2 --cp-size 2 --tp-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag", packed=True),
+    "olmo_dp8_zero1": C("olmo", "--dp-size 8 --zero-stage 1"),
+    # ---- expert parallel (expert groups of 8, 4 and 2 ranks inside the data-parallel axis)
+    "moe_dp8_ep8": C("moe", "--dp-size 8 --ep-size 8"),
+    "moe_dp8_ep4_zero2": C("moe", "--dp-size 8 --ep-size 4 --zero-stage 2"),
+    "moe_dp8_ep2_zero1": C("moe", "--dp-size 8 --ep-size 2 --zero-stage 1"),
+    "moe_dp4_tp2_ep4": C("moe", "--dp-size 4 --tp-size 2 --ep-size 4"),
+    "moe_dp4_pp2_ep2_1f1b": C("moe", "--dp-size 4 --pp-size 2 --ep-size 2 --pp-schedule 1f1b", pp_mb=2),
+    "moe_dp4_pp2_ep4_afab_zero2": C("moe", "--dp-size 4 --pp-size 2 --ep-size 4 --pp-schedule afab --zero-stage 2", pp_mb=1, accum=2),
+    "moe_dp8_ep1_zero3": C("moe", "--dp-size 8 --zero-stage 3"),
+    # ---- the small reference transformer
+    "tiny_dp4_tp2_sp_zero3": C("tiny", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3"),
+    "tiny_dp4_pp2_afab": C("tiny", "--dp-size 4 --pp-size 2 --pp-schedule afab", pp_mb=2),
+}
+
+RESUME = {   # case name -> micro-steps to run before the checkpoint (a multiple of the case's accumulation = step boundary)
+    "dp4_tp2_sp_zero3_accum2": 2, "dp4_zero3_tp2_accum2": 3, "dp2_pp2_tp2_1f1b_zero1": 1, "dp2_cp2_tp2_sp_ring_zero3": 1, "moe_dp8_ep4_zero2": 1,
+    "olmo_dp4_tp2_sp_zero3_ckpt": 3, "dp4_bucket_tp2": 2, "dp2_pp2_tp2_sp_afab_zero3": 1,
+}
+
+
+def _global_batches(packed: bool):
+    """[step] -> dict of [GLOBAL_ROWS, SEQ] tensors, identical in every process."""
+    g = torch.Generator().manual_seed(77 + int(packed))
+    out = []
+    for _ in range(STEPS + 1):
+        ids = torch.randint(0, VOCAB, (GLOBAL_ROWS, SEQ), generator=g)
+        batch = {"input_ids": ids, "labels": ids.roll(-1, 1).clone()}
+        if packed:
+            seq = torch.full((GLOBAL_ROWS, SEQ), -1, dtype=torch.long)
+            pos = torch.zeros((GLOBAL_ROWS, SEQ), dtype=torch.long)
+            for r in range(GLOBAL_ROWS):
+                cuts = sorted({0, int(torch.randint(6, 14, (1,), generator=g)), int(torch.randint(16, 26, (1,), generator=g)), SEQ - 3})
+                for d, (a, b) in enumerate(zip(cuts, cuts[1:])):
+                    seq[r, a:b] = d
+                    pos[r, a:b] = torch.arange(b - a)
+                    batch["labels"][r, b - 1] = -100           # the last token of a document has no target
+            batch["labels"][seq == -1] = -100
+            batch["sequence_ids"], batch["position_ids"] = seq, pos
+        out.append(batch)
+    return out
+
+
+def _args(case):
+    import maltos_b200  # noqa: F401
+    from maltos_b200.train import flags
+
+    argv = MODELS[case["model"]] + COMMON + case["flags"] + ["--grad-accum-steps", str(case["accum"])]
+    if case["pp_mb"]:
+        argv += ["--pp-microbatches", str(case["pp_mb"])]
+    a = flags.parse_args_from(argv + ["--micro-batch-size", "1"], require_data=False)
+    a.micro_batch_size = GLOBAL_ROWS // (a.dp_size * case["accum"])
+    return a
+
+
+def _micro_batch(batch, dp_rank, dp, accum, m):
+    rows = GLOBAL_ROWS // (dp * accum)
+    lo = (m * dp + dp_rank) * rows
+    return {k: v[lo:lo + rows].clone() for k, v in batch.items()}
+
+
+def _build(case):
+    from maltos_b200.train import cli
+
+    a = _args(case)
+    cli.validate_args(a, WORLD)
+    torch.manual_seed(a.seed)
+    core = cli._build_runtime(a, cli._build_model(a), torch.device("cpu"))
+    return a, core
+
+
+def _worker(rank, world, names):
+    import torch.distributed as dist
+
+    from maltos_b200.runtime.mesh import MeshAxis
+
+    results = {}
+    for name in names:
+        case = CASES[name]
+        try:
+            a, core = _build(case)
+            core.setup()
+            core.model.train()
+            dp_group = core.get_group(MeshAxis.DP)
+            dp_rank = dist.get_rank(dp_group) if dp_group is not None else 0
+            losses = []
+            for step in range(STEPS):
+                for m in range(case["accum"]):
+                    loss, should = core.run_step(_micro_batch(_global_batches(case["packed"])[step], dp_rank, a.dp_size, case["accum"], m))
+                assert should
+                core.step_optimizer()
+                losses.append(float(core.collect_metrics()["loss"]))      # mean over the accumulation window
+            core.close()
+            results[name] = ("ok", losses, a.cp_size)
+        except Exception as exc:  # noqa: BLE001 - one broken case must not hide the others
+            import traceback
+
+            results[name] = ("error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()[-1500:]}", 1)
+            try:
+                dist.barrier()
+            except Exception:
+                pass
+    return results
+
+
+def _baseline(model: str, packed: bool):
+    """Single process, the whole global batch as one micro-batch."""
+    from maltos_b200.train import cli
+
+    case = C(model, "--dp-size 1")
+    a = _args(case)
+    a.micro_batch_size = GLOBAL_ROWS
+    torch.manual_seed(a.seed)
+    core = cli._build_runtime(a, cli._build_model(a), torch.device("cpu"))
+    core.setup()
+    core.model.train()
+    losses = []
+    for step in range(STEPS):
+        loss, _ = core.run_step({k: v.clone() for k, v in _global_batches(packed)[step].items()})
+        core.step_optimizer()
+        losses.append(float(loss.detach()))
+    core.close()
+    return losses
+
+
+CHUNK = 10   # cases per group of worker processes: a case that fails takes only its own chunk down
+
+
+@pytest.fixture(scope="module")
+def matrix_results():
+    names = sorted(CASES)
+    merged = [dict() for _ in range(WORLD)]
+    for i in range(0, len(names), CHUNK):
+        chunk = names[i:i + CHUNK]
+        try:
+            part = run_distributed(_worker, WORLD, chunk, timeout=420.0)
+        except BaseException as exc:  # noqa: BLE001 - reported per case below
+            part = [{n: ("error", f"worker group failed: {type(exc).__name__}: {str(exc)[:1500]}", 1) for n in chunk} for _ in range(WORLD)]
+        for r in range(WORLD):
+            merged[r].update(part[r])
+    return merged
+
+
+@pytest.fixture(scope="module")
+def baselines():
+    return {(m, p): _baseline(m, p) for m in MODELS for p in (False, True) if any(c["model"] == m and c["packed"] == p for c in CASES.values())}
+
+
+def test_case_list_is_wide_enough():
+    assert len(CASES) >= 40
+    flags = " ".join(" ".join(c["flags"]) for c in CASES.values())
+    for needle in ("--zero-stage 1", "--zero-stage 2", "--zero-stage 3", "--pp-schedule 1f1b", "--pp-schedule afab", "--cp-attn-core ring",
+                   "--cp-attn-core all_gather_kv", "--ep-size 8", "--ep-size 4", "--ep-size 2", "--use-sp", "--activation-checkpointing",
+                   "--ddp-mode bucket"):
+        assert needle in flags, needle
+    assert {c["model"] for c in CASES.values()} == set(MODELS) and any(c["packed"] for c in CASES.values())
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_case_matches_single_process_training(name, matrix_results, baselines):
+    case = CASES[name]
+    per_rank = [r[name] for r in matrix_results]
+    for status, payload, _ in per_rank:
+        assert status == "ok", payload
+    cp = per_rank[0][2]
+    ref = baselines[(case["model"], case["packed"])]
+    for step in range(STEPS):
+        # CP ranks report their share of the loss (shares add up), every other axis reports the value of its data shard
+        got = sum(r[1][step] for r in per_rank) / (WORLD / cp)
+        tol = 2e-4 if step == 0 else 2e-3
+        assert abs(got - ref[step]) < tol, (name, step, got, ref[step])
+
+
+# ------------------------------------------------------------------------------------------------ resume
+def _resume_worker(rank, world, names, root):
+    import os
+
+    import torch.distributed as dist
+
+    from maltos_b200.runtime.mesh import MeshAxis
+    from maltos_b200.state import save_sharded_checkpoint
+
+    results = {}
+    for name in names:
+        case, stop_after = CASES[name], RESUME[name]
+        try:
+            total_micro = (STEPS + 1) * case["accum"]
+
+            def run(core, a, first, last, dp_rank):
+                out = []
+                for i in range(first, last):
+                    step, m = divmod(i, case["accum"])
+                    loss, should = core.run_step(_micro_batch(_global_batches(case["packed"])[step], dp_rank, a.dp_size, case["accum"], m))
+                    out.append(float(loss.detach()))
+                    if should:
+                        core.step_optimizer()
+                return out
+
+            def fresh():
+                a, core = _build(case)
+                return a, core
+
+            a, core = fresh()
+            core.setup()
+            core.model.train()
+            dp_group = core.get_group(MeshAxis.DP)
+            dp_rank = dist.get_rank(dp_group) if dp_group is not None else 0
+            continuous = run(core, a, 0, total_micro, dp_rank)
+            core.close()
+
+            a, core = fresh()
+            core.setup()
+            core.model.train()
+            head = run(core, a, 0, stop_after, dp_rank)
+            ckpt = os.path.join(root, name, "step_00000001")
+            save_sharded_checkpoint(core.state_manager, ckpt)
+            core.close()
+
+            a, core = fresh()
+            core.setup(checkpoint_path=ckpt)
+            core.model.train()
+            tail = run(core, a, stop_after, total_micro, dp_rank)
+            core.close()
+            results[name] = ("ok", continuous, head + tail)
+        except Exception as exc:  # noqa: BLE001
+            import traceback
+
+            results[name] = ("error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()[-1500:]}", None)
+            try:
+                dist.barrier()
+            except Exception:
+                pass
+    return results
+
+
+@pytest.fixture(scope="module")
+def resume_results(tmp_path_factory):
+    root = tmp_path_factory.mktemp("matrix_resume")
+    names = sorted(RESUME)
+    merged = [dict() for _ in range(WORLD)]
+    for i in range(0, len(names), 4):
+        chunk = names[i:i + 4]
+        try:
+            part = run_distributed(_resume_worker, WORLD, chunk, str(root), timeout=420.0)
+        except BaseException as exc:  # noqa: BLE001
+            part = [{n: ("error", f"worker group failed: {type(exc).__name__}: {str(exc)[:1500]}", None) for n in chunk} for _ in range(WORLD)]
+        for r in range(WORLD):
+            merged[r].update(part[r])
+    return merged
+
+
+@pytest.mark.parametrize("name", sorted(RESUME))
+def test_resume_equals_uninterrupted_training(name, resume_results):
+    """Checkpoint at a step boundary or in the middle of an accumulation window, rebuild, load, continue."""
+    mid = RESUME[name] % CASES[name]["accum"] != 0
+    for rank, res in enumerate(resume_results):
+        status, continuous, resumed = res[name]
+        assert status == "ok", continuous
+        assert len(continuous) == len(resumed)
+        worst = max(abs(x - y) for x, y in zip(continuous, resumed))
+        assert worst < (5e-5 if not mid else 2e-4), (name, rank, mid, continuous, resumed)

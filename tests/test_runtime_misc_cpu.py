@@ -188,3 +188,17 @@ def test_zero3_prefetches_in_observed_order_and_releases_everything():
         assert total0 == total1 == 2 * n_buckets
         assert ahead0 >= n_buckets // 2            # backward of the first pass
         assert ahead1 >= 2 * n_buckets - 6         # both directions of the second pass
+
+
+def test_exposed_communication_is_comm_time_not_covered_by_compute():
+    from maltos_b200.utils.profiling import exposed_comm_us, is_comm_kernel
+
+    assert is_comm_kernel("ncclDevKernel_ReduceScatter_Sum_bf16_RING_LL(...)") and is_comm_kernel("void mb::pull_all_gather_kernel<8>(...)")
+    assert not is_comm_kernel("void mb::gemm_bf16_pair_kernel<true>(...)")
+    kernels = [("gemm", 0, 100), ("nccl_ag", 50, 100),          # 50..150: 50 us hidden, 50 us exposed
+               ("gemm", 200, 50), ("pull_reduce_scatter", 210, 20),   # fully hidden
+               ("nccl_ar", 300, 40), ("nccl_ar2", 320, 40),     # overlapping comm kernels, nothing else: 60 us exposed
+               ("flash", 355, 100)]                             # covers the last 5 us of the comm union
+    exposed, total, busy = exposed_comm_us(kernels)
+    assert total == 100 + 20 + 60 and exposed == 50 + 0 + 55
+    assert busy == 150 + 50 + (455 - 300)
