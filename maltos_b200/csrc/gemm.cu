@@ -18,6 +18,18 @@
 #include "host.h"
 #include "ptx.cuh"
 
+// Timing probes (cycle counters per k-block, "MMAs without data" / "loads without math" modes) exist only in builds
+// with -DMB_GEMM_PROBE; in the default build the macros below fold every probe branch away at compile time.
+#ifdef MB_GEMM_PROBE
+#define MB_DEBUG_MODE(p) ((p).debug_mode)
+#define MB_TRACE(p) ((p).trace)
+#define MB_CLOCK() clock64()
+#else
+#define MB_DEBUG_MODE(p) 0
+#define MB_TRACE(p) (static_cast<long long*>(nullptr))
+#define MB_CLOCK() 0ll
+#endif
+
 namespace mb {
 
 constexpr int kBM = 128;
@@ -482,7 +494,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     constexpr bool is_a = true;
-    if (lane == 0 && p.debug_mode != 1) {
+    if (lane == 0 && MB_DEBUG_MODE(p) != 1) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -558,11 +570,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (p.debug_mode != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          if (MB_DEBUG_MODE(p) != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
-          if (p.debug_mode == 2) {   // timing probe: consume the stage without math
+          if (MB_DEBUG_MODE(p) == 2) {   // timing probe: consume the stage without math
             mbar_arrive(&empty_bar[stage]);
             if (++stage == STAGES) {
               stage = 0;
@@ -829,7 +841,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
     constexpr bool is_a = true;
-    if (lane == 0 && !*abort_flag && p.debug_mode != 1) {
+    if (lane == 0 && !*abort_flag && MB_DEBUG_MODE(p) != 1) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -863,13 +875,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           fence_proxy_async_global();
         }
         for (int kb = wu.kb0; kb < wu.kb1; ++kb) {
-          const long long t0 = clock64();
+          const long long t0 = MB_CLOCK();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
           }
-          t_empty += clock64() - t0;
-          if (is_a && p.trace && n_issued < 64) p.trace[4 * gridDim.x + blockIdx.x * 256 + n_issued] = clock64();   // stage free seen / TMA issue
+          t_empty += MB_CLOCK() - t0;
+          if (is_a && MB_TRACE(p) && n_issued < 64) MB_TRACE(p)[4 * gridDim.x + blockIdx.x * 256 + n_issued] = MB_CLOCK();   // stage free seen / TMA issue
           ++n_issued;
           const int k0 = kb * kBK;
           {
@@ -895,7 +907,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
         }
       }
-      if (is_a && p.trace) p.trace[4 * blockIdx.x + 3] = t_empty;
+      if (is_a && MB_TRACE(p)) MB_TRACE(p)[4 * blockIdx.x + 3] = t_empty;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -910,25 +922,25 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       long long t_full = 0, t_tempty = 0;
       int n_seen = 0;
-      const long long t_begin = clock64();
+      const long long t_begin = MB_CLOCK();
       for (int it = 0; ok; ++it) {
         const WorkUnit wu = work_unit(it, pair, n_pairs, total_tiles, p.k_blocks, p.tail_split);
         if (wu.tile < 0) break;
-        long long t0 = clock64();
+        long long t0 = MB_CLOCK();
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) break;
-        t_tempty += clock64() - t0;
+        t_tempty += MB_CLOCK() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairTile);
         for (int kb = wu.kb0; kb < wu.kb1; ++kb) {
-          t0 = clock64();
-          if (p.debug_mode != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          t0 = MB_CLOCK();
+          if (MB_DEBUG_MODE(p) != 1 && !mbar_wait(&full_bar[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
-          t_full += clock64() - t0;
-          if (p.trace && n_seen < 64) p.trace[4 * gridDim.x + blockIdx.x * 256 + 64 + n_seen] = clock64();      // data seen
+          t_full += MB_CLOCK() - t0;
+          if (MB_TRACE(p) && n_seen < 64) MB_TRACE(p)[4 * gridDim.x + blockIdx.x * 256 + 64 + n_seen] = MB_CLOCK();      // data seen
           ++n_seen;
-          if (p.debug_mode == 2) {   // consume the stage without math: release it in both CTAs
+          if (MB_DEBUG_MODE(p) == 2) {   // consume the stage without math: release it in both CTAs
             mbar_arrive(&empty_bar[stage]);
             mbar_arrive_cluster(mapa_u32(&empty_bar[stage], 1));
             if (++stage == n_stages) {
@@ -964,9 +976,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           acc_phase ^= 1;
         }
       }
-      if (p.trace) {
-        long long* t = p.trace + 4 * blockIdx.x;
-        t[0] = clock64() - t_begin, t[1] = t_full, t[2] = t_tempty;
+      if (MB_TRACE(p)) {
+        long long* t = MB_TRACE(p) + 4 * blockIdx.x;
+        t[0] = MB_CLOCK() - t_begin, t[1] = t_full, t[2] = t_tempty;
       }
     }
     __syncwarp();

@@ -91,7 +91,8 @@ def causal_attention(q, k, v, *, position_ids=None, sequence_ids=None, scale: fl
 # ------------------------------------------------------------------------------------------------ block primitives
 def attention_block_forward(q, k, v, *, q_positions, k_positions, q_sequence_ids=None, k_sequence_ids=None, scale=None):
     """One (query block, key block) attention WITHOUT autograd: returns ``(out, lse)`` with ``lse = -inf`` and
-    ``out = 0`` for rows that see no key. Building block of ring attention; merged with :func:`merge_attention_blocks`."""
+    ``out = 0`` for rows that see no key. Building block of ring attention; merged with :func:`merge_attention_blocks`.
+    ``q_positions=None`` means every key of the block is visible to every query (no mask is evaluated)."""
     with torch.no_grad():
         if _kernel_eligible(q, k, v):
             from .flash_attn import flash_block_forward
@@ -100,7 +101,7 @@ def attention_block_forward(q, k, v, *, q_positions, k_positions, q_sequence_ids
             if res is not None:
                 return res
         out, lse = attention_reference(q, k, v, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
-                                       k_sequence_ids=k_sequence_ids, scale=scale, return_lse=True)
+                                       k_sequence_ids=k_sequence_ids, causal=False, scale=scale, return_lse=True)
         return out, lse
 
 
@@ -115,7 +116,8 @@ def merge_attention_blocks(out_a, lse_a, out_b, lse_b):
 def attention_block_backward(q, k, v, out, lse, dout, *, q_positions, k_positions, q_sequence_ids=None, k_sequence_ids=None,
                              scale=None):
     """Gradients of one block given the GLOBAL output and log-sum-exp of the query rows (flash-attention backward
-    formulation): ``P = exp(S - lse)``, ``dS = P * (dO V^T - rowsum(dO * O))``. Returns fp32 ``(dq, dk, dv)``."""
+    formulation): ``P = exp(S - lse)``, ``dS = P * (dO V^T - rowsum(dO * O))``. Returns fp32 ``(dq, dk, dv)``.
+    ``q_positions=None``: every key is visible to every query."""
     with torch.no_grad():
         if _kernel_eligible(q, k, v):
             from .flash_attn import flash_block_backward
@@ -133,8 +135,11 @@ def attention_block_backward(q, k, v, out, lse, dout, *, q_positions, k_position
         of = out.float().permute(0, 2, 1, 3).reshape(B, hkv, g, Sq, D)
         dof = dout.float().permute(0, 2, 1, 3).reshape(B, hkv, g, Sq, D)
         scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-        mask = build_visibility_mask(q_positions, k_positions, q_sequence_ids, k_sequence_ids).view(B, 1, 1, Sq, Sk)
-        p = torch.exp(scores - lse.float().reshape(B, hkv, g, Sq, 1)).masked_fill(~mask, 0.0).nan_to_num(0.0)
+        p = torch.exp(scores - lse.float().reshape(B, hkv, g, Sq, 1))
+        if q_positions is not None:
+            mask = build_visibility_mask(q_positions, k_positions, q_sequence_ids, k_sequence_ids).view(B, 1, 1, Sq, Sk)
+            p = p.masked_fill(~mask, 0.0)
+        p = p.nan_to_num(0.0)
         dv = torch.matmul(p.transpose(-1, -2), dof).sum(2)
         dp = torch.matmul(dof, vf.transpose(-1, -2))
         delta = (dof * of).sum(-1, keepdim=True)

@@ -149,7 +149,9 @@ def flash_block_forward(q, k, v, q_positions, k_positions, q_sequence_ids, k_seq
         return None
     if (q_sequence_ids is None) != (k_sequence_ids is None):
         return None
-    return flash_forward(q, k, v, mode=2, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
+    if q_positions is None:                                     # every key visible: the unmasked kernel
+        return flash_forward(q, k, v, mode=MODE_FULL, scale=scale)
+    return flash_forward(q, k, v, mode=MODE_GENERAL, q_positions=q_positions, k_positions=k_positions, q_sequence_ids=q_sequence_ids,
                          k_sequence_ids=k_sequence_ids, scale=scale)
 
 
@@ -207,5 +209,7 @@ def flash_block_backward(q, k, v, out, lse, dout, q_positions, k_positions, q_se
         return None
     if (q_sequence_ids is None) != (k_sequence_ids is None):
         return None
+    if q_positions is None:
+        return flash_backward(q, k, v, out, lse, dout, mode=MODE_FULL, scale=scale, fp32_out=True)
     return flash_backward(q, k, v, out, lse, dout, mode=MODE_GENERAL, q_positions=q_positions, k_positions=k_positions,
                           q_sequence_ids=q_sequence_ids, k_sequence_ids=k_sequence_ids, scale=scale, fp32_out=True)

@@ -2,6 +2,7 @@
 resume == continuous training. Reference checks are skipped when ``baseline/_ref`` is not installed."""
 import json
 import os
+import shutil
 import subprocess
 import sys
 from pathlib import Path
@@ -71,6 +72,45 @@ def test_cross_load_with_reference(shards, tmp_path):
     m_ref = json.loads((tmp_path / "ref" / "step_00000002" / "manifest.json").read_text())
     assert m_ours == m_ref
     assert (tmp_path / "ours" / "runtime_spec.json").read_bytes() == (tmp_path / "ref" / "runtime_spec.json").read_bytes()
+
+
+def _launch(tree, entry, shards, ckpt, steps, extra, nproc, resume=None):
+    from tests.dist_utils import free_port
+
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), *entry, "--data", str(shards), *FLAGS, *extra, "--max-steps", str(steps), "--checkpoint-dir", str(ckpt)]
+    if resume:
+        cmd += ["--resume-from", str(resume)]
+    return _run(cmd, tree, {"PYTHONPATH": str(tree), "GLOO_SOCKET_IFNAME": "lo"})
+
+
+@pytest.mark.skipif(not (REF / "runtime" / "core.py").exists(), reason="reference not installed under baseline/_ref")
+def test_cross_load_with_reference_sharded_four_ranks(shards, tmp_path):
+    """DP2 x TP2 + SP + ZeRO-3 on 4 gloo ranks: the manifests (ZeRO-3 bucket order, TP shard shapes, optimizer source
+    ranks) are equal entry by entry, and each framework continues from the other's checkpoint with the same losses."""
+    extra = ["--dp-size", "2", "--tp-size", "2", "--use-sp", "--zero-stage", "3"]
+    ours = lambda ckpt, steps, resume=None: _launch(ROOT, ["-m", "maltos_b200.tools.train"], shards, ckpt, steps, extra, 4, resume)   # noqa: E731
+    ref = lambda ckpt, steps, resume=None: _launch(REF, ["tools/train.py"], shards, ckpt, steps, extra, 4, resume)                   # noqa: E731
+    def close(a, b):      # four ranks reduce in a different order in the two frameworks: equal to rounding, not bit for bit
+        return len(a) == len(b) and all(abs(float(x) - float(y)) <= 2e-4 for x, y in zip(a, b))
+
+    ours_first = _losses(ours(tmp_path / "ours", 2))
+    ref_first = _losses(ref(tmp_path / "ref", 2))
+    assert close(ours_first, ref_first), (ours_first, ref_first)
+    m_ours = json.loads((tmp_path / "ours" / "step_00000002" / "manifest.json").read_text())
+    m_ref = json.loads((tmp_path / "ref" / "step_00000002" / "manifest.json").read_text())
+    assert m_ours == m_ref
+    buckets = [e["state_key"] for e in m_ours["ranks"][0]["entries"] if e["state_key"].startswith("zero3_bucket_")]
+    assert buckets == [f"zero3_bucket_{i}" for i in range(len(buckets))] and len(buckets) >= 10
+    assert m_ours["optimizer_source_ranks"] == [0, 1, 2, 3]
+    # each checkpoint is continued by BOTH frameworks: from the same state they must agree (to rounding)
+    for made_by in ("ours", "ref"):
+        ckpt = tmp_path / made_by
+        other = tmp_path / f"{made_by}_copy"
+        shutil.copytree(ckpt, other)
+        a = _losses(ours(ckpt, 4, resume=ckpt / "step_00000002"))
+        b = _losses(ref(other, 4, resume=other / "step_00000002"))
+        assert len(a) == 2 and close(a, b), (made_by, a, b)
 
 
 def _tiny_runtime():
