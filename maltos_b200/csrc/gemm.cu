@@ -687,7 +687,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // bandwidth limit. Barriers: full[s] lives in the leader and counts the TMA bytes of both CTAs; empty[s] and
 // tfull[a] exist in both CTAs and are signalled by one commit addressed to both; tempty[a] lives in the leader and
 // collects the epilogue warps of both CTAs.
-static int g_debug_max_pairs = 0;   // debug cap on the number of CTA pairs (0 = all)
+#ifdef MB_GEMM_PROBE
+static int g_debug_max_pairs = 0;   // probe builds: cap on the number of CTA pairs (0 = all)
+#else
+constexpr int g_debug_max_pairs = 0;
+#endif
 static int g_push_split = [] {       // 1: the all-gather push runs as its own launch in front of the GEMM
   const char* e = getenv("MALTOS_B200_PUSH_SPLIT");
   return e ? atoi(e) : 0;
@@ -1324,48 +1328,56 @@ rs_reduce_kernel(const __nv_bfloat16* __restrict__ stage, long long slot_elems, 
   }
 }
 
-// Debug override of the descriptor geometry {lbo, sbo, kstep} per operand; negative = built-in value.
+#ifdef MB_GEMM_PROBE
+// Probe builds only: override of the descriptor geometry {lbo, sbo, kstep} per operand (negative = built-in value), cycle
+// trace buffer, math-only / load-only modes, ring depth.
 static int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
 static long long* g_trace = nullptr;
-static int g_pair_group_m = 8;
 static int g_debug_mode = 0;
+static int g_debug_stages = 0;
+#else
+constexpr int g_desc_override[6] = {-1, -1, -1, -1, -1, -1};
+constexpr long long* g_trace = nullptr;
+constexpr int g_debug_mode = 0;
+constexpr int g_debug_stages = 0;
+#endif
+static int g_pair_group_m = 8;
 static int g_quad_epilogue = [] {
   const char* e = getenv("MALTOS_B200_QUAD_EPILOGUE");
   return e ? atoi(e) : 1;
 }();
 static int g_push_bulk = 0;      // fused all-gather: 1 = push with bulk async copies, 0 = push with the copy warps
 static int g_scatter_kind = 0;   // tuning: kernel kind forced for the fused reduce-scatter GEMM (0 = cost model)
-static int g_debug_stages = 0;
 
 }  // namespace mb
 
-// Debug: device buffer of 4 int64 per CTA that the CTA-pair kernel fills with cycle counters (nullptr = off).
+#ifdef MB_GEMM_PROBE
+// Device buffer of 4 int64 per CTA that the CTA-pair kernel fills with cycle counters (nullptr = off).
 MB_API void mb_gemm_set_trace(long long* buf) { mb::g_trace = buf; }
+// Timing probes of the CTA-pair kernel (results are meaningless): 1 = math only, 2 = loads only, 0 = normal.
+MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
+MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
+// Cap the number of CTA pairs of the pair kernel (0 = one pair per two SMs).
+MB_API void mb_gemm_set_debug_max_pairs(int pairs) { mb::g_debug_max_pairs = pairs; }
+MB_API void mb_gemm_debug_descriptor(int a_lbo, int a_sbo, int a_kstep, int b_lbo, int b_sbo, int b_kstep) {
+  int v[6] = {a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
+  for (int i = 0; i < 6; ++i) mb::g_desc_override[i] = v[i];
+}
+#endif
 
 // Tuning knob of the CTA-pair kernel: M blocks per rasterisation group. (An L2 prefetch stream ahead of the
 // shared-memory ring was tried and removed: the extra L2 requests cost a third of the throughput.)
 MB_API void mb_gemm_set_tuning(int group_m) {
   if (group_m > 0) mb::g_pair_group_m = group_m;
 }
-// Timing probes of the CTA-pair kernel (results are meaningless): 1 = math only, 2 = loads only, 0 = normal.
-MB_API void mb_gemm_set_debug_mode(int mode) { mb::g_debug_mode = mode; }
 // 0 selects the row-per-thread epilogue everywhere, 1 the line-coalesced one where it applies
 // (initial value: environment variable MALTOS_B200_QUAD_EPILOGUE, default 1).
 MB_API void mb_gemm_set_quad_epilogue(int on) { mb::g_quad_epilogue = on ? 1 : 0; }
 // 0 switches the split tail of the 256x512 kernel off (initial value: MALTOS_B200_GEMM_TAIL_SPLIT, default 1).
 MB_API void mb_gemm_set_tail_split(int on) { mb::g_tail_split = on ? 1 : 0; }
-MB_API void mb_gemm_set_debug_stages(int stages) { mb::g_debug_stages = stages; }
 MB_API void mb_gemm_set_scatter_kind(int kind) { mb::g_scatter_kind = kind; }
 MB_API void mb_gemm_set_push_bulk(int on) { mb::g_push_bulk = on ? 1 : 0; }
 MB_API void mb_gemm_set_push_split(int on) { mb::g_push_split = on ? 1 : 0; }
-// Debug: cap the number of CTA pairs of the pair kernel (0 = one pair per two SMs).
-MB_API void mb_gemm_set_debug_max_pairs(int pairs) { mb::g_debug_max_pairs = pairs; }
-
-MB_API void mb_gemm_debug_descriptor(int a_lbo, int a_sbo, int a_kstep, int b_lbo, int b_sbo, int b_kstep) {
-  int v[6] = {a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
-  for (int i = 0; i < 6; ++i) mb::g_desc_override[i] = v[i];
-}
-
 // C[M,N] (+)= op(A) op(B) (+bias). Leading dimensions are in elements; bf16 operands need them (and the base
 // addresses) to be multiples of 8 elements / 16 bytes because the operands are fetched with TMA.
 // block_n: 0 = choose; 128 or 256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel (256x256 tiles);

@@ -41,6 +41,65 @@ class CommTimeoutError(DeviceStatusError):
         self.peer, self.block = peer, block
 
 
+# ------------------------------------------------------------------------------------------------ NVTX ranges
+def nvtx_enabled() -> bool:
+    """``MALTOS_B200_NVTX=1``: every launcher call of the library runs inside an NVTX range named after the C entry point
+    (``mb_gemm_bf16``, ``mb_flash_attn_bwd``, ...), so a timeline tool shows which op issued which kernels."""
+    return os.environ.get("MALTOS_B200_NVTX", "0") == "1"
+
+
+def _range_push(name: str) -> None:
+    torch.cuda.nvtx.range_push(name)
+
+
+def _range_pop() -> None:
+    torch.cuda.nvtx.range_pop()
+
+
+#: entry points that launch nothing (queries, setters): no range around them
+_NO_RANGE = ("mb_last_error", "mb_launch_count", "mb_set_", "mb_status_", "mb_flash_attn_bwd_scratch_words", "mb_symm_", "mb_gemm_set_")
+
+
+class _RangedFunction:
+    """A C entry point whose calls are bracketed by an NVTX range; ``restype`` / ``argtypes`` go to the real function."""
+
+    __slots__ = ("_fn", "_name")
+
+    def __init__(self, fn, name: str) -> None:
+        object.__setattr__(self, "_fn", fn)
+        object.__setattr__(self, "_name", name)
+
+    def __call__(self, *args):
+        _range_push(self._name)
+        try:
+            return self._fn(*args)
+        finally:
+            _range_pop()
+
+    def __getattr__(self, item):
+        return getattr(self._fn, item)
+
+    def __setattr__(self, item, value) -> None:
+        setattr(self._fn, item, value)
+
+
+class _RangedLibrary:
+    """The kernel library with NVTX ranges around its launchers (see :func:`nvtx_enabled`)."""
+
+    def __init__(self, handle) -> None:
+        self.__dict__["_handle"] = handle
+        self.__dict__["_cache"] = {}
+
+    def __getattr__(self, name: str):
+        fn = getattr(self._handle, name)
+        if not name.startswith("mb_") or name.startswith(_NO_RANGE):
+            return fn
+        wrapped = self._cache.get(name)
+        if wrapped is None:
+            wrapped = self._cache[name] = _RangedFunction(fn, name)
+        return wrapped
+
+
 def library_path() -> Path:
     return _LIB_PATH
 
@@ -76,7 +135,7 @@ def lib() -> ctypes.CDLL:
             raise KernelLibraryError(f"cannot load {_LIB_PATH}: {exc}") from exc
         handle.mb_last_error.restype = ctypes.c_char_p
         handle.mb_launch_count.restype = ctypes.c_ulonglong
-        _lib = handle
+        _lib = _RangedLibrary(handle) if nvtx_enabled() else handle
     return _lib
 
 

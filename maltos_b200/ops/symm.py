@@ -41,6 +41,20 @@ class SymmetricBuffer:
         return _tensor_from_ptr(self.local_ptr, numel, dtype, device)
 
 
+#: buffers whose every consumed byte is written by a transfer of the same call: safe to poison
+_POISONABLE = ("sp_partial", "sp_publish", "sp_scatter", "sp_gather", "ring_kv")
+
+
+def poison_wanted(name: str) -> bool:
+    """``MALTOS_B200_POISON=1`` fills the transfer buffers of the sequence-parallel collectives and of the ring exchange
+    with NaN patterns at allocation (race / stale-read detection; off by default). Signal pads, gradient slots that are
+    summed, sharded-optimizer buffers and the expert slots (whose unused rows are read and multiplied by zero) are left
+    zeroed."""
+    import os
+
+    return os.environ.get("MALTOS_B200_POISON", "0") == "1" and name in _POISONABLE
+
+
 class _CudaArrayInterface:
     def __init__(self, ptr: int, nbytes: int) -> None:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
@@ -96,6 +110,11 @@ class SymmetricContext:
             _lib.check(lib.mb_symm_open(buf, ctypes.byref(p)), "mb_symm_open")
             peers.append(int(p.value))
             opened.append(int(p.value))
+        if poison_wanted(name):
+            # debug aid: transfer buffers start as 0xFF bytes (NaN as bf16 / fp32), so a read of rows that no peer has
+            # written yet shows up as NaN in the result instead of as plausible zeros
+            _tensor_from_ptr(int(ptr.value), nbytes, torch.uint8, self.device).fill_(0xFF)
+            torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         table = torch.tensor(peers, dtype=torch.int64, device=self.device)
         sb = SymmetricBuffer(name=name, nbytes=nbytes, local_ptr=int(ptr.value), peer_ptrs=peers, table=table, opened=opened)

@@ -2,7 +2,8 @@
 
 Selects the owned positions of ``input_ids / labels / hidden_states / position_ids / sequence_ids``, makes
 ``position_ids`` explicit, and records ``position_offset`` and ``loss_weight = local_targets / global_targets``
-(reference ``parallel/context_batch.py:39-79,146-153``).
+(reference ``parallel/context_batch.py:39-79,146-153``), plus the per-row counts behind that weight, so that a pipeline
+runner can weight each of its micro-batches exactly (rows of a packed batch do not split their targets evenly).
 """
 from __future__ import annotations
 
@@ -11,8 +12,8 @@ from typing import Any
 
 import torch
 
-from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY,
-                                         POSITION_IDS_KEY, POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
+from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY,
+                                         LOSS_WEIGHT_KEY, POSITION_IDS_KEY, POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 
 from .context_token_planner import ContextTokenPlanner
 
@@ -37,13 +38,19 @@ def _take(value: Any, positions: torch.Tensor, seq_len: int) -> Any:
     return value
 
 
-def _target_fraction(full_labels: Any, local_labels: Any) -> float | None:
-    if not (torch.is_tensor(full_labels) and torch.is_tensor(local_labels)):
+def _target_counts(full_labels: Any, local_labels: Any) -> torch.Tensor | None:
+    """Host tensor ``[rows, 2]``: targets of each row owned by this rank, and in the whole row (one device read)."""
+    if not (torch.is_tensor(full_labels) and torch.is_tensor(local_labels)) or full_labels.dim() != 2 or local_labels.dim() != 2:
         return None
-    total = int((full_labels != IGNORE_INDEX).sum())
-    if total == 0:
+    return torch.stack([(local_labels != IGNORE_INDEX).sum(1), (full_labels != IGNORE_INDEX).sum(1)], dim=1).to("cpu", torch.float64)
+
+
+def target_fraction(counts: torch.Tensor | None) -> float | None:
+    """``local targets / global targets`` over the rows of ``counts``; None when there is no target at all."""
+    if counts is None:
         return None
-    return int((local_labels != IGNORE_INDEX).sum()) / total
+    local, total = counts.sum(0).tolist()
+    return local / total if total else None
 
 
 @dataclass(frozen=True)
@@ -92,7 +99,10 @@ class ContextParallelBatchSharder:
             pos_ids = mine.clone()
         out[POSITION_IDS_KEY] = pos_ids
         out[POSITION_OFFSET_KEY] = int(mine[0])
-        out[LOSS_WEIGHT_KEY] = _target_fraction(full_labels, out.get(LABELS_KEY))
+        counts = _target_counts(full_labels, out.get(LABELS_KEY))
+        out[LOSS_WEIGHT_KEY] = target_fraction(counts)
+        if counts is not None:
+            out[LOSS_TARGET_COUNTS_KEY] = counts
         if not isinstance(batch, dict):
             out = {k: out[k] for k in (INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY)}
         return out

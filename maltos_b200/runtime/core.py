@@ -21,7 +21,7 @@ import torch.nn as nn
 from maltos_b200.parallel.plan import ParallelPlan
 from maltos_b200.parallel.protocols import FlopsEstimatableModule
 from maltos_b200.state.state import ModelStateMeta, StateManager
-from maltos_b200.utils.constants import INPUT_IDS_KEY
+from maltos_b200.utils.constants import INPUT_IDS_KEY, LOSS_TARGET_COUNTS_KEY
 from maltos_b200.utils.profiling import profiled, span
 
 from .mesh import MeshAxis, MeshConfig, ProcessGroupManager
@@ -452,8 +452,8 @@ def _device_of(module: nn.Module) -> torch.device:
 def _to_device(value: Any, device: torch.device) -> Any:
     if torch.is_tensor(value):
         return value.to(device, non_blocking=True)
-    if isinstance(value, dict):
-        return {k: _to_device(v, device) for k, v in value.items()}
+    if isinstance(value, dict):     # host-side bookkeeping (per-row target counts) stays on the host
+        return {k: (v if k == LOSS_TARGET_COUNTS_KEY else _to_device(v, device)) for k, v in value.items()}
     if isinstance(value, tuple):
         return tuple(_to_device(v, device) for v in value)
     if isinstance(value, list):

@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from maltos_b200.runtime.buffer_allocator import BufferPolicy, acquire_buffer
 from maltos_b200.runtime.types import LossOutput, PipelineOutput, PpStatus
-from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
+from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
                                          POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 from maltos_b200.utils.distributed import all_reduce_tensor, irecv_tensor_async, isend_tensor_async
 from maltos_b200.utils.profiling import span
@@ -286,7 +286,14 @@ def split_batch(batch, num_microbatches: int) -> list:
     if n % num_microbatches:
         raise ValueError(f"pipeline microbatch split requires batch size divisible by microbatches, got batch_size={n}, microbatches={num_microbatches}")
     per = n // num_microbatches
-    return [slice_batch(batch, i * per, per) for i in range(num_microbatches)]
+    pieces = [slice_batch(batch, i * per, per) for i in range(num_microbatches)]
+    if isinstance(batch, dict) and torch.is_tensor(batch.get(LOSS_TARGET_COUNTS_KEY)):
+        # context-parallel loss weight of each piece from ITS rows (the batch-wide fraction is only right on average)
+        from maltos_b200.parallel.context_batch import target_fraction
+
+        for piece in pieces:
+            piece[LOSS_WEIGHT_KEY] = target_fraction(piece[LOSS_TARGET_COUNTS_KEY])
+    return pieces
 
 
 def unpack_batch(batch):

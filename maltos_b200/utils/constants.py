@@ -11,6 +11,9 @@ POSITION_IDS_KEY = "position_ids"
 SEQUENCE_IDS_KEY = "sequence_ids"
 POSITION_OFFSET_KEY = "position_offset"
 LOSS_WEIGHT_KEY = "loss_weight"
+#: per-row ``[rows, 2]`` (local targets, targets over the whole context-parallel group) behind ``loss_weight``: lets a
+#: pipeline runner that cuts the batch into micro-batches give every piece its own exact weight
+LOSS_TARGET_COUNTS_KEY = "loss_target_counts"
 HIDDEN_STATES_KEY = "hidden_states"
 
 MODEL_BATCH_KEYS = (

@@ -88,6 +88,14 @@ CASES = {
     "olmo_dp2_pp2_tp2_1f1b": C("olmo", "--dp-size 2 --pp-size 2 --tp-size 2 --pp-schedule 1f1b", pp_mb=2),
     "olmo_packed_dp2_cp2_tp2_ring": C("olmo", "--dp-size 2 --cp-size 2 --tp-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag", packed=True),
     "olmo_dp8_zero1": C("olmo", "--dp-size 8 --zero-stage 1"),
+    # the 13B packed recipe at toy size: TP2 x CP2 (zigzag ring) x PP2, 1F1B with 8 micro-batches, SP, activation checkpointing
+    "olmo_packed_pp2_cp2_tp2_sp_ring_1f1b_ckpt": C("olmo", "--pp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core ring --cp-token-planner fixed_zigzag "
+                                                           "--pp-schedule 1f1b --activation-checkpointing", packed=True, pp_mb=8),
+    # packed rows do not split their targets evenly over context-parallel ranks: every pipeline micro-batch needs its own loss weight
+    "olmo_packed_dp2_cp2_tp2_sp_ring": C("olmo", "--dp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core ring --cp-token-planner fixed_zigzag", packed=True),
+    "olmo_packed_dp2_pp2_cp2_ring_1f1b": C("olmo", "--dp-size 2 --pp-size 2 --cp-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --pp-schedule 1f1b", packed=True, pp_mb=4),
+    "packed_pp2_cp2_tp2_sp_ring_1f1b": C("llama", "--pp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core ring --cp-token-planner fixed_zigzag --pp-schedule 1f1b", packed=True, pp_mb=8),
+    "packed_dp2_cp2_tp2_sp_allgather": C("llama", "--dp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core all_gather_kv", packed=True),
     # ---- expert parallel (expert groups of 8, 4 and 2 ranks inside the data-parallel axis)
     "moe_dp8_ep8": C("moe", "--dp-size 8 --ep-size 8"),
     "moe_dp8_ep4_zero2": C("moe", "--dp-size 8 --ep-size 4 --zero-stage 2"),

@@ -202,3 +202,53 @@ def test_exposed_communication_is_comm_time_not_covered_by_compute():
     exposed, total, busy = exposed_comm_us(kernels)
     assert total == 100 + 20 + 60 and exposed == 50 + 0 + 55
     assert busy == 150 + 50 + (455 - 300)
+
+
+def test_nvtx_ranged_library_brackets_launchers_only(monkeypatch):
+    """With ``MALTOS_B200_NVTX=1`` every launcher call runs inside a range named after its C entry point; queries and
+    setters do not; ``restype`` assignments reach the real function."""
+    from maltos_b200.ops import _lib
+
+    events = []
+
+    class Fn:
+        def __init__(self, name):
+            self.name, self.restype = name, None
+
+        def __call__(self, *args):
+            events.append(("call", self.name, args))
+            return 0
+
+    class Handle:
+        def __init__(self):
+            self.fns = {}
+
+        def __getattr__(self, name):
+            return self.fns.setdefault(name, Fn(name))
+
+    monkeypatch.setattr(_lib, "_range_push", lambda name: events.append(("push", name)))
+    monkeypatch.setattr(_lib, "_range_pop", lambda: events.append(("pop",)))
+    handle = Handle()
+    ranged = _lib._RangedLibrary(handle)
+    assert ranged.mb_gemm_bf16(1, 2) == 0
+    assert events == [("push", "mb_gemm_bf16"), ("call", "mb_gemm_bf16", (1, 2)), ("pop",)]
+    events.clear()
+    ranged.mb_launch_count()
+    ranged.mb_set_wait_timeout_ms(5)
+    ranged.mb_status_fetch_and_clear(None, None)
+    assert [e[0] for e in events] == ["call", "call", "call"]
+    ranged.mb_flash_attn_bwd.restype = "marker"
+    assert handle.fns["mb_flash_attn_bwd"].restype == "marker"
+    monkeypatch.setenv("MALTOS_B200_NVTX", "1")
+    assert _lib.nvtx_enabled()
+
+
+def test_poison_fill_is_opt_in_and_limited_to_transfer_buffers(monkeypatch):
+    from maltos_b200.ops import symm
+
+    monkeypatch.delenv("MALTOS_B200_POISON", raising=False)
+    assert not symm.poison_wanted("sp_partial")
+    monkeypatch.setenv("MALTOS_B200_POISON", "1")
+    assert symm.poison_wanted("sp_partial") and symm.poison_wanted("ring_kv")
+    for name in ("signal_pad", "ring_dkv", "moe_dispatch_0", "zero3.shard.0", "ddp.grad"):
+        assert not symm.poison_wanted(name)
