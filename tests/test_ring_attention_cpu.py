@@ -106,3 +106,47 @@ def test_block_primitives_without_positions_see_every_key():
     dq, dk, dv = attention_block_backward(q.detach(), k.detach(), v.detach(), out, lse, w, q_positions=None, k_positions=None)
     for a, b in ((dq, q.grad), (dk, k.grad), (dv, v.grad)):
         assert torch.allclose(a, b, atol=1e-5)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_zigzag_schedule_call_sequence_for_every_rank_in_one_process(world, monkeypatch):
+    """The schedule of every rank, without process groups: which (query rows, key rows, masked?) block calls a rank makes
+    for the blocks of all owners (the reference checks its flash ring the same way with fake groups,
+    ``tests/sequence_ids_attention_mask.py:189-365``), and that merging those calls reproduces whole-sequence attention."""
+    from maltos_b200.ops import attention as A
+    from maltos_b200.runtime.layers import ring_attention as ra
+    from maltos_b200.runtime.layers.ring_layout import zigzag_positions
+
+    B, S, hq, hkv, D = 1, 16, 2, 1, 8
+    g = torch.Generator().manual_seed(9)
+    q_all, k_all, v_all = (torch.randn(B, S * world, h, D, generator=g) for h in (hq, hkv, hkv))
+    pos_all = torch.arange(S * world).unsqueeze(0)
+    ref = A.attention_reference(q_all, k_all, v_all, q_positions=pos_all, k_positions=pos_all)
+    idx = [zigzag_positions(S * world, r, world) for r in range(world)]
+    calls = []
+    real = ra.attention_block_forward
+
+    def recording(q, k, v, *, q_positions, k_positions, **kw):
+        calls.append((q.shape[1], k.shape[1], q_positions is not None))
+        return real(q, k, v, q_positions=q_positions, k_positions=k_positions, **kw)
+
+    monkeypatch.setattr(ra, "attention_block_forward", recording)
+    plan = ra.RingPlan(True, (True,) * world)
+    for me in range(world):
+        calls.clear()
+        q = q_all[:, idx[me]]
+        out = torch.zeros(B, S, hq, D)
+        lse = torch.full((B, hq, S), float("-inf"))
+        for step in range(world):
+            owner = (me - step) % world
+            blk = [k_all[:, idx[owner]], v_all[:, idx[owner]], pos_all[:, idx[owner]], torch.zeros_like(pos_all[:, idx[owner]])]
+            out, lse = ra._block_forward(plan, me, owner, q, blk, pos_all[:, idx[me]], None, None, out, lse)
+        want = []
+        for step in range(world):
+            owner = (me - step) % world
+            want.append((S, S, True) if owner == me else ((S, S // 2, False) if owner < me else (S // 2, S, False)))
+        assert calls == want, (me, calls, want)
+        assert (out - ref[:, idx[me]]).abs().max() < 1e-5
+    # the unmasked half blocks do half the score work of a masked full block
+    full, half = S * S, S * (S // 2)
+    assert half * 2 == full
