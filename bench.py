@@ -32,6 +32,9 @@ MODEL = dict(layers=32, hidden=4096, heads=32, kv_heads=8, ffn=14336, vocab=1282
              rope_theta=500000.0)
 SMALL = dict(layers=2, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=1024, seq_len=256, eps=1e-5, rope_theta=500000.0)
 GLOBAL_BATCH = 32
+#: the end-to-end region (pinned host batches in, loss out, every step) runs min(K, this) steps: the device-timed region
+#: is the one that runs EXACTLY K steps; both arms use the same cap
+E2E_MAX_STEPS = 8
 
 
 # Other configurations of the baseline's list: (recipe both frameworks ship, training-flag overrides, GPUs, synthetic layout).
@@ -409,15 +412,16 @@ def run_ours(args) -> None:
     e2e = None
     if not args.no_e2e:
         barrier_sync(device)
+        e2e_steps = min(args.steps, E2E_MAX_STEPS)
         t0 = time.perf_counter()
         last_loss = None
-        for _ in range(args.steps):
+        for _ in range(e2e_steps):
             last_loss = one_step(host, read_loss=True)   # pinned host -> device every micro-step, loss -> host every step
         if use_cuda:
             torch.cuda.synchronize(device)
-        e2e_s = max_over_ranks(time.perf_counter() - t0, device) / args.steps
+        e2e_s = max_over_ranks(time.perf_counter() - t0, device) / e2e_steps
         e2e = {"value": tokens_per_step / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": host.bytes_per_batch * accum,
-               "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "loss": last_loss}
+               "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "loss": last_loss}
 
     exposed = None
     if (args.exposed_comm if args.exposed_comm is not None else world > 1) and use_cuda:
@@ -545,14 +549,15 @@ def run_reference(args) -> None:
         e2e = None
         if not args.no_e2e:
             barrier_sync(device)
+            e2e_steps = min(args.steps, E2E_MAX_STEPS)
             t0 = time.perf_counter()
-            for _ in range(args.steps):
+            for _ in range(e2e_steps):
                 last = one_step(host, True)
             if use_cuda:
                 torch.cuda.synchronize(device)
-            e2e_s = max_over_ranks(time.perf_counter() - t0, device) / args.steps
+            e2e_s = max_over_ranks(time.perf_counter() - t0, device) / e2e_steps
             e2e = {"value": tokens_per_step / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": host.bytes_per_batch * accum,
-                   "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "loss": last}
+                   "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "loss": last}
         exposed = None
         if (args.exposed_comm if args.exposed_comm is not None else world > 1) and use_cuda:
             exposed = measure_exposed_comm(lambda: one_step(dev_batches, False), device)
