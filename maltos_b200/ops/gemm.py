@@ -74,6 +74,14 @@ def gemm(
         out.copy_(res.to(out.dtype))
         return out
 
+    if M == 0 or N == 0:
+        return out                      # nothing to compute (an expert without tokens, an empty shard)
+    if K == 0:                          # empty contraction: the product is zero
+        if not accumulate:
+            out.zero_()
+            if bias is not None:
+                out += bias.to(out.dtype)
+        return out
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError(f"gemm kernel takes bf16 operands, got {a.dtype} / {b.dtype}")
     if out.dtype not in (torch.bfloat16, torch.float32):

@@ -55,6 +55,11 @@ def _moe_experts_forward_static(flat, expert_idx, gate, keep, weights, capacity:
     return torch.zeros_like(flat).index_add(0, tokens_sorted, gated)
 
 
+def _has_module_hooks(expert) -> bool:
+    mods = expert.modules() if isinstance(expert, torch.nn.Module) else ()
+    return any(m._forward_pre_hooks or m._forward_hooks or m._backward_hooks or m._backward_pre_hooks for m in mods)
+
+
 def moe_experts_forward(flat: torch.Tensor, expert_idx: torch.Tensor, gate: torch.Tensor, keep: torch.Tensor | None,
                         experts: list, capacity: int | None = None) -> torch.Tensor:
     """``flat [N,H]``, ``expert_idx/gate [N,k]``, ``keep [N,k]`` bool or None, ``experts``: callables ``[n,H]->[n,H]``.
@@ -81,8 +86,10 @@ def moe_experts_forward(flat: torch.Tensor, expert_idx: torch.Tensor, gate: torc
     at = 0
     pieces = []
     for e, n in enumerate(counts):
-        # every expert is entered, also with zero rows: under sharded parameters (ZeRO-3) each call gathers the
-        # expert's weights collectively, so all ranks must make the same sequence of calls
+        # an expert with module hooks is entered also with zero rows: under sharded parameters (ZeRO-3) each call gathers
+        # the expert's weights collectively, so all ranks must make the same sequence of calls
+        if n == 0 and not _has_module_hooks(experts[e]):
+            continue
         pieces.append(experts[e](gathered[at:at + n]) * gates_sorted[at:at + n])
         at += n
     if pieces:

@@ -252,3 +252,46 @@ def test_poison_fill_is_opt_in_and_limited_to_transfer_buffers(monkeypatch):
     assert symm.poison_wanted("sp_partial") and symm.poison_wanted("ring_kv")
     for name in ("signal_pad", "ring_dkv", "moe_dispatch_0", "zero3.shard.0", "ddp.grad"):
         assert not symm.poison_wanted(name)
+
+
+def test_gemm_wrapper_handles_empty_problems_without_a_launch(monkeypatch):
+    """An expert without tokens reaches the GEMM wrapper with zero rows (forward, dgrad) or an empty contraction (wgrad):
+    the kernel library rejects empty problems, so the wrapper must answer them itself."""
+    from maltos_b200.ops import _lib, gemm as G
+
+    monkeypatch.setattr(_lib, "use_kernels", lambda *t: True)
+    monkeypatch.setattr(_lib, "lib", lambda: (_ for _ in ()).throw(AssertionError("no launch expected")))
+    w = torch.randn(6, 8).bfloat16()
+    y = G.gemm(torch.zeros(0, 8).bfloat16(), w)
+    assert y.shape == (0, 6)
+    dw = G.gemm(torch.zeros(0, 6).bfloat16(), torch.zeros(0, 8).bfloat16(), a_mn=True, b_mn=True)
+    assert dw.shape == (6, 8) and float(dw.abs().sum()) == 0.0
+    acc = torch.ones(6, 8)
+    G.gemm(torch.zeros(0, 6).bfloat16(), torch.zeros(0, 8).bfloat16(), a_mn=True, b_mn=True, out=acc, accumulate=True)
+    assert float(acc.sum()) == 48.0
+
+
+def test_experts_without_tokens_are_entered_only_when_hooks_need_it():
+    from maltos_b200.ops.moe import moe_experts_forward
+
+    calls = []
+
+    class E(torch.nn.Module):
+        def __init__(self, i):
+            super().__init__()
+            self.i, self.lin = i, torch.nn.Linear(4, 4)
+
+        def forward(self, x):
+            calls.append((self.i, x.shape[0]))
+            return self.lin(x)
+
+    experts = [E(i) for i in range(3)]
+    flat = torch.randn(5, 4)
+    idx = torch.zeros(5, 1, dtype=torch.long)             # every token to expert 0
+    gate = torch.ones(5, 1)
+    moe_experts_forward(flat, idx, gate, None, experts)
+    assert calls == [(0, 5)]
+    calls.clear()
+    experts[2].lin.register_forward_pre_hook(lambda m, a: None)      # what a parameter-sharding plugin installs
+    moe_experts_forward(flat, idx, gate, None, experts)
+    assert calls == [(0, 5), (2, 0)]
