@@ -78,3 +78,32 @@ def test_bench_micro_batch_defaults():
     assert not bench.parse_args(["--micro-batch", "2"]).micro_batch_auto
     assert bench.parse_args(["--small"]).micro_batch == 1
     assert bench.parse_args(["--micro-batch", "4"]).micro_batch == 4
+
+
+def test_data_presets_build_the_tool_arguments_from_the_environment(capsys):
+    from maltos_b200.tools import data_presets as dp
+
+    argv = dp.pretrain_argv({})
+    assert argv[argv.index("--config") + 1] == "sample-10BT" and "--streaming" in argv
+    argv = dp.pretrain_argv({"DATASET": "my/data", "DATASET_CONFIG": "", "MAX_TOKENS": "1000"})
+    assert "--config" not in argv and argv[argv.index("--dataset") + 1] == "my/data" and argv[argv.index("--max-tokens") + 1] == "1000"
+    olmo = dp.sft_argv("olmo2_13b_sft", {})
+    assert olmo[olmo.index("--seed") + 1] == "8" and "--assistant-only-loss" in olmo and "--chat-template-file" in olmo
+    custom = dp.sft_argv("custom", {"TOKENIZER": "tok", "DATASET": "ds", "APPEND_EOS": "false", "STREAMING": "true", "MAX_EXAMPLES": "5"})
+    assert "--no-append-eos" in custom and "--streaming" in custom and custom[custom.index("--max-examples") + 1] == "5"
+    assert "--chat-template-file" not in custom
+    import pytest
+
+    with pytest.raises(SystemExit, match="TOKENIZER must be set"):
+        dp.sft_argv("custom", {})
+    with pytest.raises(SystemExit, match="unknown PRESET"):
+        dp.sft_argv("nope", {})
+    dp.main(["pretrain", "--print"])
+    assert capsys.readouterr().out.startswith("prepare_token_shards --dataset")
+    # the tools accept what the presets produce
+    from maltos_b200.tools import prepare_sft_shards, prepare_token_shards
+
+    ns = prepare_token_shards.parse_args(dp.pretrain_argv({}))
+    assert ns.max_tokens == 500000000 and ns.streaming
+    ns = prepare_sft_shards.parse_args(olmo)
+    assert ns.seq_len == 4096 and ns.assistant_only_loss
