@@ -234,3 +234,58 @@ def test_module_without_parameters_is_rejected_by_the_optimizer_factory_path():
     rt = RuntimeCore(model=Empty(), optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.1))
     with pytest.raises((ValueError, RuntimeError)):
         rt.setup()
+
+
+def test_plugin_bind_validation_with_stand_in_runtimes():
+    """``bind`` rejects impossible configurations before any process group exists (stand-in runtimes, as the reference's
+    ``tests/hdp_plugin_contract.py:215-241`` does)."""
+    from types import SimpleNamespace
+
+    from maltos_b200.parallel.hdp_helper import ByteScaleHdpBalancedConfig
+    from maltos_b200.runtime.mesh import MeshConfig
+    from maltos_b200.runtime.plugins.cp import ContextParallelPlugin
+    from maltos_b200.runtime.plugins.hdp import ByteScaleHdpPlugin
+
+    def runtime(mesh, plugins=()):
+        return SimpleNamespace(mesh=mesh, plugins=list(plugins), has_plugin=lambda pid: any(p.id == pid for p in plugins))
+
+    hdp = ByteScaleHdpPlugin(config=ByteScaleHdpBalancedConfig(partition_tokens=64))
+    with pytest.raises(ValueError, match="DCP world size > 1"):
+        hdp.bind(runtime(MeshConfig()))
+    with pytest.raises(ValueError, match="cp_size=1"):
+        hdp.bind(runtime(MeshConfig(dp=2, cp=2)))
+    with pytest.raises(ValueError, match="pp_size=1"):
+        hdp.bind(runtime(MeshConfig(dp=2, pp=2)))
+    cp = ContextParallelPlugin()
+    with pytest.raises(ValueError, match="mutually exclusive"):
+        hdp.bind(runtime(MeshConfig(dp=2), [cp, hdp]))
+    hdp.bind(runtime(MeshConfig(dp=2), [hdp]))                                     # the valid one
+    with pytest.raises(ValueError, match="mesh.cp > 1"):
+        cp.bind(runtime(MeshConfig(dp=2), [cp]))
+    with pytest.raises(ValueError, match="mutually exclusive"):
+        cp.bind(runtime(MeshConfig(cp=2), [cp, hdp]))
+
+
+def test_context_parallel_local_loading_equals_runtime_sharding(tmp_path):
+    """A loader that shards for its context-parallel rank hands out exactly what the plugin would cut from the whole batch."""
+    import numpy as np
+
+    from maltos_b200.data import PretrainingDataLoader, TokenShardDataset
+    from maltos_b200.parallel import ContextParallelBatchSharder, ContextTokenPlannerType, build_context_token_planner
+
+    np.random.default_rng(0).integers(0, 1000, size=4000, dtype=np.uint32).tofile(tmp_path / "tokens_00000.bin")
+    for kind in (ContextTokenPlannerType.FIXED_ZIGZAG, ContextTokenPlannerType.FIXED_CONTIGUOUS):
+        sharder = ContextParallelBatchSharder(build_context_token_planner(kind), 4)
+        make = lambda **kw: PretrainingDataLoader(TokenShardDataset([tmp_path / "tokens_00000.bin"]), seq_len=32, micro_batch_size=2, **kw)  # noqa: E731
+        whole = make().next_batch()
+        for cp_rank in range(4):
+            local = make(cp_batch_sharder=sharder).next_batch(cp_rank)
+            cut = sharder.shard(whole, rank=cp_rank)
+            for key in ("input_ids", "labels", "position_ids"):
+                assert torch.equal(local[key], cut[key]), (kind, cp_rank, key)
+            assert local["loss_weight"] == cut["loss_weight"] and local["position_offset"] == cut["position_offset"]
+        # the four shares cover every token once
+        covered = torch.cat([sharder.shard(whole, rank=r)["position_ids"][0] for r in range(4)]).sort().values
+        assert torch.equal(covered, torch.arange(32))
+    with pytest.raises(RuntimeError, match="cp_batch_sharder"):
+        make().next_batch(1)
