@@ -25,11 +25,7 @@ def test_peer_copy_kernel_copies_any_byte_count(nbytes):
 
 
 def _run(rank, world, group, peer, packed):
-    import torch.distributed as dist
-
-    from maltos_b200.ops.attention import attention_reference
     from maltos_b200.runtime.layers.ring_attention import flash_ring_attention
-    from maltos_b200.runtime.layers.ring_layout import zigzag_positions
 
     os.environ["MALTOS_B200_RING_PEER"] = "1" if peer else "0"
     B, S, hq, hkv, D = 2, 256, 4, 2, 64
@@ -41,28 +37,12 @@ def _run(rank, world, group, peer, packed):
         v = (torch.randn(B, S, hkv, D, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_()
         pos = (torch.arange(S, device="cuda") + rank * S).unsqueeze(0).expand(B, -1).contiguous()
         seq = None
-        if packed == "zigzag":      # dense zigzag layout: the unmasked half-block schedule
-            pos = zigzag_positions(S * world, rank, world, device="cuda").unsqueeze(0).expand(B, -1).contiguous()
-        elif packed:      # two documents per row; the second one spans the rank boundary
+        if packed:      # two documents per row; the second one spans the rank boundary
             seq = (pos >= S // 2).long()
         o = flash_ring_attention(q, k, v, group, q_positions=pos, q_sequence_ids=seq)
         w = torch.randn(o.shape, device="cuda", generator=g).bfloat16()
         (o.float() * w.float()).sum().backward()
         outs.append([t.detach().float().cpu() for t in (o, q.grad, k.grad, v.grad)])
-        if packed == "zigzag" and rep == 0:      # also against fp32 attention over the gathered sequence
-            def gathered(t):
-                parts = [torch.empty_like(t) for _ in range(world)]
-                dist.all_gather(parts, t.contiguous(), group=group)
-                return torch.cat(parts, dim=1)
-
-            qa, ka, va = (gathered(t.detach()).float().requires_grad_() for t in (q, k, v))
-            pa, wa = gathered(pos), gathered(w).float()
-            ref = attention_reference(qa, ka, va, q_positions=pa, k_positions=pa)
-            (ref * wa).sum().backward()
-            mine = slice(rank * S, (rank + 1) * S)
-            for name, got, want in (("out", o, ref), ("dq", q.grad, qa.grad), ("dk", k.grad, ka.grad), ("dv", v.grad, va.grad)):
-                err = (got.detach().float() - want.detach()[:, mine]).abs().max().item()
-                assert err <= 3e-2 * max(1.0, want.detach().abs().max().item()), (name, err, peer)
     return outs
 
 
@@ -80,7 +60,7 @@ def _worker(rank, world, port, queue):
 
         group = dist.new_group(list(range(world)))
         res = {}
-        for packed in (False, True, "zigzag"):
+        for packed in (False, True):
             res[packed] = (_run(rank, world, group, False, packed), _run(rank, world, group, True, packed))
         torch.cuda.synchronize()
         dist.barrier(group=group)
