@@ -32,7 +32,7 @@ from maltos_b200.utils.constants import IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY,
 
 DEFAULT_CASE_FILE = Path("configs/profile_train_perf_cases.yaml")
 _SYNTHETIC_KEYS = ("packed", "packed_sequences", "segment_count_min", "segment_count_max", "supervised_fraction_min",
-                   "supervised_fraction_max", "max_padding_fraction", "delivery", "data_source")
+                   "supervised_fraction_max", "max_padding_fraction", "delivery", "data_source", "document_length_trace")
 
 
 @dataclass(frozen=True)
@@ -45,6 +45,7 @@ class CaseDefinition:
     synthetic: dict[str, Any] | None = None
     warmup: int | None = None
     steps: int | None = None
+    require_calibrated_hdp_cost: bool = False       # refuse the uncalibrated 1 / 0 / 0 cost proxy (measurement cases)
 
 
 @dataclass(frozen=True)
@@ -58,8 +59,14 @@ class SyntheticBatchConfig:
     supervised_fraction_max: float = 1.0
     max_padding_fraction: float = 0.0       # tail padding of a packed row, uniform in [0, max]
     delivery: str = "host"                  # "host": CPU batches moved by the runtime; "device": created on the device
+    document_length_trace: tuple | None = None   # packed rows follow these document lengths (row i uses trace[i % len]) instead of random cuts
 
     def __post_init__(self) -> None:
+        if self.document_length_trace is not None:
+            if self.layout != "packed":
+                raise ValueError("document_length_trace needs the packed layout")
+            if not self.document_length_trace or any(not row or any(int(n) < 2 for n in row) for row in self.document_length_trace):
+                raise ValueError("document_length_trace rows must be non-empty lists of document lengths >= 2")
         if self.layout not in ("dense", "packed"):
             raise ValueError(f"synthetic layout must be dense or packed, got {self.layout!r}")
         if not 1 <= self.segment_count_min <= self.segment_count_max:
@@ -74,7 +81,7 @@ class SyntheticBatchConfig:
 
 # ------------------------------------------------------------------------------------------------ synthetic data
 def make_synthetic_batch(*, rows: int, seq_len: int, vocab_size: int, config: SyntheticBatchConfig, generator: torch.Generator,
-                         device: torch.device | str = "cpu") -> dict[str, torch.Tensor]:
+                         device: torch.device | str = "cpu", row_offset: int = 0) -> dict[str, torch.Tensor]:
     """One ``[rows, seq_len]`` batch with already-shifted labels (and positions / sequence ids when packed)."""
     tokens = torch.randint(0, vocab_size, (rows, seq_len + 1), generator=generator, dtype=torch.long)
     ids, labels = tokens[:, :-1].clone(), tokens[:, 1:].clone()
@@ -84,11 +91,20 @@ def make_synthetic_batch(*, rows: int, seq_len: int, vocab_size: int, config: Sy
     seq = torch.full((rows, seq_len), PAD_SEQUENCE_ID, dtype=torch.long)
     uniform = lambda lo, hi: lo + (hi - lo) * float(torch.rand((), generator=generator))   # noqa: E731
     for r in range(rows):
-        used = seq_len - int(round(uniform(0.0, config.max_padding_fraction) * seq_len))
-        n_docs = int(torch.randint(config.segment_count_min, config.segment_count_max + 1, (), generator=generator))
-        n_docs = max(1, min(n_docs, used // 2))
-        cuts = sorted(set(torch.randperm(max(used - 1, 1), generator=generator)[:n_docs - 1].add(1).tolist())) if n_docs > 1 else []
-        bounds = [0, *cuts, used]
+        if config.document_length_trace is not None:
+            lengths = [int(n) for n in config.document_length_trace[(row_offset + r) % len(config.document_length_trace)]]
+            if sum(lengths) > seq_len:
+                raise ValueError(f"document_length_trace row sums to {sum(lengths)} > seq_len {seq_len}")
+            bounds = [0]
+            for n in lengths:
+                bounds.append(bounds[-1] + n)
+            used = bounds[-1]
+        else:
+            used = seq_len - int(round(uniform(0.0, config.max_padding_fraction) * seq_len))
+            n_docs = int(torch.randint(config.segment_count_min, config.segment_count_max + 1, (), generator=generator))
+            n_docs = max(1, min(n_docs, used // 2))
+            cuts = sorted(set(torch.randperm(max(used - 1, 1), generator=generator)[:n_docs - 1].add(1).tolist())) if n_docs > 1 else []
+            bounds = [0, *cuts, used]
         for d, (a, b) in enumerate(zip(bounds, bounds[1:])):
             seq[r, a:b] = d
             pos[r, a:b] = torch.arange(b - a)
@@ -109,8 +125,8 @@ class SyntheticBatchStream:
                  device: torch.device, pool: int = 8) -> None:
         gen = torch.Generator().manual_seed(seed * 1000003 + stream_id)
         target = device if config.delivery == "device" else "cpu"
-        self.batches = [make_synthetic_batch(rows=rows, seq_len=seq_len, vocab_size=vocab_size, config=config, generator=gen, device=target)
-                        for _ in range(pool)]
+        self.batches = [make_synthetic_batch(rows=rows, seq_len=seq_len, vocab_size=vocab_size, config=config, generator=gen, device=target,
+                                             row_offset=i * rows) for i in range(pool)]
         if config.delivery == "host" and device.type == "cuda":
             self.batches = [{k: v.pin_memory() for k, v in b.items()} for b in self.batches]
         self.cursor = 0
@@ -146,8 +162,10 @@ def _load_cases(path: Path) -> dict[str, CaseDefinition]:
         if bool(body.get("recipe")) == bool(body.get("runtime_spec")):
             raise ValueError(f"case {name}: exactly one of recipe / runtime_spec is required")
         cases[name] = CaseDefinition(name=name, description=str(body.get("description", "")), recipe=body.get("recipe"),
-                                     runtime_spec=body.get("runtime_spec"), recipe_overrides=tuple(str(x) for x in body.get("overrides", ())),
-                                     synthetic=synthetic, warmup=body.get("warmup"), steps=body.get("steps"))
+                                     runtime_spec=body.get("runtime_spec"),
+                                     recipe_overrides=tuple(str(x) for x in (body.get("overrides") or body.get("recipe_overrides") or ())),
+                                     synthetic=synthetic, warmup=body.get("warmup"), steps=body.get("steps"),
+                                     require_calibrated_hdp_cost=bool(body.get("require_calibrated_hdp_cost", False)))
     return cases
 
 
@@ -161,21 +179,34 @@ def _parse_tool_args(argv=None) -> argparse.Namespace:
     p.add_argument("--warmup", type=int, default=None, help="untimed global optimizer steps")
     p.add_argument("--steps", type=int, default=None, help="timed global optimizer steps")
     p.add_argument("--synthetic-layout", choices=("dense", "packed"), default=None)
+    p.add_argument("--packed-input", action=argparse.BooleanOptionalAction, default=None, help="shortcut for --synthetic-layout packed / dense")
+    p.add_argument("--packed-sequences", type=int, default=None, help="fixed number of documents per packed row (min = max)")
     p.add_argument("--segment-count-min", type=int, default=None)
     p.add_argument("--segment-count-max", type=int, default=None)
     p.add_argument("--supervised-fraction-min", type=float, default=None)
     p.add_argument("--supervised-fraction-max", type=float, default=None)
     p.add_argument("--max-padding-fraction", type=float, default=None)
-    p.add_argument("--delivery", choices=("host", "device"), default=None, help="where synthetic batches are created")
+    p.add_argument("--delivery", "--synthetic-delivery", dest="delivery", choices=("host", "device", "cuda"), default=None,
+                   help="host: pinned CPU batches moved by the runtime (what a data loader delivers); device / cuda: created on the GPU")
+    p.add_argument("--data-source", choices=("synthetic", "recipe"), default=None,
+                   help="synthetic generator (default) or the recipe's own memory-mapped data loader (needs --data after --)")
     p.add_argument("--seed", type=int, default=1234, help="synthetic data seed")
     p.add_argument("--output-dir", type=Path, default=Path("profiles/train_perf"))
     p.add_argument("--profile", action="store_true", help="export a torch.profiler trace of the timed steps")
+    p.add_argument("--profile-all-ranks", action="store_true", help="trace every rank (large); default traces rank 0 only")
     p.add_argument("--profile-record-shapes", action="store_true")
     p.add_argument("--profile-memory", action="store_true")
     p.add_argument("--use-recipe-optimizer", action="store_true", help="keep the recipe's learning rate instead of lr=0")
     p.add_argument("--benchmark-lr", type=float, default=None, help="learning rate of the benchmark (default 0)")
     p.add_argument("recipe_overrides", nargs=argparse.REMAINDER, help="normal training flags after --")
-    return p.parse_args(argv)
+    args = p.parse_args(argv)
+    if args.packed_sequences is not None and args.packed_sequences < 2:
+        p.error("--packed-sequences must be >= 2")
+    if args.delivery == "cuda":
+        args.delivery = "device"
+    if args.packed_input is not None and args.synthetic_layout is None:
+        args.synthetic_layout = "packed" if args.packed_input else "dense"
+    return args
 
 
 def _resolve_case(args: argparse.Namespace, cases: dict[str, CaseDefinition]) -> CaseDefinition:
@@ -211,13 +242,19 @@ def _synthetic_config(args: argparse.Namespace, case: CaseDefinition) -> Synthet
     layout = args.synthetic_layout or ("packed" if spec.get("packed") else "dense")
     pick = lambda cli, key, default: cli if cli is not None else spec.get(key, default)   # noqa: E731
     packed = layout == "packed"
+    fixed = args.packed_sequences if args.packed_sequences is not None else spec.get("packed_sequences")
+    if fixed is not None and args.segment_count_min is None and args.segment_count_max is None:
+        spec["segment_count_min"] = spec["segment_count_max"] = int(fixed)
+    trace = spec.get("document_length_trace")
+    delivery = pick(args.delivery, "delivery", "host")
     return SyntheticBatchConfig(
+        document_length_trace=None if trace is None or not packed else tuple(tuple(int(n) for n in row) for row in trace),
         layout=layout, segment_count_min=pick(args.segment_count_min, "segment_count_min", 3),
         segment_count_max=pick(args.segment_count_max, "segment_count_max", 7),
         supervised_fraction_min=pick(args.supervised_fraction_min, "supervised_fraction_min", 0.55 if packed else 1.0),
         supervised_fraction_max=pick(args.supervised_fraction_max, "supervised_fraction_max", 0.70 if packed else 1.0),
         max_padding_fraction=pick(args.max_padding_fraction, "max_padding_fraction", 0.02 if packed else 0.0),
-        delivery=pick(args.delivery, "delivery", "host"))
+        delivery="device" if delivery == "cuda" else delivery)
 
 
 # ------------------------------------------------------------------------------------------------ run
@@ -261,10 +298,67 @@ def _flops_per_token(args: argparse.Namespace) -> float | None:
 
 
 def _environment() -> dict[str, Any]:
-    env: dict[str, Any] = {"python": platform.python_version(), "torch": torch.__version__, "host": platform.node()}
+    """What a number depends on besides the code: interpreter, libraries, devices, launcher and tuning variables, commit."""
+    import os
+    import subprocess
+
+    env: dict[str, Any] = {"python": platform.python_version(), "torch": torch.__version__, "host": platform.node(),
+                           "platform": platform.platform(), "cpu_count": os.cpu_count()}
     if torch.cuda.is_available():
-        env.update(device=torch.cuda.get_device_name(), cuda=torch.version.cuda, devices=torch.cuda.device_count())
+        props = torch.cuda.get_device_properties(torch.cuda.current_device())
+        env.update(device=props.name, cuda=torch.version.cuda, devices=torch.cuda.device_count(), sm=f"{props.major}.{props.minor}",
+                   sm_count=props.multi_processor_count, device_memory_gib=round(props.total_memory / 2**30, 1))
+        try:
+            env["nccl"] = ".".join(str(v) for v in torch.cuda.nccl.version())
+        except Exception:  # noqa: BLE001 - builds without NCCL
+            env["nccl"] = None
+    from maltos_b200.ops import _lib
+
+    env["kernel_library"] = str(_lib.library_path()) if _lib.available() else None
+    env["variables"] = {k: v for k, v in sorted(os.environ.items())
+                        if k.startswith(("MALTOS_B200_", "NCCL_", "TORCH_NCCL_", "CUDA_DEVICE_MAX_CONNECTIONS", "CUDA_VISIBLE_DEVICES", "OMP_NUM_THREADS"))}
+    try:
+        root = Path(__file__).resolve().parents[2]
+        env["commit"] = subprocess.run(["git", "-C", str(root), "rev-parse", "--short", "HEAD"], capture_output=True, text=True, timeout=5).stdout.strip() or None
+    except Exception:  # noqa: BLE001 - not a work tree / no git
+        env["commit"] = None
     return env
+
+
+def _trace_summary(config: SyntheticBatchConfig, seq_len: int) -> dict[str, Any] | None:
+    """Identity and shape of a fixed document trace (so that two summaries can be checked to describe the same workload)."""
+    trace = config.document_length_trace
+    if trace is None:
+        return None
+    import hashlib
+
+    flat = [n for row in trace for n in row]
+    return {"sha256": hashlib.sha256(json.dumps([list(r) for r in trace]).encode()).hexdigest()[:16], "rows": len(trace),
+            "documents": len(flat), "min_length": min(flat), "max_length": max(flat),
+            "active_fraction": sum(flat) / (len(trace) * seq_len)}
+
+
+class _TimedLoader:
+    """Wraps a loader and accumulates the time the training loop waits in ``next_batch`` (data stalls of a step)."""
+
+    def __init__(self, inner) -> None:
+        self.inner, self.wait_seconds, self.calls = inner, 0.0, 0
+
+    def next_batch(self, cp_rank=None):
+        t0 = time.perf_counter()
+        batch = self.inner.next_batch(cp_rank)
+        self.wait_seconds += time.perf_counter() - t0
+        self.calls += 1
+        return batch
+
+    def take(self) -> float:
+        w, self.wait_seconds = self.wait_seconds, 0.0
+        return w
+
+    def close(self) -> None:
+        closer = getattr(self.inner, "close", None)
+        if callable(closer):
+            closer()
 
 
 def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: CaseDefinition) -> dict[str, Any] | None:
@@ -277,6 +371,12 @@ def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: Cas
     elif not tool_args.use_recipe_optimizer:
         train_args.lr, train_args.min_lr = 0.0, 0.0        # stable workload: every kernel runs, nothing moves
     synthetic = _synthetic_config(tool_args, case)
+    data_source = tool_args.data_source or (case.synthetic or {}).get("data_source") or "synthetic"
+    if data_source == "recipe" and not getattr(train_args, "data", None):
+        raise SystemExit("--data-source recipe needs the recipe's data: pass --data <shards> after --")
+    if case.require_calibrated_hdp_cost and (train_args.hdp_cost_alpha, train_args.hdp_cost_beta, train_args.hdp_cost_gamma) == (1.0, 0.0, 0.0):
+        raise SystemExit(f"case {case.name} is a measurement case: pass calibrated --hdp-cost-alpha/-beta/-gamma after -- "
+                         "(the 1 / 0 / 0 proxy is refused)")
 
     train_cli._maybe_init_distributed(train_args)
     device = train_cli._select_device()
@@ -291,14 +391,22 @@ def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: Cas
         dp_group = core.get_group(MeshAxis.DP)
         dp_rank = dist.get_rank(dp_group) if dp_group is not None else 0
         stream_id = 0 if train_args.hdp_balanced else dp_rank
-        batches: Any = SyntheticBatchStream(rows=train_args.micro_batch_size, seq_len=train_args.seq_len, vocab_size=train_args.vocab_size,
-                                            config=synthetic, seed=tool_args.seed, stream_id=stream_id, device=device)
-        stream = batches
-        if train_args.hdp_balanced:
-            from maltos_b200.data.bytescale_hdp import ByteScaleHdpDataLoader
+        stream = None
+        if data_source == "recipe":
+            _, batches, _ = train_cli._build_dataloader(train_args, dp_rank=dp_rank, cp_token_planner=core.plan.cp_token_planner)
+        else:
+            batches = stream = SyntheticBatchStream(rows=train_args.micro_batch_size, seq_len=train_args.seq_len, vocab_size=train_args.vocab_size,
+                                                    config=synthetic, seed=tool_args.seed, stream_id=stream_id, device=device)
+            if train_args.hdp_balanced:
+                from maltos_b200.data.bytescale_hdp import ByteScaleHdpDataLoader
 
-            batches = ByteScaleHdpDataLoader(batches, hdp_rank=dp_rank, hdp_world_size=train_args.dp_size,
-                                             config=train_cli._build_hdp_config(train_args))
+                batches = ByteScaleHdpDataLoader(batches, hdp_rank=dp_rank, hdp_world_size=train_args.dp_size,
+                                                 config=train_cli._build_hdp_config(train_args))
+        if getattr(train_args, "data_prefetch_batches", 0):
+            from maltos_b200.data.prefetch import PrefetchDataLoader
+
+            batches = PrefetchDataLoader(batches)          # the next batch (and its HDP schedule) is prepared under the current step
+        batches = _TimedLoader(batches)
 
         def sync() -> None:
             if device.type == "cuda":
@@ -310,12 +418,13 @@ def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: Cas
         if device.type == "cuda":
             torch.cuda.reset_peak_memory_stats(device)
         profiler = None
-        if tool_args.profile and rank == 0:
+        if tool_args.profile and (rank == 0 or tool_args.profile_all_ranks):
             acts = [torch.profiler.ProfilerActivity.CPU] + ([torch.profiler.ProfilerActivity.CUDA] if device.type == "cuda" else [])
             profiler = torch.profiler.profile(activities=acts, record_shapes=tool_args.profile_record_shapes,
                                               profile_memory=tool_args.profile_memory)
             profiler.__enter__()
-        local, final_loss = [], float("nan")
+        local, waits, final_loss = [], [], float("nan")
+        batches.take()
         for i in range(steps):
             if dist.is_initialized():
                 dist.barrier()
@@ -324,12 +433,14 @@ def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: Cas
             loss = _run_global_step(core, batches)
             sync()
             local.append(time.perf_counter() - t0)
+            waits.append(batches.take())
             final_loss = _check_finite(loss, phase="timed", step=i)
         if profiler is not None:
             profiler.__exit__(None, None, None)
             tool_args.output_dir.mkdir(parents=True, exist_ok=True)
-            profiler.export_chrome_trace(str(tool_args.output_dir / "trace_rank0.json"))
+            profiler.export_chrome_trace(str(tool_args.output_dir / f"trace_rank{rank}.json"))
         seconds = _max_over_ranks(local, device)
+        data_wait = _max_over_ranks(waits, device)
         peak = torch.tensor([float(torch.cuda.max_memory_allocated(device)) if device.type == "cuda" else 0.0], dtype=torch.float64,
                             device=device if device.type == "cuda" else "cpu")
         if dist.is_initialized() and world > 1:
@@ -349,7 +460,11 @@ def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: Cas
             "synthetic_seed": tool_args.seed, "warmup_steps": warmup, "timed_steps": steps, "step_seconds": seconds,
             "mean_step_seconds": mean, "p50_step_seconds": float(torch.quantile(t, 0.5)), "p90_step_seconds": float(torch.quantile(t, 0.9)),
             "tokens_per_step": tokens, "tokens_per_second": tokens / mean,
-            "active_target_fraction": sum(stream.active_tokens) / (len(stream.batches) * train_args.micro_batch_size * train_args.seq_len),
+            "active_target_fraction": None if stream is None else
+            sum(stream.active_tokens) / (len(stream.batches) * train_args.micro_batch_size * train_args.seq_len),
+            "data_source": data_source, "data_prefetch_batches": int(getattr(train_args, "data_prefetch_batches", 0) or 0),
+            "data_wait_seconds_per_step": sum(data_wait) / len(data_wait), "data_wait_fraction": sum(data_wait) / sum(seconds),
+            "document_trace": _trace_summary(synthetic, train_args.seq_len),
             "model_flops_per_token": fpt, "model_tflops_per_gpu": None if fpt is None else tokens / mean * fpt / world / 1e12,
             "peak_memory_gib": float(peak.item()) / 2**30, "final_loss": final_loss, "profiled": bool(tool_args.profile),
             "learning_rate": train_args.lr, "environment": _environment(),
@@ -358,6 +473,9 @@ def run(train_args: argparse.Namespace, tool_args: argparse.Namespace, case: Cas
         return summary
     finally:
         core.close()
+        closer = getattr(locals().get("batches"), "close", None)
+        if callable(closer):
+            closer()
 
 
 def _write_summary(output_dir: Path, summary: dict[str, Any]) -> None:
@@ -368,6 +486,8 @@ def _write_summary(output_dir: Path, summary: dict[str, Any]) -> None:
              f"steps: warmup={summary['warmup_steps']} timed={summary['timed_steps']}  layout={summary['synthetic']['layout']}",
              f"step time: mean {summary['mean_step_seconds']:.4f}s  p50 {summary['p50_step_seconds']:.4f}s  p90 {summary['p90_step_seconds']:.4f}s",
              f"throughput: {summary['tokens_per_second']:,.0f} tokens/s" + (f"  {tf:.1f} model TFLOP/s/GPU" if tf is not None else ""),
+             f"data: {summary['data_source']} prefetch={summary['data_prefetch_batches']} wait {summary['data_wait_seconds_per_step'] * 1e3:.2f} ms/step "
+             f"({summary['data_wait_fraction'] * 100:.1f} % of the step)",
              f"peak memory: {summary['peak_memory_gib']:.2f} GiB  final loss: {summary['final_loss']:.4f}"]
     (output_dir / "summary.txt").write_text("\n".join(lines) + "\n", encoding="utf-8")
     print("\n".join(lines))

@@ -107,3 +107,54 @@ def test_data_presets_build_the_tool_arguments_from_the_environment(capsys):
     assert ns.max_tokens == 500000000 and ns.streaming
     ns = prepare_sft_shards.parse_args(olmo)
     assert ns.seq_len == 4096 and ns.assistant_only_loss
+
+
+def _tiny_recipe(tmp_path):
+    recipe = tmp_path / "r.yaml"
+    recipe.write_text("seed: 1\ndata: {seq_len: 32, micro_batch_size: 2}\nmodel: {type: llama, hidden_size: 64, num_heads: 4, num_kv_heads: 2, "
+                      "intermediate_size: 128, num_layers: 2, vocab_size: 128}\ntraining: {grad_accum_steps: 2, lr: 0.001}\n")
+    return recipe
+
+
+def test_profiler_document_trace_fixed_segments_and_metadata(tmp_path):
+    recipe = _tiny_recipe(tmp_path)
+    cases = tmp_path / "cases.yaml"
+    cases.write_text(f"cases:\n  traced:\n    recipe: {recipe}\n    synthetic:\n      packed: true\n      document_length_trace:\n        - [16, 8, 4]\n"
+                     f"        - [30]\n    warmup: 0\n    steps: 1\n  measured:\n    recipe: {recipe}\n    require_calibrated_hdp_cost: true\n")
+    ptp.main(["--case-file", str(cases), "--case", "traced", "--output-dir", str(tmp_path / "out")])
+    summary = json.loads((tmp_path / "out" / "summary.json").read_text())
+    trace = summary["document_trace"]
+    assert trace["rows"] == 2 and trace["documents"] == 4 and trace["max_length"] == 30 and abs(trace["active_fraction"] - 58 / 64) < 1e-9
+    assert summary["data_source"] == "synthetic" and 0.0 <= summary["data_wait_fraction"] < 1.0
+    env = summary["environment"]
+    assert {"python", "torch", "host", "platform", "variables", "commit", "kernel_library"} <= set(env)
+    # rows follow the trace in order, across batches
+    cfg = ptp.SyntheticBatchConfig(layout="packed", document_length_trace=((16, 8, 4), (30,)))
+    b = ptp.make_synthetic_batch(rows=2, seq_len=32, vocab_size=50, config=cfg, generator=torch.Generator().manual_seed(0), row_offset=1)
+    assert int((b["sequence_ids"][0] != PAD_SEQUENCE_ID).sum()) == 30 and int(b["sequence_ids"][1].max()) == 2
+    assert (b["sequence_ids"][1][28:] == PAD_SEQUENCE_ID).all()
+    with pytest.raises(ValueError, match="sums to"):
+        ptp.make_synthetic_batch(rows=1, seq_len=16, vocab_size=50, config=cfg, generator=torch.Generator().manual_seed(0))
+    with pytest.raises(ValueError, match="packed layout"):
+        ptp.SyntheticBatchConfig(layout="dense", document_length_trace=((4,),))
+    # a measurement case refuses the uncalibrated cost proxy
+    with pytest.raises(SystemExit, match="calibrated"):
+        ptp.main(["--case-file", str(cases), "--case", "measured", "--output-dir", str(tmp_path / "out2")])
+    # compatibility spellings of the flags
+    args = ptp._parse_tool_args(["--recipe", str(recipe), "--packed-input", "--packed-sequences", "4", "--synthetic-delivery", "cuda"])
+    cfg = ptp._synthetic_config(args, ptp.CaseDefinition(name="x", recipe=str(recipe)))
+    assert cfg.layout == "packed" and cfg.segment_count_min == cfg.segment_count_max == 4 and cfg.delivery == "device"
+
+
+def test_profiler_can_time_the_recipes_own_loader(tmp_path):
+    import numpy as np
+
+    recipe = _tiny_recipe(tmp_path)
+    np.random.default_rng(0).integers(0, 128, size=4000, dtype=np.uint32).tofile(tmp_path / "tokens_00000.bin")
+    ptp.main(["--recipe", str(recipe), "--data-source", "recipe", "--warmup", "0", "--steps", "2", "--output-dir", str(tmp_path / "out"), "--",
+              "--data", str(tmp_path / "tokens_00000.bin"), "--data-prefetch-batches", "1"])
+    summary = json.loads((tmp_path / "out" / "summary.json").read_text())
+    assert summary["data_source"] == "recipe" and summary["data_prefetch_batches"] == 1 and summary["active_target_fraction"] is None
+    assert summary["timed_steps"] == 2 and summary["tokens_per_second"] > 0
+    with pytest.raises(SystemExit, match="--data"):
+        ptp.main(["--recipe", str(recipe), "--data-source", "recipe", "--output-dir", str(tmp_path / "o2")])
