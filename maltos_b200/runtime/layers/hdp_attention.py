@@ -20,7 +20,7 @@ from maltos_b200.utils.constants import PAD_SEQUENCE_ID
 from maltos_b200.utils.profiling import span
 
 from .attn_masking_utils import canonical_position_ids, canonical_sequence_ids
-from .cp_functional import dynamic_flash_ring_attention
+from .cp_functional import document_ring_plan, dynamic_flash_ring_attention
 
 if TYPE_CHECKING:
     from maltos_b200.parallel.hdp_helper import ByteScaleHdpLocalLayout
@@ -77,11 +77,15 @@ class HdpBalancedAttentionCore(nn.Module):
                     continue
                 rows, cols = slice(doc.local_row, doc.local_row + 1), slice(doc.local_start, doc.local_end)
                 doc_seq = seq[rows, cols] if seq is not None else None
+                cache_key = ("ring", str(q.device), doc.document_id)
+                plan = layout.attention_metadata_cache.get(cache_key)
+                if plan is None:      # host-side knowledge of the document's ring, shared by all layers of the wave
+                    plan = document_ring_plan(sequence_length=doc.sequence_length, padded_length=doc.padded_length,
+                                              local_length=doc.local_end - doc.local_start, ring_size=len(doc.participant_ranks))
                 piece = dynamic_flash_ring_attention(q[rows, cols], k[rows, cols], v[rows, cols], positions=pos[rows, cols],
                                                      sequence_ids=doc_seq, group=self.group, participant_ranks=doc.participant_ranks,
                                                      module_id=id(self), partition_tokens=layout.partition_tokens,
-                                                     metadata_cache=layout.attention_metadata_cache,
-                                                     metadata_cache_key=("ring", str(q.device), doc.document_id))
+                                                     metadata_cache=layout.attention_metadata_cache, metadata_cache_key=cache_key, plan=plan)
                 out = out + _scatter_columns(piece, B, S, doc.local_row, doc.local_start)
             return out
 

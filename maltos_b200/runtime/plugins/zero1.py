@@ -378,47 +378,10 @@ class Zero1Plugin(ZeroPluginBase):
         return out
 
 
-class Zero2Plugin(Zero1Plugin):
-    accumulate_on_shard = True
+def __getattr__(name: str):
+    # `zero1.Zero2Plugin` keeps working for callers that imported it from here; the class lives in zero2.py
+    if name == "Zero2Plugin":
+        from .zero2 import Zero2Plugin
 
-    def __init__(self, bucket_mb_size: int = 25, *, peer_memory: bool | None = None) -> None:
-        super().__init__(bucket_mb_size, peer_memory=peer_memory, _id=PluginId.ZERO2, _name="zero2")
-
-    def _pre_backward(self, ctx) -> None:
-        for b in self.buckets:
-            if ctx.accum_start and b.local_param.grad is not None:
-                b.local_param.grad.zero_()
-            if b.grad is None:
-                b.grad_handle = acquire_buffer(shape=(b.data.numel(),), dtype=b.data.dtype, device=b.data.device, policy=BufferPolicy.TEMPORARY)
-                b.grad = b.grad_handle.tensor
-            b.grad.zero_()
-            self._attach_grad_views(b)
-            b.pending = len(b.params)
-            b.fired = False
-
-    def _post_backward(self, ctx) -> None:
-        with span("maltos::zero.grad_sync.wait"):
-            self._peer_phase(True)
-            for b in self.buckets:
-                self._finish(b)
-                for p in b.params:
-                    p.grad = None
-                if b.grad_handle is not None:
-                    release_buffer(b.grad_handle)
-                if b.peer_grad_ptrs is None:
-                    b.grad, b.grad_handle = None, None
-            self._peer_phase(False)
-
-    def export_plugin_state(self):
-        ctx = self.runtime.state.step_context
-        if ctx.microbatch_idx == 0:
-            return {}
-        return {"bucket_local_grads": [None if b.local_param.grad is None else b.local_param.grad.detach().cpu().clone() for b in self.buckets]}
-
-    def import_plugin_state(self, state) -> None:
-        grads = state.get("bucket_local_grads")
-        if not isinstance(grads, list):
-            return
-        for b, g in zip(self.buckets, grads):
-            if g is not None:
-                b.local_param.grad = g.to(device=b.local_param.device, dtype=b.local_param.dtype)
+        return Zero2Plugin
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

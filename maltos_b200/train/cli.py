@@ -214,7 +214,8 @@ def _build_runtime(args: argparse.Namespace, model: nn.Module, device: torch.dev
     from maltos_b200.runtime.plugins.torch_profiler import TorchProfilerPlugin
     from maltos_b200.runtime.plugins.tp import TensorParallelPlugin
     from maltos_b200.runtime.plugins.tp_sp import TpSpPlugin
-    from maltos_b200.runtime.plugins.zero1 import Zero1Plugin, Zero2Plugin
+    from maltos_b200.runtime.plugins.zero1 import Zero1Plugin
+    from maltos_b200.runtime.plugins.zero2 import Zero2Plugin
     from maltos_b200.runtime.plugins.zero3 import Zero3Plugin
 
     dtype = {"fp32": None, "bf16": torch.bfloat16, "fp16": torch.float16}[args.precision]

@@ -128,13 +128,23 @@ def _opt(params):
     return torch.optim.AdamW(params, lr=1e-2, weight_decay=0.0)
 
 
-def _hdp_worker(rank, world):
+def _hdp_worker(rank, world, partition_tokens=16):
     import maltos_b200  # noqa: F401
     from maltos_b200.runtime import MeshConfig, RuntimeCore
+    from maltos_b200.runtime.layers import hdp_attention
     from maltos_b200.runtime.plugins import ddp
     from maltos_b200.runtime.plugins.hdp import ByteScaleHdpPlugin
 
-    cfg = ByteScaleHdpBalancedConfig(partition_tokens=16, cost_model=ByteScaleHdpCostModel(1.0, 8.0, 32.0))
+    plans = []
+    make_plan = hdp_attention.document_ring_plan
+
+    def recording(**kw):
+        plan = make_plan(**kw)
+        plans.append((kw["ring_size"], plan.zigzag))
+        return plan
+
+    hdp_attention.document_ring_plan = recording
+    cfg = ByteScaleHdpBalancedConfig(partition_tokens=partition_tokens, cost_model=ByteScaleHdpCostModel(1.0, 8.0, 32.0))
     rt = RuntimeCore(model=_model(), mesh=MeshConfig(dp=world), plugins=[ddp.DataParallelPlugin(), ByteScaleHdpPlugin(config=cfg)],
                      optimizer_factory=_opt, grad_accum_steps=1)
     rt.setup()
@@ -150,10 +160,22 @@ def _hdp_worker(rank, world):
     metrics = rt.collect_metrics()
     params = {n: p.detach().clone() for n, p in rt.model.named_parameters()}
     rt.close()
-    return losses, params, {k: v for k, v in metrics.items() if "wave" in k}
+    return losses, params, {k: v for k, v in metrics.items() if "wave" in k}, plans
 
 
-def test_hdp_training_matches_single_process():
+def test_document_ring_plan_allows_the_half_block_schedule_only_with_confined_padding():
+    from maltos_b200.runtime.layers.cp_functional import document_ring_plan
+
+    ok = document_ring_plan(sequence_length=30, padded_length=32, local_length=8, ring_size=4)        # chunk 4, padding 2
+    assert ok.zigzag and ok.visible == (True,) * 4
+    assert document_ring_plan(sequence_length=32, padded_length=32, local_length=16, ring_size=2).zigzag
+    assert not document_ring_plan(sequence_length=26, padded_length=32, local_length=8, ring_size=4).zigzag    # padding spills into chunk 6
+    assert not document_ring_plan(sequence_length=30, padded_length=30, local_length=15, ring_size=2).zigzag   # not a multiple of 2R
+    assert not document_ring_plan(sequence_length=8, padded_length=8, local_length=8, ring_size=1).zigzag
+
+
+@pytest.mark.parametrize("world,partition_tokens", [(2, 16), (4, 8)])
+def test_hdp_training_matches_single_process(world, partition_tokens):
     model = _model()
     opt = _opt(model.parameters())
     ref_losses = []
@@ -165,12 +187,15 @@ def test_hdp_training_matches_single_process():
         opt.step()
         ref_losses.append(float(loss.detach()))
     ref_params = {n: p.detach().clone() for n, p in model.named_parameters()}
-    world = 2
-    results = run_distributed(_hdp_worker, world)
+    results = run_distributed(_hdp_worker, world, partition_tokens)
+    rings = [p for r in results for p in r[3]]
+    assert any(z for _, z in rings), "no document ring used the half-block schedule"
+    if world == 4:
+        assert {n for n, _ in rings} >= {2, 4}, rings                       # rings of different sizes in one batch
     for step in range(2):   # each rank reports world x its share of the global mean
         total = sum(r[0][step] for r in results) / world
         assert abs(total - ref_losses[step]) < 2e-4, (total, ref_losses[step])
-    for _, params, wave_metrics in results:
+    for _, params, wave_metrics, _ in results:
         assert wave_metrics.get("hdp/real_wave_count", wave_metrics.get("real_wave_count", 1)) >= 1
         for name, ref in ref_params.items():
             assert torch.allclose(params[name], ref, atol=2e-4, rtol=1e-3), name
