@@ -8,9 +8,11 @@ copy stream while the previous block is computed. In backward each dK/dV contrib
 owner keeps for the contributing rank, and the owner sums its slots in rank order (deterministic), so the accumulator
 never circulates.
 
-The copy kernel never waits on a peer. Barriers (one-element all-reduces, stream-ordered): A before a rank overwrites
-what it published (all pulls of the previous call are done), B after publishing (and zeroing the gradient slots), C in
-backward after the pushes.
+The copy kernel never waits on a peer. Barriers (one-element all-reduces, stream-ordered): B after publishing (and
+zeroing the gradient slots), C in backward after the pushes. The published block is double-buffered by call parity, which
+makes a barrier in front of the publish unnecessary: a rank reaches the publish of call ``n + 2`` only after barrier B of
+call ``n + 1``, which every rank enters (in stream order) after its pulls of call ``n``; the gradient slots are recycled
+only after barrier C (``utils/flag_protocol.ring_publish`` checks both over every interleaving).
 """
 from __future__ import annotations
 
@@ -55,6 +57,7 @@ class PeerRing:
         self.rank, self.world = ctx.rank, ctx.world
         self.copy_stream = torch.cuda.Stream(device=ctx.device)
         self._token = torch.zeros(1, dtype=torch.float32, device=ctx.device)
+        self._calls = 0          # publishes so far; its parity picks the half of the published buffer (same on every rank)
 
     def barrier(self) -> None:
         dist.all_reduce(self._token, group=self.group)
@@ -73,7 +76,11 @@ class PeerRing:
         ``grad_slots_like`` also zeroes ``world`` fp32 slots shaped like those tensors. Returns the layout."""
         tensors = [t.contiguous() for t in tensors]
         offs, total = self._layout(tensors)
-        sb = self.ctx.ensure_buffer("ring_kv", total)
+        sb = self.ctx.ensure_buffer("ring_kv", 2 * total)
+        half = sb.nbytes // 2 // _ALIGN * _ALIGN           # from the buffer's size: equal on every rank, stable while it lives
+        base = (self._calls & 1) * half
+        self._calls += 1
+        offs = [base + o for o in offs]
         slots = None
         if grad_slots_like is not None:
             sizes = [t.numel() * 4 for t in grad_slots_like]
@@ -84,28 +91,27 @@ class PeerRing:
             g_total = at
             gsb = self.ctx.ensure_buffer("ring_dkv", g_total * self.world)
             slots = (gsb, g_offs, g_total)
-        self.barrier()                                                                    # A
         for t, o in zip(tensors, offs):
             _copy(sb.local_ptr + o, t.data_ptr(), t.numel() * t.element_size())
         if slots is not None:
             gsb, _, g_total = slots
             gsb.local_tensor(torch.uint8, g_total * self.world, self.ctx.device).zero_()
         self.barrier()                                                                    # B
-        return (sb, offs, total, [(t.shape, t.dtype) for t in tensors]), slots
+        return (sb, offs, total, [(t.shape, t.dtype) for t in tensors], base), slots
 
     def pull(self, layout, owner: int):
         """Starts fetching ``owner``'s published block on the copy stream; returns ``(views, event)``."""
-        sb, offs, total, metas = layout
+        sb, offs, total, metas, base = layout
         main = torch.cuda.current_stream()
         stage = torch.empty(total, dtype=torch.uint8, device=self.ctx.device)
         self.copy_stream.wait_stream(main)               # the staging memory may have been in use on the main stream
         with torch.cuda.stream(self.copy_stream):
-            _copy(stage.data_ptr(), sb.peer_ptrs[owner], total, self.PULL_BLOCKS)
+            _copy(stage.data_ptr(), sb.peer_ptrs[owner] + base, total, self.PULL_BLOCKS)
             ev = torch.cuda.Event()
             ev.record(self.copy_stream)
         stage.record_stream(self.copy_stream)
         views = []
-        for o, (shape, dtype) in zip(offs, metas):
+        for o, (shape, dtype) in zip((o - base for o in offs), metas):
             n = 1
             for d in shape:
                 n *= d

@@ -190,22 +190,26 @@ def alternating_buffers_with_barrier(world: int, transfers: int, *, buffers: int
     return programs
 
 
-def ring_publish(world: int, calls: int, *, barrier_before_overwrite: bool = True, backward: bool = True) -> dict:
-    """Ring attention over peer memory: barrier A (all pulls of the previous call are done), publish the own block,
-    barrier B, pull the peers' blocks; in backward push one gradient contribution into every owner's slot for this rank,
-    barrier C, sum the own slots. ``barrier_before_overwrite=False`` drops barrier A (broken)."""
+def ring_publish(world: int, calls: int, *, barrier_before_overwrite: bool = True, backward: bool = True, buffers: int = 1) -> dict:
+    """Ring attention over peer memory: publish the own block into buffer ``n % buffers``, barrier B, pull the peers'
+    blocks; in backward push one gradient contribution into every owner's slot for this rank, barrier C, sum the own slots.
+    With ONE published buffer a barrier A is needed in front (all pulls of the previous call are done) -
+    ``barrier_before_overwrite=False`` with one buffer is the broken variant. With TWO buffers alternating by call A is
+    redundant: a rank reaches the publish of call ``n + 2`` only after barrier B of call ``n + 1``, which every rank enters
+    after its pulls of call ``n``. The gradient slots need neither: they are recycled only after barrier C."""
     members = tuple(f"rank{r}" for r in range(world))
     programs = {}
     for me in range(world):
         prog = []
         for n in range(1, calls + 1):
+            b = n % buffers
             if barrier_before_overwrite:
                 prog.append(("barrier", f"A{n}", members))
-            prog.append(("write", ("kv", me), n))
+            prog.append(("write", ("kv", me, b), n))
             if backward:
                 prog += [("write", ("grad", me, src), -n) for src in range(world)]       # the owner zeroes its slots
             prog.append(("barrier", f"B{n}", members))
-            prog += [("read", ("kv", (me - s) % world), n) for s in range(1, world)]
+            prog += [("read", ("kv", (me - s) % world, b), n) for s in range(1, world)]
             if backward:
                 prog += [("write", ("grad", owner, me), n) for owner in range(world)]
                 prog.append(("barrier", f"C{n}", members))

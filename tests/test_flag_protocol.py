@@ -39,10 +39,13 @@ def test_alternating_dispatch_buffers_with_one_barrier(world):
 
 @pytest.mark.parametrize("world", [2, 3])
 def test_ring_publish_barriers(world):
-    fp.explore(fp.ring_publish(world, 3))                                    # backward form: A, B, C
-    fp.explore(fp.ring_publish(world, 3, backward=False))                    # forward form: A, B
+    fp.explore(fp.ring_publish(world, 3))                                    # one buffer, backward form: A, B, C
+    fp.explore(fp.ring_publish(world, 3, backward=False))                    # one buffer, forward form: A, B
     with pytest.raises(fp.ProtocolViolation, match="overlaps a write"):
         fp.explore(fp.ring_publish(world, 3, backward=False, barrier_before_overwrite=False))
+    # what ops/peer_ring.py does: two buffers alternating by call, no barrier in front of the publish
+    fp.explore(fp.ring_publish(world, 4, backward=False, buffers=2, barrier_before_overwrite=False))
+    fp.explore(fp.ring_publish(world, 3, backward=True, buffers=2, barrier_before_overwrite=False))
 
 
 def test_explorer_reports_deadlock_and_overlapping_writes():
