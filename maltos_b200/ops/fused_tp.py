@@ -170,9 +170,10 @@ if _SCATTER_KIND:
 
 
 def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
-    # MALTOS_B200_FUSED_SCATTER: "1" always, "0" never, unset = only for groups of two. Measured on B200 at TP=2 the fused
-    # launch beats GEMM + NCCL reduce-scatter (o_proj 214 vs 247 us, down 469 vs 542 us, +2.3 % on the training step); on
-    # larger NVSwitch groups NCCL reduces inside the switch and was the faster pair when last measured (TP=4).
+    # MALTOS_B200_FUSED_SCATTER: "1" always, "0" never, unset = only for groups of two. Measured on B200 at TP=2 the
+    # epilogue push beats GEMM + NCCL reduce-scatter (o_proj 214 vs 247 us, down 469 vs 542 us, +2.3 % on the training
+    # step); in larger groups GEMM + the owner-side pull kernel is the faster pair (TP=4: 165 vs 171 us, TP=8: 163 vs
+    # 267 us for o_proj), which is what reduce_scatter_gemm picks there.
     mode = os.environ.get("MALTOS_B200_FUSED_SCATTER", "auto")
     if mode == "0" or (mode != "1" and symm.world > 2):
         return False
@@ -182,8 +183,8 @@ def _fused_scatter_ok(symm, x2: torch.Tensor, n_out: int) -> bool:
 def _fused_gather_ok(symm, M: int, N: int, K: int) -> bool:
     """Whether the all-gather should ride inside the GEMM launch. MALTOS_B200_FUSED_GATHER: "1" always, "0" never, unset =
     measured rule: in groups larger than four a GEMM of less than ~1.5e11 FLOP is shorter than the push of this rank's
-    rows to seven peers, and NCCL all-gather + GEMM wins (q/k/v at TP=8: 206 vs 416 us; gate/up at TP=8 is a tie, every
-    shape at TP=2 and TP=4 is faster fused)."""
+    rows to seven peers, so the gather runs as a launch of its own in front of the GEMM (q/k/v at TP=8: pull kernel + GEMM
+    231 us vs 257 us with the push inside; gate/up at TP=8 and every shape at TP=2 and TP=4 are faster fused)."""
     mode = os.environ.get("MALTOS_B200_FUSED_GATHER", "auto")
     if mode in ("0", "1"):
         return mode == "1"
