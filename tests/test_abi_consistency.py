@@ -1,0 +1,51 @@
+"""Static check of the Python <-> C boundary: every ``mb_*`` entry point that Python calls is exported by a ``csrc/*.cu``
+file, and every call passes exactly as many arguments as the C prototype declares (ctypes would not notice a mismatch:
+a missing trailing argument becomes whatever is in the register)."""
+import ast
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+PKG = ROOT / "maltos_b200"
+
+
+def _c_prototypes() -> dict[str, int]:
+    protos = {}
+    for src in sorted((PKG / "csrc").glob("*.cu")):
+        text = re.sub(r"//[^\n]*", "", src.read_text(encoding="utf-8"))
+        for m in re.finditer(r"MB_API\s+[\w\s\*]+?\b(mb_\w+)\s*\(([^)]*)\)\s*\{", text, flags=re.S):
+            params = m.group(2).strip()
+            protos[m.group(1)] = 0 if params in ("", "void") else len([p for p in params.split(",") if p.strip()])
+    return protos
+
+
+def _python_calls():
+    calls = []
+    for py in sorted(PKG.rglob("*.py")) + [ROOT / "bench.py", ROOT / "__graft_entry__.py"]:
+        tree = ast.parse(py.read_text(encoding="utf-8"))
+        for node in ast.walk(tree):
+            if isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr.startswith("mb_"):
+                if any(isinstance(a, ast.Starred) for a in node.args):
+                    continue
+                calls.append((py.relative_to(ROOT), node.lineno, node.func.attr, len(node.args)))
+    return calls
+
+
+def test_every_called_entry_point_exists_with_the_same_number_of_arguments():
+    protos = _c_prototypes()
+    assert len(protos) >= 40, sorted(protos)
+    calls = _python_calls()
+    assert len(calls) >= 40
+    problems = []
+    for path, line, name, nargs in calls:
+        if name not in protos:
+            problems.append(f"{path}:{line}: {name} is not exported by any csrc/*.cu")
+        elif protos[name] != nargs:
+            problems.append(f"{path}:{line}: {name} called with {nargs} arguments, the C prototype has {protos[name]}")
+    assert not problems, "\n".join(problems)
+
+
+def test_probe_only_entry_points_are_not_called_from_the_package():
+    called = {name for _, _, name, _ in _python_calls()}
+    assert not called & {"mb_gemm_set_trace", "mb_gemm_set_debug_mode", "mb_gemm_set_debug_stages", "mb_gemm_set_debug_max_pairs",
+                         "mb_gemm_debug_descriptor", "mb_flash_probe_read", "mb_pull_probe_read"}
