@@ -305,7 +305,8 @@ class Zero1Plugin(ZeroPluginBase):
         elif phase is RuntimePhase.POST_STEP:
             self._gather_updated_params()
         elif phase is RuntimePhase.POST_LOAD:
-            self._resync_from_buffers()
+            # with a restored optimizer state the fp32 masters came from the checkpoint; only a weights-only load re-derives them
+            self._resync_from_buffers(sync_masters=not self.runtime.state.metadata.get("optimizer_state_restored", False))
 
     def _pre_backward(self, ctx) -> None:
         for b in self.buckets:
@@ -354,12 +355,12 @@ class Zero1Plugin(ZeroPluginBase):
                 for g in self._peer_groups():
                     self._barrier(g)    # all peers' stores have landed before the next forward reads the parameters
 
-    def _resync_from_buffers(self) -> None:
+    def _resync_from_buffers(self, *, sync_masters: bool = True) -> None:
         with torch.no_grad():
             for b in self.buckets:
                 b.local_param.data.copy_(b.data[b.shard_start:b.shard_end])
         sync = getattr(self.optimizer, "sync_master_params_from_model", None)
-        if callable(sync):
+        if sync_masters and callable(sync):
             sync()
 
     # ------------------------------------------------------------------ clipping

@@ -418,8 +418,9 @@ class Zero3Plugin(ZeroPluginBase):
         elif phase is RuntimePhase.POST_STEP:
             self._peer_barrier()     # every shard is updated before the next forward pulls it
         elif phase is RuntimePhase.POST_LOAD:
+            # with a restored optimizer state the fp32 masters came from the checkpoint; only a weights-only load re-derives them
             sync = getattr(self.optimizer, "sync_master_params_from_model", None)
-            if callable(sync):
+            if callable(sync) and not self.runtime.state.metadata.get("optimizer_state_restored", False):
                 sync()
             self._peer_barrier()
 

@@ -212,6 +212,8 @@ def load_sharded_checkpoint(state_manager: StateManager, path, *, weights_only: 
             dataloader=trainer_blob.get("dataloader"),
             plugin_states=trainer_blob.get("plugin_states"),
         ))
+    # plugins that re-derive their shards after a load must not round restored fp32 master weights through the model dtype
+    runtime.state.metadata["optimizer_state_restored"] = optim_blob is not None
     runtime._run_step_phase(RuntimePhase.POST_LOAD)
     distributed_barrier()
 

@@ -109,6 +109,9 @@ CASES = {
     "bf16_dp4_tp2_zero1_accum2": C("llama", "--dp-size 4 --tp-size 2 --zero-stage 1 --precision bf16", accum=2),
     "bf16_dp2_pp2_tp2_1f1b": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --pp-schedule 1f1b --precision bf16", pp_mb=2),
     "fp16_dp8_zero2": C("llama", "--dp-size 8 --zero-stage 2 --precision fp16"),
+    "bf16_dp8": C("llama", "--dp-size 8 --precision bf16"),
+    "bf16_dp8_zero1": C("llama", "--dp-size 8 --zero-stage 1 --precision bf16"),
+    "bf16_dp8_zero3": C("llama", "--dp-size 8 --zero-stage 3 --precision bf16"),
     # ---- the small reference transformer
     "tiny_dp4_tp2_sp_zero3": C("tiny", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3"),
     "tiny_dp4_pp2_afab": C("tiny", "--dp-size 4 --pp-size 2 --pp-schedule afab", pp_mb=2),
@@ -117,6 +120,8 @@ CASES = {
 RESUME = {   # case name -> micro-steps to run before the checkpoint (a multiple of the case's accumulation = step boundary)
     "dp4_tp2_sp_zero3_accum2": 2, "dp4_zero3_tp2_accum2": 3, "dp2_pp2_tp2_1f1b_zero1": 1, "dp2_cp2_tp2_sp_ring_zero3": 1, "moe_dp8_ep4_zero2": 1,
     "olmo_dp4_tp2_sp_zero3_ckpt": 3, "dp4_bucket_tp2": 2, "dp2_pp2_tp2_sp_afab_zero3": 1,
+    # bf16 with fp32 master weights: the masters, not the rounded model weights, must come back
+    "bf16_dp4_tp2_sp_zero3": 1, "bf16_dp4_tp2_zero1_accum2": 3, "fp16_dp8_zero2": 1, "bf16_dp8": 1, "bf16_dp8_zero1": 1, "bf16_dp8_zero3": 1,
 }
 
 
@@ -361,4 +366,7 @@ def test_resume_equals_uninterrupted_training(name, resume_results):
         assert status == "ok", continuous
         assert len(continuous) == len(resumed)
         worst = max(abs(x - y) for x, y in zip(continuous, resumed))
-        assert worst < (5e-5 if not mid else 2e-4), (name, rank, mid, continuous, resumed)
+        limit = 5e-5 if not mid else 2e-4
+        if "--precision" in CASES[name]["flags"] and mid:
+            limit = 2e-3      # a window interrupted in bf16 re-rounds the partial gradient once
+        assert worst < limit, (name, rank, mid, continuous, resumed)
