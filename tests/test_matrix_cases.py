@@ -32,8 +32,9 @@ COMMON = ["--vocab-size", str(VOCAB), "--seq-len", str(SEQ), "--lr", "1e-3", "--
           "--precision", "fp32", "--disable-metrics"]
 
 
-def C(model, flags, *, accum=1, packed=False, pp_mb=None):
-    return dict(model=model, flags=flags.split(), accum=accum, packed=packed, pp_mb=pp_mb)
+def C(model, flags, *, accum=1, packed=False, pp_mb=None, common=""):
+    """``common``: flags that change the mathematics (router, schedule) and therefore also go to the single-process baseline."""
+    return dict(model=model, flags=flags.split() + common.split(), accum=accum, packed=packed, pp_mb=pp_mb, common=common)
 
 
 CASES = {
@@ -109,6 +110,11 @@ CASES = {
     "bf16_dp4_tp2_zero1_accum2": C("llama", "--dp-size 4 --tp-size 2 --zero-stage 1 --precision bf16", accum=2),
     "bf16_dp2_pp2_tp2_1f1b": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --pp-schedule 1f1b --precision bf16", pp_mb=2),
     "fp16_dp8_zero2": C("llama", "--dp-size 8 --zero-stage 2 --precision fp16"),
+    # ---- choices that change the mathematics: the baseline gets them too
+    "moe_top2_dp8_ep4": C("moe", "--dp-size 8 --ep-size 4", common="--moe-top-k 2"),
+    "moe_top2_dp4_tp2_ep2_zero1": C("moe", "--dp-size 4 --tp-size 2 --ep-size 2 --zero-stage 1", common="--moe-top-k 2"),
+    "cosine_dp4_tp2_sp_zero3": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3", common="--lr-schedule cosine --warmup-steps 1 --max-steps 6"),
+    "ckpt_every2_dp4_tp2_sp": C("llama", "--dp-size 4 --tp-size 2 --use-sp --activation-checkpointing --activation-checkpoint-every-n-layers 2"),
     "bf16_dp8": C("llama", "--dp-size 8 --precision bf16"),
     "bf16_dp8_zero1": C("llama", "--dp-size 8 --zero-stage 1 --precision bf16"),
     "bf16_dp8_zero3": C("llama", "--dp-size 8 --zero-stage 3 --precision bf16"),
@@ -122,6 +128,7 @@ RESUME = {   # case name -> micro-steps to run before the checkpoint (a multiple
     "olmo_dp4_tp2_sp_zero3_ckpt": 3, "dp4_bucket_tp2": 2, "dp2_pp2_tp2_sp_afab_zero3": 1,
     # bf16 with fp32 master weights: the masters, not the rounded model weights, must come back
     "bf16_dp4_tp2_sp_zero3": 1, "bf16_dp4_tp2_zero1_accum2": 3, "fp16_dp8_zero2": 1, "bf16_dp8": 1, "bf16_dp8_zero1": 1, "bf16_dp8_zero3": 1,
+    "cosine_dp4_tp2_sp_zero3": 1, "bf16_dp2_pp2_tp2_1f1b": 1, "moe_top2_dp8_ep4": 1,
 }
 
 
@@ -209,11 +216,11 @@ def _worker(rank, world, names):
     return results
 
 
-def _baseline(model: str, packed: bool):
+def _baseline(model: str, packed: bool, common: str = ""):
     """Single process, the whole global batch as one micro-batch."""
     from maltos_b200.train import cli
 
-    case = C(model, "--dp-size 1")
+    case = C(model, "--dp-size 1", common=common)
     a = _args(case)
     a.micro_batch_size = GLOBAL_ROWS
     torch.manual_seed(a.seed)
@@ -249,7 +256,7 @@ def matrix_results():
 
 @pytest.fixture(scope="module")
 def baselines():
-    return {(m, p): _baseline(m, p) for m in MODELS for p in (False, True) if any(c["model"] == m and c["packed"] == p for c in CASES.values())}
+    return {key: _baseline(*key) for key in sorted({(c["model"], c["packed"], c["common"]) for c in CASES.values()})}
 
 
 def test_case_list_is_wide_enough():
@@ -269,7 +276,7 @@ def test_case_matches_single_process_training(name, matrix_results, baselines):
     for status, payload, _ in per_rank:
         assert status == "ok", payload
     cp = per_rank[0][2]
-    ref = baselines[(case["model"], case["packed"])]
+    ref = baselines[(case["model"], case["packed"], case["common"])]
     for step in range(STEPS):
         # CP ranks report their share of the loss (shares add up), every other axis reports the value of its data shard
         got = sum(r[1][step] for r in per_rank) / (WORLD / cp)
