@@ -48,6 +48,12 @@ CASES = {
     "pp2_tp2_1f1b": ["--pp-size", "2", "--tp-size", "2", "--pp-schedule", "1f1b", "--pp-microbatches", "2", "--micro-batch-size", "4",
                      "--grad-accum-steps", "1"],
     "cp2_ring_tp2_sp": ["--cp-size", "2", "--cp-attn-core", "ring", "--tp-size", "2", "--use-sp", "--micro-batch-size", "4", "--grad-accum-steps", "1"],
+    # the loader itself hands every context-parallel rank its zigzag share (no sharding inside the runtime)
+    "cp2_ring_loader_sharded_tp2_sp": ["--cp-size", "2", "--cp-attn-core", "ring", "--cp-token-planner", "fixed_zigzag", "--batch-data-cp-aware",
+                                       "--tp-size", "2", "--use-sp", "--micro-batch-size", "4", "--grad-accum-steps", "1"],
+    "dp2_cp2_allgather_loader_sharded_prefetch": ["--dp-size", "2", "--cp-size", "2", "--cp-attn-core", "all_gather_kv", "--cp-token-planner",
+                                                  "fixed_contiguous", "--batch-data-cp-aware", "--data-prefetch-batches", "1", "--micro-batch-size", "2",
+                                                  "--grad-accum-steps", "1"],
     "dp2_pp2_zero1_accum": ["--dp-size", "2", "--pp-size", "2", "--zero-stage", "1", "--pp-microbatches", "1", "--micro-batch-size", "1",
                             "--grad-accum-steps", "2"],
 }
