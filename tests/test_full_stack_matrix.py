@@ -54,6 +54,9 @@ CASES = {
     "dp2_cp2_allgather_loader_sharded_prefetch": ["--dp-size", "2", "--cp-size", "2", "--cp-attn-core", "all_gather_kv", "--cp-token-planner",
                                                   "fixed_contiguous", "--batch-data-cp-aware", "--data-prefetch-batches", "1", "--micro-batch-size", "2",
                                                   "--grad-accum-steps", "1"],
+    # balanced hybrid data parallelism: all four ranks cut their waves from the same canonical batch of 4 rows
+    "dp4_hdp_balanced_zero1": ["--dp-size", "4", "--hdp-balanced", "--hdp-partition-tokens", "16", "--zero-stage", "1", "--micro-batch-size", "4",
+                               "--grad-accum-steps", "1"],
     "dp2_pp2_zero1_accum": ["--dp-size", "2", "--pp-size", "2", "--zero-stage", "1", "--pp-microbatches", "1", "--micro-batch-size", "1",
                             "--grad-accum-steps", "2"],
 }
