@@ -289,3 +289,47 @@ def test_context_parallel_local_loading_equals_runtime_sharding(tmp_path):
         assert torch.equal(covered, torch.arange(32))
     with pytest.raises(RuntimeError, match="cp_batch_sharder"):
         make().next_batch(1)
+
+
+def test_torch_profiler_plugin_follows_its_schedule_and_writes_one_trace_per_cycle(tmp_path):
+    from maltos_b200.runtime.plugins.torch_profiler import TorchProfilerPlugin
+
+    plugin = TorchProfilerPlugin(str(tmp_path / "traces"), wait=1, warmup=1, active=2, repeat=2)
+    rt = _runtime([plugin])
+    rt.setup()
+    for _ in range(9):                                   # two full cycles of 4 steps, then one more
+        rt.run_step(torch.randn(4, 32))
+        rt.step_optimizer()
+    rt.close()
+    names = sorted(p.name for p in (tmp_path / "traces" / "rank_00000").iterdir())
+    assert names == ["trace.json", "trace_1.json"]
+    events = json.loads((tmp_path / "traces" / "rank_00000" / "trace.json").read_text())["traceEvents"]
+    spans = {e.get("name") for e in events}
+    assert "maltos::forward" in spans and "maltos::backward" in spans
+    # the active window holds exactly two optimizer steps
+    assert sum(1 for e in events if e.get("name") == "maltos::micro_step_runner") == 2
+
+
+def test_compile_plugin_is_scope_bookkeeping_only():
+    """It validates the scope against the model's ``compile_spec()``, reports the covered modules and groups their parameters
+    for ZeRO-3 - and compiles nothing: the modules are the same objects afterwards."""
+    import maltos_b200.models as models
+    from maltos_b200.runtime.plugins.compile import CompilePlugin
+
+    torch.manual_seed(0)
+    model = models.TinyTransformer(32, 4, 2, 64, 1e-5, 2, 64, 16)
+    before = {n: id(m) for n, m in model.named_modules()}
+    plugin = CompilePlugin(scope="mlp")
+    rt = RuntimeCore(model=model, optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.1), plugins=[plugin])
+    rt.setup()
+    assert {n: id(m) for n, m in rt.model.named_modules()} == before
+    assert len(plugin.covered_paths) == 2 and all(p.endswith("mlp") for p in plugin.covered_paths)
+    groups = plugin.param_materialization_groups()
+    assert len(groups) == 2 and all(len(params) == 3 for _, params in groups)
+    assert rt.collect_metrics()["compile/fused_scopes"] == 2
+    rt.close()
+    with pytest.raises(ValueError, match="not offered"):
+        RuntimeCore(model=models.TinyTransformer(32, 4, 2, 64, 1e-5, 2, 64, 16), optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.1),
+                    plugins=[CompilePlugin(scope="attention_block_that_does_not_exist")]).setup()
+    with pytest.raises(ValueError, match="compile_spec"):
+        RuntimeCore(model=TinyModel(), optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.1), plugins=[CompilePlugin()]).setup()
