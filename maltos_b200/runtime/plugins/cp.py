@@ -31,7 +31,9 @@ _ZERO = (PluginId.ZERO1, PluginId.ZERO2, PluginId.ZERO3)
 
 class ContextParallelPlugin(RuntimePlugin):
     def __init__(self) -> None:
-        super().__init__(id=PluginId.CP, name="context_parallel", runs_after={PluginId.PP, PluginId.TP, PluginId.TP_SP})
+        # after the data-parallel plugins: their reductions of the same gradient tensors (blocking or bucketed) are complete
+        # when this plugin adds the sum over the context-parallel group - two collectives in flight on one tensor would race
+        super().__init__(id=PluginId.CP, name="context_parallel", runs_after={PluginId.PP, PluginId.TP, PluginId.TP_SP, PluginId.DP, PluginId.EP})
         self._sharder: ContextParallelBatchSharder | None = None
         self._pending: list = []
 
@@ -101,7 +103,8 @@ class ContextParallelPlugin(RuntimePlugin):
                     w = all_reduce_tensor(p.grad, op=dist.ReduceOp.SUM, group=self.cp_group, async_op=True)
                     if w is not None:
                         self._pending.append(w)
-        elif phase is RuntimePhase.PRE_STEP:
-            for w in self._pending:
-                w.wait()
-            self._pending.clear()
+                # all of them are in flight together, and all are finished before any later plugin (sequence-parallel partial
+                # gradients at PRE_STEP, clipping) reads or reduces the same tensors
+                for w in self._pending:
+                    w.wait()
+                self._pending.clear()

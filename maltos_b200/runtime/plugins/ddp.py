@@ -185,11 +185,15 @@ class BucketDataParallelPlugin(_DdpBase):
         bucket.work = all_reduce_tensor(bucket.buffer, op=dist.ReduceOp.AVG, group=self.dp_group, async_op=True)
         bucket.fired = True
 
-    def _reattach(self, bucket: _GradBucket) -> None:
-        # optimizer.zero_grad(set_to_none=True) dropped the views: point .grad back into the flat buffer
+    def _reattach(self, bucket: _GradBucket, *, keep_values: bool = False) -> None:
+        # optimizer.zero_grad(set_to_none=True) dropped the views: point .grad back into the flat buffer. A gradient that
+        # lives elsewhere inside an accumulation window (restored from a checkpoint) is moved into the buffer first.
         for p, at in zip(bucket.params, bucket.offsets):
             if p.grad is None or p.grad.data_ptr() != bucket.buffer.data_ptr() + at * bucket.buffer.element_size():
-                p.grad = bucket.buffer[at:at + p.numel()].view_as(p)
+                view = bucket.buffer[at:at + p.numel()].view_as(p)
+                if keep_values and p.grad is not None:
+                    view.copy_(p.grad)
+                p.grad = view
 
     def on_step_phase(self, phase: RuntimePhase) -> None:
         if self.dp_group is None:
@@ -199,7 +203,7 @@ class BucketDataParallelPlugin(_DdpBase):
             for b in self.buckets:
                 if ctx.accum_start:
                     b.buffer.zero_()
-                self._reattach(b)
+                self._reattach(b, keep_values=not ctx.accum_start)
                 b.pending = rearm_bucket_pending(len(b.params), grad_accum_end=ctx.is_step_boundary)
                 b.fired = False
         elif phase is RuntimePhase.POST_BACKWARD and ctx.is_step_boundary:

@@ -355,6 +355,22 @@ class Zero1Plugin(ZeroPluginBase):
                 for g in self._peer_groups():
                     self._barrier(g)    # all peers' stores have landed before the next forward reads the parameters
 
+    # ------------------------------------------------------------------ checkpoint inside an accumulation window
+    def export_plugin_state(self):
+        """The flat gradient buffers hold the micro-steps done so far when a checkpoint is taken inside an accumulation
+        window; at a step boundary there is nothing to keep."""
+        if self.runtime.state.step_context.microbatch_idx == 0:
+            return {}
+        return {"bucket_grads": [None if b.grad is None else b.grad.detach().to("cpu").clone() for b in self.buckets]}
+
+    def import_plugin_state(self, state) -> None:
+        grads = state.get("bucket_grads")
+        if not isinstance(grads, list):
+            return
+        for b, g in zip(self.buckets, grads):
+            if g is not None and b.grad is not None:
+                b.grad.copy_(g.to(device=b.grad.device, dtype=b.grad.dtype))
+
     def _resync_from_buffers(self, *, sync_masters: bool = True) -> None:
         with torch.no_grad():
             for b in self.buckets:

@@ -66,6 +66,11 @@ class OptimizerState:
     state: dict[str, Any]
 
 
+#: key of the runtime's own entry among the plugin states of ``trainer_rank_N.pt`` (plugin ids are the other keys; a loader that
+#: does not know a key skips it)
+_RUNTIME_STATE_KEY = "runtime"
+
+
 def _meta_for(name: str, tensor: torch.Tensor) -> ModelStateMeta:
     shape = tuple(tensor.shape)
     return ModelStateMeta(state_key=name, logical_names=[name], logical_shapes=[shape], physical_shape=shape,
@@ -206,6 +211,9 @@ class StateManager:
             exported = plugin.export_plugin_state()
             if exported:
                 plugin_states[plugin.id.value] = exported
+        partial = self._partial_gradients()
+        if partial:
+            plugin_states[_RUNTIME_STATE_KEY] = {"partial_grads": partial}
         return TrainerState(rng=rng, step_context=asdict(rt.state.step_context),
                             dataloader=self._dataloader_state(), plugin_states=plugin_states or None)
 
@@ -222,6 +230,22 @@ class StateManager:
                 saved = state.plugin_states.get(plugin.id.value)
                 if isinstance(saved, dict):
                     plugin.import_plugin_state(saved)
+            own = state.plugin_states.get(_RUNTIME_STATE_KEY)
+            if isinstance(own, dict) and isinstance(own.get("partial_grads"), dict):
+                for name, grad in own["partial_grads"].items():
+                    entry = self.params.get(name)
+                    if entry is not None and torch.is_tensor(grad):
+                        entry.param.grad = grad.to(device=entry.param.device, dtype=entry.param.dtype).reshape(entry.param.shape).clone()
+
+    def _partial_gradients(self) -> dict[str, torch.Tensor]:
+        """Gradients accumulated so far when a checkpoint is taken INSIDE an accumulation window and the runtime itself owns
+        the optimizer (the sharded-optimizer plugins keep and save their own partial gradients). Without them the resumed
+        window would be missing the micro-steps done before the save."""
+        rt = self.runtime
+        if rt.state.step_context.microbatch_idx == 0 or getattr(rt, "_optimizer_owner", rt) is not rt:
+            return {}
+        return {name: e.param.grad.detach().to("cpu").clone() for name, e in self.params.items()
+                if e.param.requires_grad and e.param.grad is not None}
 
     def _dataloader_state(self) -> dict[str, Any] | None:
         if self._dataloader is None:
