@@ -229,25 +229,33 @@ def _worker(rank, world, names):
 
 
 def _replica_spread(core) -> float:
-    """Largest difference between the copies of a shared parameter held by the ranks that replicate it (the data x context
-    parallel group). Must be exactly zero: every replica applies the same update to the same reduced gradient - a nonzero
-    value means two gradient reductions raced or one was skipped."""
+    """Largest difference between the copies of a parameter held by the ranks that replicate it, over every mesh axis the
+    checkpoint metadata declares it replicated on (data / context parallel ranks; tensor parallel ranks for norms and
+    other unsharded weights). Must be exactly zero: every replica applies the same update to the same reduced gradient - a
+    nonzero value means two gradient reductions raced or one was skipped."""
     import torch.distributed as dist
 
     from maltos_b200.runtime.mesh import MeshAxis
     from maltos_b200.runtime.types import ParamRole
 
-    group = core.get_group(MeshAxis.DCP)
-    if group is None or dist.get_world_size(group) <= 1:
-        return 0.0
     worst = 0.0
-    for p in core.model.parameters():
+    for name, entry in core.state_manager.params.items():
+        p = entry.param
         if core.get_param_role(p) == ParamRole.EXPERT or p.untyped_storage().size() == 0:
             continue        # expert copies differ by design; ZeRO-3 parameters are not materialised between steps
-        lo, hi = p.detach().float().clone(), p.detach().float().clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
-        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
-        worst = max(worst, float((hi - lo).abs().max()))
+        axes = set(entry.attrs.replicated_axes)
+        if axes & {MeshAxis.DP, MeshAxis.CP, MeshAxis.DCP}:
+            axes = (axes - {MeshAxis.DP, MeshAxis.CP}) | {MeshAxis.DCP}
+        for axis in sorted(axes, key=lambda a: a.value):
+            if axis not in (MeshAxis.DCP, MeshAxis.TP):
+                continue
+            group = core.get_group(axis)
+            if group is None or dist.get_world_size(group) <= 1:
+                continue
+            lo, hi = p.detach().float().clone(), p.detach().float().clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+            worst = max(worst, float((hi - lo).abs().max()))
     return worst
 
 
