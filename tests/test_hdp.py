@@ -159,6 +159,15 @@ def _hdp_worker(rank, world, partition_tokens=16):
         losses.append(float(loss))
     metrics = rt.collect_metrics()
     params = {n: p.detach().clone() for n, p in rt.model.named_parameters()}
+    import torch.distributed as dist
+
+    spread = 0.0                      # every rank holds a replica: they must stay bit-identical
+    for p in rt.model.parameters():
+        lo, hi = p.detach().clone(), p.detach().clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        spread = max(spread, float((hi - lo).abs().max()))
+    assert spread == 0.0, spread
     rt.close()
     return losses, params, {k: v for k, v in metrics.items() if "wave" in k}, plans
 
