@@ -69,7 +69,7 @@ def test_axis_combination_matches_single_process(name, data, reference):
         # every CP rank reports its SHARE of the loss (local mean x local / global targets) and the logged value is the
         # mean over ranks, i.e. the global loss divided by the CP degree - the reference logs the same quantity
         got = [v * int(CASES[name][CASES[name].index("--cp-size") + 1]) for v in got]
-    # first step: same parameters, only the summation order differs; later steps also see the order of the gradient
-    # reductions (gloo's order is not fixed from run to run), amplified by Adam's normalisation
-    assert abs(got[0] - reference[0]) < 5e-4, (name, got, reference)
-    assert max(abs(a - b) for a, b in zip(got, reference)) < 3e-3, (name, got, reference)
+    # first step: same parameters, only the summation order differs from the single process; later steps also see the
+    # order of the gradient reductions, amplified by Adam's normalisation (runs are bit-reproducible from run to run)
+    assert abs(got[0] - reference[0]) < 1e-4, (name, got, reference)
+    assert max(abs(a - b) for a, b in zip(got, reference)) < 1e-3, (name, got, reference)
