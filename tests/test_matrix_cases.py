@@ -324,9 +324,9 @@ def test_case_matches_single_process_training(name, matrix_results, baselines):
     for step in range(STEPS):
         # CP ranks report their share of the loss (shares add up), every other axis reports the value of its data shard
         got = sum(r[1][step] for r in per_rank) / (WORLD / cp)
-        tol = 2e-4 if step == 0 else 2e-3
+        tol = 2e-5                       # fp32: only the order of summation differs from the single process
         if "--precision" in case["flags"]:
-            tol = 5e-3
+            tol = 2e-3                   # bf16 / fp16 compute against the fp32 baseline
         assert abs(got - ref[step]) < tol, (name, step, got, ref[step])
 
 
