@@ -118,6 +118,17 @@ CASES = {
     "olmo_dp2_pp2_cp2_allgather_zero1": C("olmo", "--dp-size 2 --pp-size 2 --cp-size 2 --cp-attn-core all_gather_kv --zero-stage 1", pp_mb=2),
     "packed_dp2_pp2_tp2_sp_1f1b_zero3": C("llama", "--dp-size 2 --pp-size 2 --tp-size 2 --use-sp --pp-schedule 1f1b --zero-stage 3", packed=True, pp_mb=2),
     "packed_moe_dp4_tp2_ep4_zero2": C("moe", "--dp-size 4 --tp-size 2 --ep-size 4 --zero-stage 2", packed=True),
+    "dp2_tp4_sp_zero1_accum2": C("llama", "--dp-size 2 --tp-size 4 --use-sp --zero-stage 1", accum=2),
+    "pp4_tp2_sp_1f1b": C("llama", "--pp-size 4 --tp-size 2 --use-sp --pp-schedule 1f1b", pp_mb=4),
+    "pp4_dp2_afab_zero2": C("llama", "--pp-size 4 --dp-size 2 --pp-schedule afab --zero-stage 2", pp_mb=2),
+    "cp8_ring": C("llama", "--cp-size 8 --cp-attn-core ring --cp-token-planner fixed_zigzag"),
+    "cp8_allgather_packed": C("llama", "--cp-size 8 --cp-attn-core all_gather_kv", packed=True),
+    "packed_dp2_cp2_pp2_allgather_zero2": C("llama", "--dp-size 2 --cp-size 2 --pp-size 2 --cp-attn-core all_gather_kv --zero-stage 2 --pp-schedule 1f1b",
+                                            packed=True, pp_mb=2),
+    "moe_dp8_ep8_zero1": C("moe", "--dp-size 8 --ep-size 8 --zero-stage 1"),
+    "olmo_pp2_cp2_tp2_ring_afab": C("olmo", "--pp-size 2 --cp-size 2 --tp-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --pp-schedule afab", pp_mb=4),
+    "dp8_async_ckpt": C("llama", "--dp-size 8 --ddp-mode async --activation-checkpointing"),
+    "tiny_dp2_cp2_tp2_sp_ring_zero2": C("tiny", "--dp-size 2 --cp-size 2 --tp-size 2 --use-sp --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 2"),
     # ---- choices that change the mathematics: the baseline gets them too
     "moe_top2_dp8_ep4": C("moe", "--dp-size 8 --ep-size 4", common="--moe-top-k 2"),
     "moe_top2_dp4_tp2_ep2_zero1": C("moe", "--dp-size 4 --tp-size 2 --ep-size 2 --zero-stage 1", common="--moe-top-k 2"),
