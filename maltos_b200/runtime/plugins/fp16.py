@@ -1,6 +1,7 @@
-"""fp16 loss scaling: active only when the runtime dtype is float16 on CUDA. Scales the loss at PRE_BACKWARD through a
-``torch.amp.GradScaler`` kept in ``runtime.state.scaler`` (the core steps through it), checkpoints the scaler state
-(reference ``runtime/plugins/fp16.py:10-74``)."""
+"""fp16 loss scaling: active when the runtime dtype is float16 on CUDA (on CPU only when asked for, which the tests do).
+Scales the loss at PRE_BACKWARD through a gradient scaler kept in ``runtime.state.scaler`` (the core steps through it) and
+checkpoints the scaler state (reference ``runtime/plugins/fp16.py:10-74``). The scaler is the distributed one: an overflow
+on any rank skips the step on every rank (``utils/amp.py``)."""
 from __future__ import annotations
 
 import torch
@@ -10,20 +11,24 @@ from maltos_b200.runtime.types import RuntimePhase, SetupPhase
 
 
 class Fp16Plugin(RuntimePlugin):
-    def __init__(self, init_scale: float = 2.0 ** 16, growth_interval: int = 2000) -> None:
+    def __init__(self, init_scale: float = 2.0 ** 16, growth_interval: int = 2000, *, allow_cpu: bool = False) -> None:
         super().__init__(id=PluginId.FP16, name="fp16")
         self.init_scale = init_scale
         self.growth_interval = growth_interval
+        self.allow_cpu = allow_cpu
         self.scaler = None
 
     @property
     def active(self) -> bool:
         rt = self.runtime
-        return rt is not None and rt.dtype == torch.float16 and torch.device(rt.device).type == "cuda"
+        return rt is not None and rt.dtype == torch.float16 and (torch.device(rt.device).type == "cuda" or self.allow_cpu)
 
     def on_setup_phase(self, phase: SetupPhase, model):
         if phase is SetupPhase.FINALIZE and self.active:
-            self.scaler = torch.amp.GradScaler("cuda", init_scale=self.init_scale, growth_interval=self.growth_interval)
+            from maltos_b200.utils.amp import DistributedGradScaler
+
+            self.scaler = DistributedGradScaler(torch.device(self.runtime.device).type, init_scale=self.init_scale,
+                                                growth_interval=self.growth_interval)
             self.runtime.state.scaler = self.scaler
         return model
 

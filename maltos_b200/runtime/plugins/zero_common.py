@@ -212,6 +212,14 @@ class ZeroPluginBase(RuntimePlugin):
         for b in self.buckets:
             local_sq.add_(self._bucket_local_sq(b))
         norm = float(global_grad_norm(local_sq).item())
+        scaler = rt.state.scaler
+        if scaler is not None:
+            # fp16: the shards still carry the loss scale (the scaler divides it out inside its step), and an overflow is an
+            # ordinary event - the scaler skips the step on every rank and backs the scale off; nothing to clip then
+            if not math.isfinite(norm):
+                rt.state.metadata["grad_norm"] = norm
+                return
+            norm /= float(scaler.get_scale())
         if not math.isfinite(norm):
             bad = []
             for b in self.buckets:
