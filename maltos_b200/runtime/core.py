@@ -225,11 +225,14 @@ class RuntimeCore:
             batch = _to_device(batch, torch.device(self.device))
         st = self.state
         st.batch = batch
-        ntok = _token_count(batch)
-        if ntok is not None:
-            st.metadata["tokens"] = ntok
+        # tokens of the whole accumulation window (the reference reports the last micro-step only, which under-reports the
+        # throughput by the accumulation factor); a plugin may correct the micro-step's count in PRE_STEP_RUNNER
+        st.metadata["tokens_micro"] = _token_count(batch)
         ctx = st.step_context
         self._run_step_phase(RuntimePhase.PRE_STEP_RUNNER)
+        ntok = st.metadata.pop("tokens_micro", None)
+        if ntok is not None:
+            st.metadata["tokens"] = ntok + (st.metadata.get("tokens") or 0 if ctx.microbatch_idx != 0 else 0)
         with span("maltos::micro_step_runner"):
             loss = self._step_runner.run(self, st.batch)
         self._accumulate_loss_metric()
@@ -389,6 +392,11 @@ class RuntimeCore:
             out["loss"] = float((total / count).item())  # the only host read of the loss per optimizer step
         elif self.state.loss is not None:
             out["loss"] = float(self.state.loss.detach().float().item())
+        if "loss" in out and self.mesh.cp > 1 and self.has_plugin(PluginId.CP):
+            # every context-parallel rank differentiates its SHARE of the loss (local mean x local / global targets); the
+            # logged value is averaged over all ranks, so report cp x share: the average is then the loss of the whole rows
+            # (the reference logs the share, i.e. loss / cp)
+            out["loss"] *= float(self.mesh.cp)
         model_metrics = md.get("model_metrics")
         if model_metrics is not None:
             if not isinstance(model_metrics, dict):

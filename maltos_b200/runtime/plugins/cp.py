@@ -93,6 +93,9 @@ class ContextParallelPlugin(RuntimePlugin):
         if phase is RuntimePhase.PRE_STEP_RUNNER:
             if not rt.plan.batch_data_cp_aware:
                 rt.state.batch = self._sharder.shard(rt.state.batch, rank=dist.get_rank(self.cp_group))
+            elif isinstance(rt.state.metadata.get("tokens_micro"), int):
+                # the loader handed over this rank's share only: count the whole rows, as in the other arrangement
+                rt.state.metadata["tokens_micro"] *= rt.mesh.cp
         elif phase is RuntimePhase.POST_BACKWARD:
             if self._needs_own_grad_sync() and rt.state.step_context.is_step_boundary:
                 for p in rt.model.parameters():

@@ -133,7 +133,7 @@ class ByteScaleHdpPlugin(RuntimePlugin):
                 if s.partition_tokens != self.config.partition_tokens:
                     raise ValueError(f"ByteScale dataloader/plugin partition_tokens mismatch: loader={s.partition_tokens} "
                                      f"plugin={self.config.partition_tokens}")
-            state.metadata["tokens"] = schedules[0].global_valid_targets
+            state.metadata["tokens_micro"] = schedules[0].global_valid_targets
             self._metrics = _wave_metrics(schedules)
         elif phase is RuntimePhase.PRE_FORWARD:
             schedule = _schedule_from_batch(state.batch)

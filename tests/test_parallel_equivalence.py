@@ -140,8 +140,9 @@ def test_matches_single_process(kind, mode, mesh_kw, clip):
     results = run_distributed(_worker, world, kind, mode, mesh_kw, clip)
     # the reported loss is the mean over the accumulation window of this rank's micro-batches; PP/CP ranks see the global one
     if mesh_kw.get("cp", 1) > 1:
-        # every CP rank reports its share (local mean x local/global targets); the shares add up to the global loss
-        total = [sum(r[0][i] for r in results) for i in range(STEPS)]
+        # every CP rank differentiates its share (local mean x local/global targets) and reports cp x share, so that the mean
+        # over the ranks is the loss of the whole rows
+        total = [sum(r[0][i] for r in results) / len(results) for i in range(STEPS)]
         assert max(abs(a - b) for a, b in zip(total, ref_losses)) < 2e-4, (total, ref_losses)
     elif n_shards == 1:
         for losses, _ in results:
