@@ -69,3 +69,19 @@ def test_axis_combination_matches_single_process(name, data, reference):
     # order of the gradient reductions, amplified by Adam's normalisation (runs are bit-reproducible from run to run)
     assert abs(got[0] - reference[0]) < 1e-4, (name, got, reference)
     assert max(abs(a - b) for a, b in zip(got, reference)) < 1e-3, (name, got, reference)
+
+
+@pytest.mark.parametrize("loader_sharded", [False, True])
+def test_logged_tokens_cover_the_accumulation_window_once(loader_sharded, data, tmp_path):
+    """dp2 x cp2, two micro-batches of 2 rows x 32 tokens per optimizer step: 2 (dp) x 2 (accum) x 2 x 32 = 256 tokens, however
+    the rows reach the context-parallel ranks; and the logged loss is the loss of the whole rows, not a rank's share."""
+    import json
+
+    out = tmp_path / "metrics.jsonl"
+    flags = ["--dp-size", "2", "--cp-size", "2", "--cp-attn-core", "ring", "--cp-token-planner", "fixed_zigzag", "--micro-batch-size", "2",
+             "--grad-accum-steps", "2", "--metrics-jsonl", str(out)] + (["--batch-data-cp-aware"] if loader_sharded else [])
+    losses = _losses(data, flags, 4)
+    rows = [json.loads(l) for l in out.read_text().splitlines()]
+    assert [r["train/tokens"] for r in rows] == [256.0, 256.0, 256.0]
+    single = _losses(data, ["--micro-batch-size", "8", "--grad-accum-steps", "1"], 1)
+    assert abs(losses[0] - single[0]) < 1e-4, (losses, single)
