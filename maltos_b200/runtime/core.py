@@ -289,12 +289,16 @@ class RuntimeCore:
     def get_param_role(self, param: nn.Parameter) -> ParamRole:
         return self._param_roles.get(id(param), ParamRole.SHARED)
 
-    def grad_norm_replica_factor(self, param: nn.Parameter) -> int:
-        """How many ranks hold an identical copy of this parameter's gradient (its square is counted once)."""
+    def grad_norm_replica_factor(self, param: nn.Parameter, *, sharded_over: frozenset = frozenset()) -> int:
+        """How many ranks hold an identical copy of this parameter's gradient (its square is counted once).
+        ``sharded_over``: mesh axes over which the CALLER holds different pieces of the gradient (a sharded optimizer's
+        shard group); replication along them does not apply to a shard."""
         name = self.state_manager.get_param_name(param)
         sizes = {MeshAxis.DP: self.mesh.dp, MeshAxis.TP: self.mesh.tp, MeshAxis.PP: self.mesh.pp, MeshAxis.CP: self.mesh.cp}
         factor = 1
         for axis in self.state_manager.params[name].attrs.replicated_axes:
+            if axis in sharded_over:
+                continue
             if axis in sizes:
                 factor *= sizes[axis]
             else:

@@ -26,7 +26,7 @@ from maltos_b200.runtime.types import ParamRole, RuntimePhase, SetupPhase
 from maltos_b200.utils.distributed import all_reduce_tensor
 
 from .tp import set_submodule
-from .zero_common import (ChainedWork, CompletedWork, build_param_buckets, expert_data_shards, expert_erep_correction,
+from .zero_common import (ChainedWork, CompletedWork, build_param_buckets, expert_data_shards, expert_erep_correction, expert_token_copies,
                           rearm_bucket_pending)
 
 _ZERO = {PluginId.ZERO1, PluginId.ZERO2, PluginId.ZERO3}
@@ -128,7 +128,7 @@ class ExpertParallelPlugin(RuntimePlugin):
         def functor():
             mesh, plan = self.runtime.mesh, self.runtime.plan
             kw = dict(tp=mesh.tp, cp=mesh.cp, ep=mesh.ep, reuse_tp=plan.reuse_tp_for_ep, reuse_cp=plan.reuse_cp_for_ep)
-            shards = expert_data_shards(**kw)
+            shards = expert_data_shards(**kw) * expert_token_copies(self.runtime)
             if group is None or dist.get_world_size(group) <= 1:
                 if shards != 1:
                     bucket.grad_buffer.div_(shards)

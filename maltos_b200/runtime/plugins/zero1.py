@@ -257,7 +257,7 @@ class Zero1Plugin(ZeroPluginBase):
         b.direct = not has_links and lp.grad.dtype == b.grad.dtype and lp.grad.is_contiguous() and lp.grad.numel() == b.shard_numel
         accumulate = b.direct and existed and self.accumulate_on_shard
         out = lp.grad if b.direct else dst
-        plain_norm = all(float(self.runtime.grad_norm_replica_factor(p)) == 1.0 for p in b.params)
+        plain_norm = all(float(self._shard_replica_factor(p)) == 1.0 for p in b.params)
         if b.direct and plain_norm:
             b.fused_sq = torch.zeros((), dtype=torch.float64, device=dst.device) if b.fused_sq is None else b.fused_sq.zero_()
         else:
@@ -391,7 +391,7 @@ class Zero1Plugin(ZeroPluginBase):
         for p, at in zip(b.params, b.offsets):
             s, e = max(at, lo), min(at + p.numel(), hi)
             if s < e:
-                out.add_(g[s - lo:e - lo].detach().double().pow(2).sum() / float(self.runtime.grad_norm_replica_factor(p)))
+                out.add_(g[s - lo:e - lo].detach().double().pow(2).sum() / float(self._shard_replica_factor(p)))
         return out
 
 

@@ -445,7 +445,7 @@ class Zero3Plugin(ZeroPluginBase):
         entry = self.runtime.state_manager.params.get(name)
         if entry is None:
             return 1
-        return self.runtime.grad_norm_replica_factor(entry.param)
+        return self._shard_replica_factor(entry.param)
 
     # ------------------------------------------------------------------ metadata & model state
     def annotate_param_metadata(self) -> None:

@@ -90,6 +90,18 @@ def expert_data_shards(*, tp: int, cp: int, ep: int, reuse_tp: bool, reuse_cp: b
     return max(ep // inner, 1) if ep > inner else 1
 
 
+def expert_token_copies(runtime) -> int:
+    """How many times one token reaches an expert through the EP all-to-all. With tensor parallelism WITHOUT sequence
+    parallelism the activations in front of the MoE layer are replicated over the TP ranks; when the expert group reuses those
+    ranks, every one of them dispatches the same tokens, the expert sees each token ``tp`` times and its gradient comes out
+    ``tp`` times too large (AdamW hides the factor, clipping and the reported norm do not). Expert gradients are divided by
+    this number."""
+    mesh, plan = runtime.mesh, runtime.plan
+    if mesh.tp > 1 and mesh.ep > 1 and plan.reuse_tp_for_ep and runtime.has_plugin(PluginId.TP) and not runtime.has_plugin(PluginId.TP_SP):
+        return mesh.tp
+    return 1
+
+
 def rearm_bucket_pending(num_params: int, *, grad_accum_end: bool) -> int:
     """Pending-hook count for a bucket at the start of a backward: only the window-closing micro-step may reach 0."""
     return num_params if grad_accum_end else 0
@@ -169,11 +181,12 @@ class ZeroPluginBase(RuntimePlugin):
         mesh = rt.mesh
         if role == ParamRole.EXPERT:
             group = rt.get_group(MeshAxis.EREP)
+            copies = expert_token_copies(rt)
             if group is None:
                 shards = expert_data_shards(tp=mesh.tp, cp=mesh.cp, ep=mesh.ep, reuse_tp=rt.plan.reuse_tp_for_ep, reuse_cp=rt.plan.reuse_cp_for_ep)
-                return GroupContext(None, 1, 0, correction=1.0 / shards)
+                return GroupContext(None, 1, 0, correction=1.0 / (shards * copies))
             corr = expert_erep_correction(tp=mesh.tp, cp=mesh.cp, ep=mesh.ep, reuse_tp=rt.plan.reuse_tp_for_ep, reuse_cp=rt.plan.reuse_cp_for_ep)
-            corr /= expert_data_shards(tp=mesh.tp, cp=mesh.cp, ep=mesh.ep, reuse_tp=rt.plan.reuse_tp_for_ep, reuse_cp=rt.plan.reuse_cp_for_ep)
+            corr /= expert_data_shards(tp=mesh.tp, cp=mesh.cp, ep=mesh.ep, reuse_tp=rt.plan.reuse_tp_for_ep, reuse_cp=rt.plan.reuse_cp_for_ep) * copies
             return GroupContext(group, dist.get_world_size(group), dist.get_rank(group), correction=corr)
         group = rt.get_group(MeshAxis.DCP)
         if group is None:
@@ -197,6 +210,18 @@ class ZeroPluginBase(RuntimePlugin):
         return build_param_buckets(params, self.bucket_byte_size)
 
     # ---- clipping on local shards
+    def _shard_replica_factor(self, param: nn.Parameter) -> int:
+        """Replication of a SHARD of ``param``'s gradient: the ranks of the shard group (data x context parallel ranks for
+        shared parameters, the expert replicas for expert parameters) hold different pieces, so replication along those axes
+        does not count - only copies on other axes (unsharded weights under tensor parallelism) do. Counting the shard-group
+        axes as well (the reference does) under-reports the global norm by sqrt(cp) or sqrt(expert replicas)."""
+        rt = self.runtime
+        if rt.get_param_role(param) == ParamRole.EXPERT:
+            over = frozenset({MeshAxis.EREP, MeshAxis.DP, MeshAxis.CP, MeshAxis.DCP})
+        else:
+            over = frozenset({MeshAxis.DP, MeshAxis.CP, MeshAxis.DCP})
+        return rt.grad_norm_replica_factor(param, sharded_over=over)
+
     def _bucket_local_sq(self, bucket) -> torch.Tensor:
         raise NotImplementedError
 

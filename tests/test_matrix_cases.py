@@ -28,7 +28,7 @@ MODELS = {
     "moe": ["--model", "tiny_moe", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "96", "--n-layers", "2", "--num-experts", "8",
             "--moe-aux-loss-coef", "0"],
 }
-COMMON = ["--vocab-size", str(VOCAB), "--seq-len", str(SEQ), "--lr", "1e-3", "--weight-decay", "0.01", "--grad-clip", "1.0", "--seed", "5",
+COMMON = ["--vocab-size", str(VOCAB), "--seq-len", str(SEQ), "--lr", "1e-3", "--weight-decay", "0.01", "--grad-clip", "0.1", "--seed", "5",
           "--precision", "fp32", "--disable-metrics"]
 
 
@@ -218,16 +218,18 @@ def _worker(rank, world, names):
             core.model.train()
             dp_group = core.get_group(MeshAxis.DP)
             dp_rank = dist.get_rank(dp_group) if dp_group is not None else 0
-            losses = []
+            losses, norms = [], []
             for step in range(STEPS):
                 for m in range(case["accum"]):
                     loss, should = core.run_step(_micro_batch(_global_batches(case["packed"])[step], dp_rank, a.dp_size, case["accum"], m))
                 assert should
                 core.step_optimizer()
-                losses.append(float(core.collect_metrics()["loss"]))      # mean over the accumulation window
+                metrics = core.collect_metrics()
+                losses.append(float(metrics["loss"]))      # mean over the accumulation window
+                norms.append(next((float(v) for k, v in metrics.items() if k.endswith("/grad_norm")), None))
             spread = _replica_spread(core)
             core.close()
-            results[name] = ("ok", losses, a.cp_size, spread)
+            results[name] = ("ok", losses, a.cp_size, spread, norms)
         except Exception as exc:  # noqa: BLE001 - one broken case must not hide the others
             import traceback
 
@@ -281,13 +283,14 @@ def _baseline(model: str, packed: bool, common: str = ""):
     core = cli._build_runtime(a, cli._build_model(a), torch.device("cpu"))
     core.setup()
     core.model.train()
-    losses = []
+    losses, norms = [], []
     for step in range(STEPS):
         loss, _ = core.run_step({k: v.clone() for k, v in _global_batches(packed)[step].items()})
         core.step_optimizer()
         losses.append(float(loss.detach()))
+        norms.append(next((float(v) for k, v in core.collect_metrics().items() if k.endswith("/grad_norm")), None))
     core.close()
-    return losses
+    return losses, norms
 
 
 CHUNK = 10   # cases per group of worker processes: a case that fails takes only its own chunk down
@@ -331,8 +334,13 @@ def test_case_matches_single_process_training(name, matrix_results, baselines):
         assert status == "ok", payload
     assert max(r[3] for r in per_rank) == 0.0, (name, "replicas of shared parameters drifted apart", [r[3] for r in per_rank])
     cp = per_rank[0][2]
-    ref = baselines[(case["model"], case["packed"], case["common"])]
+    ref, ref_norms = baselines[(case["model"], case["packed"], case["common"])]
     for step in range(STEPS):
+        # the clipped norm is the norm of the GLOBAL gradient: every rank must report the single-process value (AdamW hides a
+        # wrong clip coefficient from the loss, so the norm is checked directly)
+        for r in per_rank:
+            if r[4][step] is not None and "--precision" not in case["flags"]:
+                assert abs(r[4][step] - ref_norms[step]) < 2e-5 * max(1.0, ref_norms[step]), (name, step, r[4][step], ref_norms[step])
         # every rank reports the loss of its data shard (context-parallel ranks: cp x their share), so the plain mean is global
         got = sum(r[1][step] for r in per_rank) / WORLD
         tol = 2e-5                       # fp32: only the order of summation differs from the single process
