@@ -99,10 +99,12 @@ class ContextParallelPlugin(RuntimePlugin):
         elif phase is RuntimePhase.POST_BACKWARD:
             if self._needs_own_grad_sync() and rt.state.step_context.is_step_boundary:
                 for p in rt.model.parameters():
-                    if p.grad is None or not p.requires_grad:
+                    if not p.requires_grad:
                         continue
                     if rt.get_param_role(p) == ParamRole.EXPERT and rt.plan.reuse_cp_for_ep:
                         continue
+                    if p.grad is None:      # unused here, maybe used on another rank: same collectives everywhere
+                        p.grad = torch.zeros_like(p)
                     w = all_reduce_tensor(p.grad, op=dist.ReduceOp.SUM, group=self.cp_group, async_op=True)
                     if w is not None:
                         self._pending.append(w)

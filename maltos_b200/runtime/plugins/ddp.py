@@ -65,7 +65,9 @@ class DataParallelPlugin(_DdpBase):
         works = []
         for p in self._shared_params(self.runtime.model):
             if p.grad is None:
-                continue
+                # a parameter this rank did not use in the window (an expert without tokens) may have been used elsewhere: every
+                # rank must issue the same collectives, so it contributes zeros (what the flat-buffer modes do anyway)
+                p.grad = torch.zeros_like(p)
             w = all_reduce_tensor(p.grad, op=dist.ReduceOp.AVG, group=self.dp_group, async_op=self.async_op)
             if w is not None:
                 works.append(w)

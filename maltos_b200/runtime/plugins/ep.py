@@ -174,7 +174,9 @@ class ExpertParallelPlugin(RuntimePlugin):
             return
         works = []
         for p in rt.model.parameters():
-            if p.requires_grad and p.grad is not None and id(p) not in self._expert_param_ids:
+            if p.requires_grad and id(p) not in self._expert_param_ids:
+                if p.grad is None:      # unused here, maybe used on another rank: same collectives everywhere
+                    p.grad = torch.zeros_like(p)
                 w = all_reduce_tensor(p.grad, op=dist.ReduceOp.AVG, group=self.dp_group, async_op=True)
                 if w is not None:
                     works.append(w)

@@ -197,8 +197,9 @@ class TpSpPlugin(TensorParallelTransformPlugin):
             return
         works = []
         for p in self._partial_params:
-            if p.grad is not None:
-                works.append(all_reduce_tensor(p.grad, op=dist.ReduceOp.SUM, group=self.sp_group, async_op=True))
+            if p.grad is None:          # unused here, maybe used on another rank: same collectives everywhere
+                p.grad = torch.zeros_like(p)
+            works.append(all_reduce_tensor(p.grad, op=dist.ReduceOp.SUM, group=self.sp_group, async_op=True))
         for w in works:
             if w is not None:
                 w.wait()

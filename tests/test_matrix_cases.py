@@ -134,6 +134,13 @@ CASES = {
     "moe_top2_dp4_tp2_ep2_zero1": C("moe", "--dp-size 4 --tp-size 2 --ep-size 2 --zero-stage 1", common="--moe-top-k 2"),
     "cosine_dp4_tp2_sp_zero3": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3", common="--lr-schedule cosine --warmup-steps 1 --max-steps 6"),
     "ckpt_every2_dp4_tp2_sp": C("llama", "--dp-size 4 --tp-size 2 --use-sp --activation-checkpointing --activation-checkpoint-every-n-layers 2"),
+    # load-balance loss switched on: it is a statistic of the LOCAL batch, so these are compared with each other (same data
+    # sharding, experts placed differently), not with the full-batch baseline
+    "moe_aux_dp8": C("moe", "--dp-size 8", common="--moe-aux-loss-coef 0.05"),
+    "moe_aux_dp8_ep4": C("moe", "--dp-size 8 --ep-size 4", common="--moe-aux-loss-coef 0.05"),
+    "moe_aux_dp8_ep8_zero2": C("moe", "--dp-size 8 --ep-size 8 --zero-stage 2", common="--moe-aux-loss-coef 0.05"),
+    "moe_aux_dp4_pp2": C("moe", "--dp-size 4 --pp-size 2 --pp-schedule 1f1b", common="--moe-aux-loss-coef 0.05", pp_mb=1),
+    "moe_aux_dp4_pp2_ep4": C("moe", "--dp-size 4 --pp-size 2 --ep-size 4 --pp-schedule 1f1b", common="--moe-aux-loss-coef 0.05", pp_mb=1),
     "bf16_dp8": C("llama", "--dp-size 8 --precision bf16"),
     "bf16_dp8_zero1": C("llama", "--dp-size 8 --zero-stage 1 --precision bf16"),
     "bf16_dp8_zero3": C("llama", "--dp-size 8 --zero-stage 3 --precision bf16"),
@@ -326,7 +333,25 @@ def test_case_list_is_wide_enough():
     assert {c["model"] for c in CASES.values()} == set(MODELS) and any(c["packed"] for c in CASES.values())
 
 
-@pytest.mark.parametrize("name", sorted(CASES))
+AUX_PAIRS = [("moe_aux_dp8", "moe_aux_dp8_ep4"), ("moe_aux_dp8", "moe_aux_dp8_ep8_zero2"), ("moe_aux_dp4_pp2", "moe_aux_dp4_pp2_ep4")]
+
+
+@pytest.mark.parametrize("plain,expert_parallel", AUX_PAIRS)
+def test_load_balance_loss_is_the_same_wherever_the_experts_live(plain, expert_parallel, matrix_results):
+    """With the auxiliary loss on, expert parallelism (and ZeRO on top) must not change loss or gradient norm of a run
+    with the same data sharding."""
+    for step in range(STEPS):
+        vals = []
+        for name in (plain, expert_parallel):
+            per_rank = [r[name] for r in matrix_results]
+            for status, payload, *_ in per_rank:
+                assert status == "ok", payload
+            vals.append((sum(r[1][step] for r in per_rank) / WORLD, per_rank[0][4][step]))
+        (la, na), (lb, nb) = vals
+        assert abs(la - lb) < 2e-5 and (na is None or nb is None or abs(na - nb) < 2e-5 * max(1.0, na)), (step, vals)
+
+
+@pytest.mark.parametrize("name", sorted(n for n in CASES if not n.startswith("moe_aux_")))
 def test_case_matches_single_process_training(name, matrix_results, baselines):
     case = CASES[name]
     per_rank = [r[name] for r in matrix_results]
