@@ -34,7 +34,7 @@ from maltos_b200.parallel.specs import TpSpComm, TpSpShardAxis
 from maltos_b200.runtime.layers.functional import all_gather
 from maltos_b200.runtime.layers.linear import ColumnParallelLinear, RowParallelLinear
 from maltos_b200.runtime.plugin import PluginId
-from maltos_b200.runtime.types import RuntimePhase, SetupPhase
+from maltos_b200.runtime.types import ParamRole, RuntimePhase, SetupPhase
 from maltos_b200.utils.distributed import all_reduce_tensor
 
 from .tp import TensorParallelTransformPlugin
@@ -176,6 +176,10 @@ class TpSpPlugin(TensorParallelTransformPlugin):
                 continue
             seen.add(id(p))
             if self.is_tp_sharded(name):
+                continue
+            if self.runtime.get_param_role(p) == ParamRole.EXPERT and self.runtime.plan.reuse_tp_for_ep and self.runtime.mesh.ep > 1:
+                # the expert group reuses the tensor-parallel ranks: each of them holds DIFFERENT experts (or a replica that the
+                # expert plugin reduces itself over the expert-replica group) - summing them over the TP group would mix experts
                 continue
             full_input = any(name == g or name.startswith(g + ".") for g in self._gathered_paths)
             if full_input and id(p) not in row_bias:

@@ -134,6 +134,12 @@ CASES = {
     "moe_top2_dp4_tp2_ep2_zero1": C("moe", "--dp-size 4 --tp-size 2 --ep-size 2 --zero-stage 1", common="--moe-top-k 2"),
     "cosine_dp4_tp2_sp_zero3": C("llama", "--dp-size 4 --tp-size 2 --use-sp --zero-stage 3", common="--lr-schedule cosine --warmup-steps 1 --max-steps 6"),
     "ckpt_every2_dp4_tp2_sp": C("llama", "--dp-size 4 --tp-size 2 --use-sp --activation-checkpointing --activation-checkpoint-every-n-layers 2"),
+    # expert group reusing the tensor-parallel ranks under sequence parallelism: every TP rank holds different experts and different tokens
+    "moe_dp4_tp2_sp_ep4": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 4"),
+    "moe_dp4_tp2_sp_ep2": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 2"),
+    "moe_top2_dp4_tp2_sp_ep2_zero2": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 2 --zero-stage 2", common="--moe-top-k 2"),
+    "moe_dp4_tp2_sp": C("moe", "--dp-size 4 --tp-size 2 --use-sp"),
+    "moe_dp4_tp2": C("moe", "--dp-size 4 --tp-size 2"),
     # load-balance loss switched on: it is a statistic of the LOCAL batch, so these are compared with each other (same data
     # sharding, experts placed differently), not with the full-batch baseline
     "moe_aux_dp8": C("moe", "--dp-size 8", common="--moe-aux-loss-coef 0.05"),
@@ -141,6 +147,11 @@ CASES = {
     "moe_aux_dp8_ep8_zero2": C("moe", "--dp-size 8 --ep-size 8 --zero-stage 2", common="--moe-aux-loss-coef 0.05"),
     "moe_aux_dp4_pp2": C("moe", "--dp-size 4 --pp-size 2 --pp-schedule 1f1b", common="--moe-aux-loss-coef 0.05", pp_mb=1),
     "moe_aux_dp4_pp2_ep4": C("moe", "--dp-size 4 --pp-size 2 --ep-size 4 --pp-schedule 1f1b", common="--moe-aux-loss-coef 0.05", pp_mb=1),
+    # capacity-limited top-2 routing drops assignments per LOCAL batch: compared across expert placements as well
+    "moe_aux_cap_dp8": C("moe", "--dp-size 8", common="--moe-top-k 2 --moe-capacity-factor 0.75 --moe-aux-loss-coef 0.05"),
+    "moe_aux_cap_dp8_ep4_zero1": C("moe", "--dp-size 8 --ep-size 4 --zero-stage 1", common="--moe-top-k 2 --moe-capacity-factor 0.75 --moe-aux-loss-coef 0.05"),
+    "moe_aux_cap_dp4_tp2_sp_ep4": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 4", common="--moe-top-k 2 --moe-capacity-factor 0.75 --moe-aux-loss-coef 0.05"),
+    "moe_aux_cap_dp4_tp2_sp": C("moe", "--dp-size 4 --tp-size 2 --use-sp", common="--moe-top-k 2 --moe-capacity-factor 0.75 --moe-aux-loss-coef 0.05"),
     "bf16_dp8": C("llama", "--dp-size 8 --precision bf16"),
     "bf16_dp8_zero1": C("llama", "--dp-size 8 --zero-stage 1 --precision bf16"),
     "bf16_dp8_zero3": C("llama", "--dp-size 8 --zero-stage 3 --precision bf16"),
@@ -261,13 +272,15 @@ def _replica_spread(core) -> float:
     worst = 0.0
     for name, entry in core.state_manager.params.items():
         p = entry.param
-        if core.get_param_role(p) == ParamRole.EXPERT or p.untyped_storage().size() == 0:
-            continue        # expert copies differ by design; ZeRO-3 parameters are not materialised between steps
+        if p.untyped_storage().size() == 0:
+            continue        # ZeRO-3 parameters are not materialised between steps
         axes = set(entry.attrs.replicated_axes)
+        if core.get_param_role(p) == ParamRole.EXPERT:
+            axes &= {MeshAxis.EREP}          # an expert's copies live on the expert-replica group only
         if axes & {MeshAxis.DP, MeshAxis.CP, MeshAxis.DCP}:
             axes = (axes - {MeshAxis.DP, MeshAxis.CP}) | {MeshAxis.DCP}
         for axis in sorted(axes, key=lambda a: a.value):
-            if axis not in (MeshAxis.DCP, MeshAxis.TP):
+            if axis not in (MeshAxis.DCP, MeshAxis.TP, MeshAxis.EREP):
                 continue
             group = core.get_group(axis)
             if group is None or dist.get_world_size(group) <= 1:
@@ -333,7 +346,8 @@ def test_case_list_is_wide_enough():
     assert {c["model"] for c in CASES.values()} == set(MODELS) and any(c["packed"] for c in CASES.values())
 
 
-AUX_PAIRS = [("moe_aux_dp8", "moe_aux_dp8_ep4"), ("moe_aux_dp8", "moe_aux_dp8_ep8_zero2"), ("moe_aux_dp4_pp2", "moe_aux_dp4_pp2_ep4")]
+AUX_PAIRS = [("moe_aux_dp8", "moe_aux_dp8_ep4"), ("moe_aux_dp8", "moe_aux_dp8_ep8_zero2"), ("moe_aux_dp4_pp2", "moe_aux_dp4_pp2_ep4"),
+             ("moe_aux_cap_dp8", "moe_aux_cap_dp8_ep4_zero1"), ("moe_aux_cap_dp4_tp2_sp", "moe_aux_cap_dp4_tp2_sp_ep4")]
 
 
 @pytest.mark.parametrize("plain,expert_parallel", AUX_PAIRS)
