@@ -138,6 +138,10 @@ CASES = {
     "moe_dp4_tp2_sp_ep4": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 4"),
     "moe_dp4_tp2_sp_ep2": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 2"),
     "moe_top2_dp4_tp2_sp_ep2_zero2": C("moe", "--dp-size 4 --tp-size 2 --use-sp --ep-size 2 --zero-stage 2", common="--moe-top-k 2"),
+    "moe_dp2_pp2_tp2_sp_ep2_1f1b": C("moe", "--dp-size 2 --pp-size 2 --tp-size 2 --use-sp --ep-size 2 --pp-schedule 1f1b", pp_mb=2),
+    "moe_dp2_cp2_tp2_sp_ep2_ring_zero1": C("moe", "--dp-size 2 --cp-size 2 --tp-size 2 --use-sp --ep-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 1"),
+    "moe_dp2_cp2_tp2_ep2_allgather": C("moe", "--dp-size 2 --cp-size 2 --tp-size 2 --ep-size 2 --cp-attn-core all_gather_kv"),
+    "moe_top2_dp2_cp4_ep2_ring_zero3": C("moe", "--dp-size 2 --cp-size 4 --ep-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 3", common="--moe-top-k 2"),
     "moe_dp4_tp2_sp": C("moe", "--dp-size 4 --tp-size 2 --use-sp"),
     "moe_dp4_tp2": C("moe", "--dp-size 4 --tp-size 2"),
     # load-balance loss switched on: it is a statistic of the LOCAL batch, so these are compared with each other (same data
