@@ -11,6 +11,7 @@ from maltos_b200.utils.constants import IGNORE_INDEX, PAD_SEQUENCE_ID
 from tests.dist_utils import run_distributed
 
 VOCAB, SEQ = 96, 48
+CLIP = 0.05     # below the gradient norm, so that clipping acts in every step
 
 
 def _packed_batch(seed=0, rows=3):
@@ -132,7 +133,7 @@ def _hdp_worker(rank, world, partition_tokens=16):
     import maltos_b200  # noqa: F401
     from maltos_b200.runtime import MeshConfig, RuntimeCore
     from maltos_b200.runtime.layers import hdp_attention
-    from maltos_b200.runtime.plugins import ddp
+    from maltos_b200.runtime.plugins import ddp, grad_clip
     from maltos_b200.runtime.plugins.hdp import ByteScaleHdpPlugin
 
     plans = []
@@ -145,11 +146,11 @@ def _hdp_worker(rank, world, partition_tokens=16):
 
     hdp_attention.document_ring_plan = recording
     cfg = ByteScaleHdpBalancedConfig(partition_tokens=partition_tokens, cost_model=ByteScaleHdpCostModel(1.0, 8.0, 32.0))
-    rt = RuntimeCore(model=_model(), mesh=MeshConfig(dp=world), plugins=[ddp.DataParallelPlugin(), ByteScaleHdpPlugin(config=cfg)],
+    rt = RuntimeCore(model=_model(), mesh=MeshConfig(dp=world), plugins=[ddp.DataParallelPlugin(), ByteScaleHdpPlugin(config=cfg), grad_clip.GradClipPlugin(CLIP)],
                      optimizer_factory=_opt, grad_accum_steps=1)
     rt.setup()
     loader = ByteScaleHdpDataLoader(_FixedLoader([_packed_batch(seed=11), _packed_batch(seed=12)]), hdp_rank=rank, hdp_world_size=world, config=cfg)
-    losses = []
+    losses, norms = [], []
     for _ in range(2):
         env = loader.next_batch()
         assert len(env[BYTESCALE_HDP_WAVES_KEY]) >= 1
@@ -157,6 +158,7 @@ def _hdp_worker(rank, world, partition_tokens=16):
         assert should
         rt.step_optimizer()
         losses.append(float(loss))
+        norms.append(float(rt.collect_metrics()["grad_clip/grad_norm"]))
     metrics = rt.collect_metrics()
     params = {n: p.detach().clone() for n, p in rt.model.named_parameters()}
     import torch.distributed as dist
@@ -169,7 +171,7 @@ def _hdp_worker(rank, world, partition_tokens=16):
         spread = max(spread, float((hi - lo).abs().max()))
     assert spread == 0.0, spread
     rt.close()
-    return losses, params, {k: v for k, v in metrics.items() if "wave" in k}, plans
+    return losses, params, {k: v for k, v in metrics.items() if "wave" in k}, plans, norms
 
 
 def test_document_ring_plan_allows_the_half_block_schedule_only_with_confined_padding():
@@ -187,12 +189,13 @@ def test_document_ring_plan_allows_the_half_block_schedule_only_with_confined_pa
 def test_hdp_training_matches_single_process(world, partition_tokens):
     model = _model()
     opt = _opt(model.parameters())
-    ref_losses = []
+    ref_losses, ref_norms = [], []
     for seed in (11, 12):
         opt.zero_grad(set_to_none=True)
         out = model(_packed_batch(seed=seed))
         loss = out.loss if hasattr(out, "loss") else out
         loss.backward()
+        ref_norms.append(float(torch.nn.utils.clip_grad_norm_(model.parameters(), CLIP)))
         opt.step()
         ref_losses.append(float(loss.detach()))
     ref_params = {n: p.detach().clone() for n, p in model.named_parameters()}
@@ -204,7 +207,9 @@ def test_hdp_training_matches_single_process(world, partition_tokens):
     for step in range(2):   # each rank reports world x its share of the global mean
         total = sum(r[0][step] for r in results) / world
         assert abs(total - ref_losses[step]) < 2e-4, (total, ref_losses[step])
-    for _, params, wave_metrics, _ in results:
+    for r in results:            # the clipped norm is the norm of the global gradient (AdamW hides a wrong scale from the loss)
+        assert all(abs(a - b) < 1e-5 for a, b in zip(r[4], ref_norms)), (r[4], ref_norms)
+    for _, params, wave_metrics, *_ in results:
         assert wave_metrics.get("hdp/real_wave_count", wave_metrics.get("real_wave_count", 1)) >= 1
         for name, ref in ref_params.items():
             assert torch.allclose(params[name], ref, atol=2e-4, rtol=1e-3), name
