@@ -158,3 +158,23 @@ def test_manifest_validation_errors(tmp_path):
     assert fresh.state.step_context.step == 1
     with pytest.raises(RuntimeError, match="insufficient free space"):
         save_sharded_checkpoint(rt.state_manager, tmp_path / "step_00000002", min_free_gb=1e9)
+
+
+@pytest.mark.skipif(not (REF / "runtime" / "core.py").exists(), reason="reference not installed under baseline/_ref")
+@pytest.mark.parametrize("name,extra,model", [
+    ("dp4_bucket", ["--dp-size", "4", "--ddp-mode", "bucket"], None),
+    ("tp4_sp_accum", ["--tp-size", "4", "--use-sp"], ["--n-kv-heads", "4"]),
+    ("moe_dp4_ep2_zero1", ["--dp-size", "4", "--ep-size", "2", "--zero-stage", "1"],
+     ["--model", "tiny_moe", "--num-experts", "4", "--moe-aux-loss-coef", "0.01"]),
+])
+def test_same_losses_as_the_reference_on_four_ranks(name, extra, model, shards, tmp_path):
+    """The unmodified reference and this framework, same flags, four gloo ranks: the logged losses agree. Under TP + SP the
+    reference does not sum the partial gradients of unsharded parameters (norm weights) over the TP group, so its third
+    step drifts by a few 1e-4 from single-process training, which this framework reproduces exactly - hence the tolerance.
+    (Under pipeline parallelism the reference logs a different quantity on non-final stages; not compared.)"""
+    flags = list(extra) + (model or [])
+    ours = _losses(_launch(ROOT, ["-m", "maltos_b200.tools.train"], shards, tmp_path / "ours", 3, flags, 4))
+    ref = _losses(_launch(REF, ["tools/train.py"], shards, tmp_path / "ref", 3, flags, 4))
+    assert len(ours) == len(ref) == 3
+    assert all(abs(float(a) - float(b)) <= (1e-3 if "--use-sp" in flags else 1e-4) for a, b in zip(ours, ref)), (name, ours, ref)
+    assert ours[:2] == ref[:2]
