@@ -25,6 +25,8 @@ MODELS = {
     "llama": ["--model", "llama", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "4", "--hidden-size", "128", "--n-layers", "4"],
     "olmo": ["--model", "olmo2", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "4", "--hidden-size", "128", "--n-layers", "4"],
     "tiny": ["--model", "tiny", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "128", "--n-layers", "4"],
+    "moe4": ["--model", "tiny_moe", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "4", "--hidden-size", "96", "--n-layers", "2", "--num-experts", "8",
+             "--moe-aux-loss-coef", "0"],
     "moe": ["--model", "tiny_moe", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "96", "--n-layers", "2", "--num-experts", "8",
             "--moe-aux-loss-coef", "0"],
 }
@@ -142,6 +144,8 @@ CASES = {
     "moe_dp2_cp2_tp2_sp_ep2_ring_zero1": C("moe", "--dp-size 2 --cp-size 2 --tp-size 2 --use-sp --ep-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 1"),
     "moe_dp2_cp2_tp2_ep2_allgather": C("moe", "--dp-size 2 --cp-size 2 --tp-size 2 --ep-size 2 --cp-attn-core all_gather_kv"),
     "moe_top2_dp2_cp4_ep2_ring_zero3": C("moe", "--dp-size 2 --cp-size 4 --ep-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 3", common="--moe-top-k 2"),
+    "moe_dp2_tp4_ep2": C("moe4", "--dp-size 2 --tp-size 4 --ep-size 2"),
+    "moe_dp2_tp4_sp_ep2_zero1": C("moe4", "--dp-size 2 --tp-size 4 --use-sp --ep-size 2 --zero-stage 1"),
     "moe_dp4_tp2_sp": C("moe", "--dp-size 4 --tp-size 2 --use-sp"),
     "moe_dp4_tp2": C("moe", "--dp-size 4 --tp-size 2"),
     # load-balance loss switched on: it is a statistic of the LOCAL batch, so these are compared with each other (same data
