@@ -177,6 +177,7 @@ RESUME = {   # case name -> micro-steps to run before the checkpoint (a multiple
     "dp4_pp2_afab_accum2": 1, "moe_dp4_pp2_ep2_1f1b": 1, "packed_dp2_cp2_tp2_ring": 1, "moe_dp8_ep4_zero3": 1,
     # in the middle of an accumulation window WITHOUT a sharded optimizer: the partial gradients travel with the checkpoint
     "dp4_bucket_tp2": 3, "dp8_bucket_accum2": 1,
+    "moe_dp4_tp2_sp_ep4": 1, "cp8_ring": 1, "olmo_packed_pp2_cp2_tp2_sp_ring_1f1b_ckpt": 1, "moe_top2_dp2_cp4_ep2_ring_zero3": 1,
 }
 
 
