@@ -158,3 +158,29 @@ def test_profiler_can_time_the_recipes_own_loader(tmp_path):
     assert summary["timed_steps"] == 2 and summary["tokens_per_second"] > 0
     with pytest.raises(SystemExit, match="--data"):
         ptp.main(["--recipe", str(recipe), "--data-source", "recipe", "--output-dir", str(tmp_path / "o2")])
+
+
+def test_bench_line_carries_every_key_of_the_contract():
+    """`python bench.py` prints ONE JSON line with the agreed keys (checked on the tiny CPU plumbing configuration, for both
+    arms when the reference is installed)."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    arms = [[]] + ([["--impl", "reference"]] if (root / "baseline" / "_ref" / "runtime" / "core.py").exists() else [])
+    for arm in arms:
+        out = subprocess.run([sys.executable, "bench.py", "--small", "--device", "cpu", "--steps", "2", "--warmup", "1", *arm], cwd=root,
+                             capture_output=True, text=True, timeout=900)
+        assert out.returncode == 0, out.stderr[-2000:]
+        lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+        assert len(lines) == 1, out.stdout[-2000:]
+        row = json.loads(lines[0])
+        for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline", "dtype",
+                    "data", "config", "clocks", "e2e", "gpu_launches", "impl"):
+            assert key in row, (arm, key)
+        assert row["steps"] == 2 and row["warmup"] == 1 and row["n_gpus"] == 1 and row["higher_is_better"] is True
+        assert row["impl"] == ("reference" if arm else "ours")
+        assert {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"} <= set(row["e2e"]) and row["e2e"]["h2d_bytes_per_step"] > 0
+        assert {"micro_batch", "grad_accum", "global_batch", "seq_len"} <= set(row["config"])
+        assert row["config"]["micro_batch"] * row["config"]["grad_accum"] == row["config"]["global_batch"]
