@@ -184,3 +184,31 @@ def test_bench_line_carries_every_key_of_the_contract():
         assert {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"} <= set(row["e2e"]) and row["e2e"]["h2d_bytes_per_step"] > 0
         assert {"micro_batch", "grad_accum", "global_batch", "seq_len"} <= set(row["config"])
         assert row["config"]["micro_batch"] * row["config"]["grad_accum"] == row["config"]["global_batch"]
+
+
+def test_every_recipe_and_every_profiler_case_validates():
+    """All YAML recipes in ``configs/`` and all named profiler cases parse, and their parallel layout passes the CLI's
+    validation for the world size they ask for."""
+    from pathlib import Path
+
+    from maltos_b200.train import cli, flags
+
+    root = Path(__file__).resolve().parents[1]
+    recipes = sorted(p for p in (root / "configs").glob("*.yaml") if p.name != "profile_train_perf_cases.yaml")
+    assert len(recipes) >= 8
+    for recipe in recipes:
+        a = flags.parse_args_from(["--config", str(recipe)], require_data=False)
+        cli.validate_args(a, a.dp_size * a.tp_size * a.pp_size * a.cp_size)
+    import os
+
+    here = os.getcwd()
+    os.chdir(root)      # cases name their recipes relative to the repository root
+    try:
+        cases = ptp._load_cases(root / "configs" / "profile_train_perf_cases.yaml")
+        assert len(cases) >= 12
+        for case in cases.values():
+            a = ptp._training_args(case, [])
+            cli.validate_args(a, a.dp_size * a.tp_size * a.pp_size * a.cp_size)
+            ptp._synthetic_config(ptp._parse_tool_args(["--case", case.name]), case)
+    finally:
+        os.chdir(here)
