@@ -369,8 +369,18 @@ def _build_logging(args: argparse.Namespace, rank: int):
         loggers.append(JsonlMetricLogger(args.metrics_jsonl))
     uploader = None
     if args.wandb_project and args.wandb_mode != "disabled":
-        wb = WandbMetricLogger(project=args.wandb_project, name=args.wandb_run_name, entity=args.wandb_entity, run_id=args.wandb_run_id,
-                               mode=args.wandb_mode, tags=_parse_tags(args.wandb_tags), config=vars(args))
+        try:
+            wb = WandbMetricLogger(project=args.wandb_project, name=args.wandb_run_name, entity=args.wandb_entity, run_id=args.wandb_run_id,
+                                   mode=args.wandb_mode, tags=_parse_tags(args.wandb_tags), config=vars(args))
+        except Exception as exc:  # noqa: BLE001 - no key, no network, package missing
+            # Only this rank builds loggers: raising here would leave every other rank waiting in the next collective until
+            # the process-group timeout. Training goes on with the console / JSONL sinks.
+            if os.environ.get("MALTOS_B200_WANDB_REQUIRED", "0") == "1":
+                raise
+            print(f"WARNING: Weights & Biases logging was requested (project={args.wandb_project!r}, mode={args.wandb_mode!r}) but could not be "
+                  f"started: {type(exc).__name__}: {exc}. Continuing without it (--wandb-mode offline|disabled selects that explicitly; "
+                  "MALTOS_B200_WANDB_REQUIRED=1 makes this fatal).", file=sys.stderr, flush=True)
+            return loggers, None
         loggers.append(wb)
         if args.wandb_checkpoint_every is not None:
             uploader = WandbCheckpointUploader(wb, every_steps=args.wandb_checkpoint_every)

@@ -295,3 +295,26 @@ def test_experts_without_tokens_are_entered_only_when_hooks_need_it():
     experts[2].lin.register_forward_pre_hook(lambda m, a: None)      # what a parameter-sharding plugin installs
     moe_experts_forward(flat, idx, gate, None, experts)
     assert calls == [(0, 5), (2, 0)]
+
+
+def test_wandb_that_cannot_start_degrades_to_the_other_sinks(monkeypatch, capsys):
+    """Only rank 0 builds loggers; an exception there would leave the other ranks in their next collective until the
+    process-group timeout. The run goes on with console / JSONL logging unless the environment makes W&B mandatory."""
+    import argparse
+
+    from maltos_b200.train import cli
+    from maltos_b200.utils import metrics
+
+    def broken(**kw):
+        raise RuntimeError("No API key configured")
+
+    monkeypatch.setattr(metrics, "WandbMetricLogger", broken)
+    args = argparse.Namespace(metrics_jsonl=None, wandb_project="p", wandb_mode=None, wandb_run_name=None, wandb_entity=None, wandb_run_id=None,
+                              wandb_tags=None, wandb_checkpoint_every=5)
+    loggers, uploader = cli._build_logging(args, 0)
+    assert len(loggers) == 1 and uploader is None
+    assert "could not be" in capsys.readouterr().err
+    assert cli._build_logging(args, 1) == (None, None)
+    monkeypatch.setenv("MALTOS_B200_WANDB_REQUIRED", "1")
+    with pytest.raises(RuntimeError):
+        cli._build_logging(args, 0)
