@@ -16,17 +16,18 @@ from maltos_b200.ops.cross_entropy import linear_cross_entropy
 from maltos_b200.ops.gemm import linear
 from maltos_b200.ops.grouped import grouped_linear
 from maltos_b200.utils.activation_checkpoint import activation_checkpoint_context_fn
-from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
+from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
                                          POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 from maltos_b200.utils.losses import causal_cross_entropy
 
 
 class ParsedBatch:
-    __slots__ = ("input_ids", "hidden_states", "labels", "position_offset", "position_ids", "sequence_ids", "loss_weight")
+    __slots__ = ("input_ids", "hidden_states", "labels", "position_offset", "position_ids", "sequence_ids", "loss_weight", "aux_loss_weight")
 
     def __init__(self, batch: Any) -> None:
         self.hidden_states = self.labels = self.position_ids = self.sequence_ids = self.loss_weight = None
         self.position_offset = 0
+        self.aux_loss_weight = None
         if isinstance(batch, dict):
             self.input_ids = batch.get(INPUT_IDS_KEY)
             self.hidden_states = batch.get(HIDDEN_STATES_KEY)
@@ -35,6 +36,7 @@ class ParsedBatch:
             self.position_ids = batch.get(POSITION_IDS_KEY)
             self.sequence_ids = batch.get(SEQUENCE_IDS_KEY)
             self.loss_weight = batch.get(LOSS_WEIGHT_KEY)
+            self.aux_loss_weight = batch.get(AUX_LOSS_WEIGHT_KEY)
         elif isinstance(batch, (tuple, list)):
             self.input_ids, self.labels = batch
         else:

@@ -168,6 +168,8 @@ class TinyMoETransformer(nn.Module):
         if want_aux:
             balance = torch.stack(aux_terms).sum() / float(self._total_moe_layers) if aux_terms else x.new_zeros((), dtype=torch.float32)
             aux_loss = self.moe_aux_loss_coef * balance
+            if b.aux_loss_weight is not None:       # this rank sees 1 / cp of every sequence and the gradients are summed
+                aux_loss = aux_loss * float(b.aux_loss_weight)
         if self.norm is None or self.lm_head is None:
             return PipelineOutput(activation=x, auxiliary_loss=aux_loss) if want_aux else x
         h = self.norm(x)

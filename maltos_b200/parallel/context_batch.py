@@ -12,7 +12,7 @@ from typing import Any
 
 import torch
 
-from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY,
+from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY,
                                          LOSS_WEIGHT_KEY, POSITION_IDS_KEY, POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 
 from .context_token_planner import ContextTokenPlanner
@@ -103,6 +103,7 @@ class ContextParallelBatchSharder:
         out[LOSS_WEIGHT_KEY] = target_fraction(counts)
         if counts is not None:
             out[LOSS_TARGET_COUNTS_KEY] = counts
+        out[AUX_LOSS_WEIGHT_KEY] = 1.0 / self.world_size      # every rank holds the same number of tokens
         if not isinstance(batch, dict):
-            out = {k: out[k] for k in (INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY)}
+            out = {k: out[k] for k in (INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY, AUX_LOSS_WEIGHT_KEY)}
         return out

@@ -451,6 +451,18 @@ class Zero3Plugin(ZeroPluginBase):
     def annotate_param_metadata(self) -> None:
         return
 
+    def bucket_checkpoint_names(self, bucket: ShardedBucket) -> list[str]:
+        """Names under which the tensors of ``bucket`` go into a checkpoint: the logical name another plugin has recorded for a
+        parameter (expert parallelism: ``local_experts.{i}`` of this rank -> ``experts.{global id}``), else the runtime name.
+        Without this the expert buckets of different expert-parallel ranks would carry the same names."""
+        params = self.runtime.state_manager.params
+        out = []
+        for name in bucket.logical_names:
+            entry = params.get(name)
+            logical = list(entry.meta.logical_names) if entry is not None else []
+            out.append(logical[0] if len(logical) == 1 else name)
+        return out
+
     def export_model_state(self, state_manager):
         rank = dist.get_rank() if dist.is_initialized() else 0
         tensors: dict[str, torch.Tensor] = {}
@@ -458,7 +470,7 @@ class Zero3Plugin(ZeroPluginBase):
         for b in self.buckets:
             key = f"zero3_bucket_{b.index}"
             tensors[key] = b.local_param.detach().cpu().clone()
-            metas.append(ModelStateMeta(state_key=key, logical_names=list(b.logical_names), logical_shapes=[tuple(s) for s in b.param_shapes],
+            metas.append(ModelStateMeta(state_key=key, logical_names=self.bucket_checkpoint_names(b), logical_shapes=[tuple(s) for s in b.param_shapes],
                                         physical_shape=(b.shard_numel,), dtype=str(b.local_param.dtype), source_rank=rank))
         for name, entry in state_manager.buffers.items():
             tensors[name] = entry.tensor.detach().cpu().clone()

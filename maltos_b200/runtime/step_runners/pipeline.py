@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from maltos_b200.runtime.buffer_allocator import BufferPolicy, acquire_buffer
 from maltos_b200.runtime.types import LossOutput, PipelineOutput, PpStatus
-from maltos_b200.utils.constants import (HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
+from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
                                          POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 from maltos_b200.utils.distributed import all_reduce_tensor, irecv_tensor_async, isend_tensor_async
 from maltos_b200.utils.profiling import span
@@ -72,7 +72,7 @@ def one_f_one_b_actions(m: int, stage: int, stages: int) -> list[PipelineAction]
     return out
 
 
-_PASS_THROUGH_KEYS = (POSITION_OFFSET_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY)
+_PASS_THROUGH_KEYS = (POSITION_OFFSET_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY, AUX_LOSS_WEIGHT_KEY)
 
 
 @dataclass(frozen=True)

@@ -355,10 +355,12 @@ def iter_logical_tensors_from_runtime_checkpoint(checkpoint_dir: str | Path, *, 
     zero3_groups: dict[tuple, list[tuple[int, ModelStateMeta]]] = {}
     for owner, entry in _owned_model_entries(manifest):
         if _is_zero3_entry(entry):
-            # slices of one bucket live on the ranks that differ only in the sharding (dp / cp) coordinates
+            # The slices of one bucket live on the ranks that differ only in the sharding (dp / cp) coordinates. Every
+            # tensor-parallel coordinate has a bucket of its own, also for tensors that are replicated over that axis (their
+            # copies are compared when the tensor is assembled); expert buckets of different expert-parallel ranks differ in
+            # their (global) names.
             _, pp_idx, _, tp_idx = _rank_coordinates(rank=owner, dp_size=dp_size, pp_size=pp_size, cp_size=cp_size, tp_size=tp_size)
-            tp_sharded = any(rules.get(n) in (TpSpShardAxis.PARAM_OUT, TpSpShardAxis.PARAM_IN) for n in entry.logical_names)
-            key = ("zero3", pp_idx, tp_idx if tp_sharded else None, tuple(entry.logical_names), tuple(entry.logical_shapes))
+            key = ("zero3", pp_idx, tp_idx, tuple(entry.logical_names), tuple(entry.logical_shapes))
             zero3_groups.setdefault(key, []).append((owner, entry))
             continue
         for name, local in _split_entry_tensor(entry, files.entry(owner, entry.state_key)):
@@ -406,7 +408,7 @@ def _runtime_model_state_entries(runtime: "RuntimeCore") -> list[ModelStateMeta]
     if zero3 is None:
         return [e.meta for e in sm.params.values()] + buffer_entries
     rank = dist.get_rank() if dist.is_initialized() else 0
-    buckets = [ModelStateMeta(state_key=f"{_ZERO3_PREFIX}{b.index}", logical_names=list(b.logical_names),
+    buckets = [ModelStateMeta(state_key=f"{_ZERO3_PREFIX}{b.index}", logical_names=_bucket_names(zero3, b),
                               logical_shapes=[tuple(s) for s in b.param_shapes], physical_shape=tuple(b.local_param.shape),
                               dtype=str(b.local_param.dtype), source_rank=rank) for b in zero3.buckets]
     return buckets + buffer_entries
@@ -433,13 +435,19 @@ def _build_runtime_entry_tensor(*, runtime: "RuntimeCore", entry: ModelStateMeta
     return out.to(dtype=target.dtype).cpu().contiguous()
 
 
-def _build_zero3_bucket_tensor(*, bucket, tensors: Mapping[str, torch.Tensor], shard_rules: dict[str, str], tp_rank: int,
+def _bucket_names(plugin, bucket) -> list[str]:
+    """Checkpoint names of a flat bucket's tensors (logical names where a plugin renamed parameters, e.g. experts)."""
+    mapper = getattr(plugin, "bucket_checkpoint_names", None)
+    return list(mapper(bucket)) if mapper is not None else list(bucket.logical_names)
+
+
+def _build_zero3_bucket_tensor(*, bucket, names: list[str], tensors: Mapping[str, torch.Tensor], shard_rules: dict[str, str], tp_rank: int,
                                tp_world_size: int, expected_shape: tuple[int, ...]) -> torch.Tensor:
     """This rank's slice of a flat ZeRO-3 bucket filled from logical tensors (padding stays zero)."""
     total = getattr(bucket, "buffer_size", None) or bucket.padded
     flat = torch.zeros(total, dtype=bucket.local_param.dtype, device="cpu")
     at = 0
-    for name, n, shape in zip(bucket.logical_names, bucket.param_numels, bucket.param_shapes, strict=True):
+    for name, n, shape in zip(names, bucket.param_numels, bucket.param_shapes, strict=True):
         if name not in tensors:
             raise KeyError(f"logical checkpoint missing tensor={name}")
         local = _local_tensor_for_runtime_tensor(name=name, logical=tensors[name], shard_rules=shard_rules, tp_rank=tp_rank,
@@ -472,7 +480,7 @@ def _build_runtime_model_state_from_logical_tensors(runtime: "RuntimeCore", tens
             bucket = buckets.get(entry.state_key)
             if bucket is None:
                 raise ValueError(f"zero3 runtime bucket metadata missing for state_key={entry.state_key}")
-            state[entry.state_key] = _build_zero3_bucket_tensor(bucket=bucket, tensors=tensors, shard_rules=rules, tp_rank=tp_rank,
+            state[entry.state_key] = _build_zero3_bucket_tensor(bucket=bucket, names=list(entry.logical_names), tensors=tensors, shard_rules=rules, tp_rank=tp_rank,
                                                                 tp_world_size=tp_world, expected_shape=entry.physical_shape)
         else:
             state[entry.state_key] = _build_runtime_entry_tensor(runtime=runtime, entry=entry, tensors=tensors, shard_rules=rules,

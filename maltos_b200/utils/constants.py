@@ -14,10 +14,13 @@ LOSS_WEIGHT_KEY = "loss_weight"
 #: per-row ``[rows, 2]`` (local targets, targets over the whole context-parallel group) behind ``loss_weight``: lets a
 #: pipeline runner that cuts the batch into micro-batches give every piece its own exact weight
 LOSS_TARGET_COUNTS_KEY = "loss_target_counts"
+#: weight of token-count based auxiliary losses (expert load balance) of a rank that holds ``1 / cp`` of every sequence:
+#: context-parallel gradients are SUMMED over the group, so an unweighted local term would count ``cp`` times
+AUX_LOSS_WEIGHT_KEY = "auxiliary_loss_weight"
 HIDDEN_STATES_KEY = "hidden_states"
 
 MODEL_BATCH_KEYS = (
     INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY,
-    POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY,
+    POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY, AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY,
 )
 SFT_BATCH_KEYS = (INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY)

@@ -153,6 +153,10 @@ CASES = {
     "moe_aux_dp8": C("moe", "--dp-size 8", common="--moe-aux-loss-coef 0.05"),
     "moe_aux_dp8_ep4": C("moe", "--dp-size 8 --ep-size 4", common="--moe-aux-loss-coef 0.05"),
     "moe_aux_dp8_ep8_zero2": C("moe", "--dp-size 8 --ep-size 8 --zero-stage 2", common="--moe-aux-loss-coef 0.05"),
+    # context parallelism cuts every sequence in two: the balance term of a rank covers half the tokens and is weighted 1 / cp
+    "moe_aux_dp4_cp2": C("moe", "--dp-size 4 --cp-size 2", common="--moe-aux-loss-coef 0.05"),
+    "moe_aux_dp4_cp2_ring_ep4": C("moe", "--dp-size 4 --cp-size 2 --cp-attn-core ring --ep-size 4", common="--moe-aux-loss-coef 0.05"),
+    "moe_aux_dp4_tp2": C("moe", "--dp-size 4 --tp-size 2", common="--moe-aux-loss-coef 0.05"),
     "moe_aux_dp4_pp2": C("moe", "--dp-size 4 --pp-size 2 --pp-schedule 1f1b", common="--moe-aux-loss-coef 0.05", pp_mb=1),
     "moe_aux_dp4_pp2_ep4": C("moe", "--dp-size 4 --pp-size 2 --ep-size 4 --pp-schedule 1f1b", common="--moe-aux-loss-coef 0.05", pp_mb=1),
     # capacity-limited top-2 routing drops assignments per LOCAL batch: compared across expert placements as well
@@ -372,6 +376,23 @@ def test_load_balance_loss_is_the_same_wherever_the_experts_live(plain, expert_p
             vals.append((sum(r[1][step] for r in per_rank) / WORLD, per_rank[0][4][step]))
         (la, na), (lb, nb) = vals
         assert abs(la - lb) < 2e-5 and (na is None or nb is None or abs(na - nb) < 2e-5 * max(1.0, na)), (step, vals)
+
+
+@pytest.mark.parametrize("cp_case", ["moe_aux_dp4_cp2", "moe_aux_dp4_cp2_ring_ep4"])
+def test_load_balance_loss_has_the_same_strength_under_context_parallelism(cp_case, matrix_results):
+    """The balance term is a product of two token averages, so halves of a sequence do not give exactly the value of the
+    whole - but nearly; counted once per context-parallel rank (gradients are summed over that group) it would be off by
+    the whole term (~0.05 here). Compared with a run whose data-parallel ranks see the same rows uncut."""
+    for step in range(STEPS):
+        vals = []
+        for name in ("moe_aux_dp4_tp2", cp_case):
+            per_rank = [r[name] for r in matrix_results]
+            for status, payload, *_ in per_rank:
+                assert status == "ok", payload
+            vals.append((sum(r[1][step] for r in per_rank) / WORLD, per_rank[0][4][step]))    # the logged loss is cp x the share
+        (la, na), (lb, nb) = vals
+        assert abs(la - lb) < 4e-3, (step, vals)
+        assert na is None or nb is None or abs(na - nb) < 0.03 * na, (step, vals)
 
 
 @pytest.mark.parametrize("name", sorted(n for n in CASES if not n.startswith("moe_aux_")))
