@@ -113,6 +113,18 @@ class Zero1Plugin(ZeroPluginBase):
                     p.register_post_accumulate_grad_hook(self._make_hook(b))
         return model
 
+    def annotate_param_metadata(self) -> None:
+        """Stages 1 and 2 shard optimizer state and gradients, not the weights: every data-parallel rank holds the same
+        non-expert parameters, so ONE of them writes each into a checkpoint (the reference leaves the axis unmarked under
+        ZeRO-1/2 and every data-parallel replica writes its own copy: dp times the bytes, and an offline conversion that
+        joins tensor-parallel pieces sees each piece dp times). Experts are marked by the expert-parallel plugin."""
+        if self.runtime.mesh.dp <= 1:
+            return
+        sm = self.runtime.state_manager
+        for name, entry in sm.params.items():
+            if self.runtime.get_param_role(entry.param) != ParamRole.EXPERT:
+                sm.update_model_state(name, replicated_axes=entry.attrs.replicated_axes | {MeshAxis.DP})
+
     def _build_buckets(self, model: nn.Module) -> None:
         self.buckets = []
         for role in (ParamRole.SHARED, ParamRole.EXPERT):

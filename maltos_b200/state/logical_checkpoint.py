@@ -352,8 +352,9 @@ def iter_logical_tensors_from_runtime_checkpoint(checkpoint_dir: str | Path, *, 
     files = _RankFiles(checkpoint_dir, manifest)
 
     pieces: dict[str, list[tuple[int, torch.Tensor]]] = {}
+    first_writer: dict[tuple[str, int, int], int] = {}
     zero3_groups: dict[tuple, list[tuple[int, ModelStateMeta]]] = {}
-    for owner, entry in _owned_model_entries(manifest):
+    for owner, entry in sorted(_owned_model_entries(manifest), key=lambda item: item[0]):
         if _is_zero3_entry(entry):
             # The slices of one bucket live on the ranks that differ only in the sharding (dp / cp) coordinates. Every
             # tensor-parallel coordinate has a bucket of its own, also for tensors that are replicated over that axis (their
@@ -363,8 +364,16 @@ def iter_logical_tensors_from_runtime_checkpoint(checkpoint_dir: str | Path, *, 
             key = ("zero3", pp_idx, tp_idx, tuple(entry.logical_names), tuple(entry.logical_shapes))
             zero3_groups.setdefault(key, []).append((owner, entry))
             continue
-        for name, local in _split_entry_tensor(entry, files.entry(owner, entry.state_key)):
-            pieces.setdefault(name, []).append((owner, local.detach().cpu().contiguous()))
+        _, pp_idx, _, tp_idx = _rank_coordinates(rank=owner, dp_size=dp_size, pp_size=pp_size, cp_size=cp_size, tp_size=tp_size)
+        for name in entry.logical_names:
+            # a tensor that several data / context-parallel replicas wrote (a checkpoint whose writer left those axes
+            # unmarked) is taken once per pipeline and tensor-parallel coordinate: from its lowest writer
+            first = first_writer.setdefault((name, pp_idx, tp_idx), owner)
+            if first != owner:
+                break
+        else:
+            for name, local in _split_entry_tensor(entry, files.entry(owner, entry.state_key)):
+                pieces.setdefault(name, []).append((owner, local.detach().cpu().contiguous()))
 
     for members in zero3_groups.values():
         exemplar = members[0][1]

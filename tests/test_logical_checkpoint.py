@@ -180,3 +180,37 @@ def test_zero3_buckets_under_tensor_and_expert_parallelism_convert_to_logical(tm
           "--output", str(tmp_path / "logical_c")])
     a, c = load_logical_checkpoint(tmp_path / "logical"), load_logical_checkpoint(tmp_path / "logical_c")
     assert set(a) == set(c) and all(torch.equal(a[n], c[n]) for n in a)
+
+
+def test_zero1_checkpoint_is_written_once_per_tensor_parallel_rank_and_converts(tmp_path):
+    """ZeRO-1/2 keep full weights on every data-parallel rank: one replica writes them (tensor-parallel shards: one writer
+    per TP rank), and the offline converter joins exactly one piece per TP rank (buffers, which every rank writes, are
+    taken from the lowest writer of each TP rank)."""
+    def recipe(path, parallel, steps, micro_batch):
+        cfg = {"seed": 1, "data": {"seq_len": 32, "micro_batch_size": micro_batch}, "model": MODEL, "parallel": parallel,
+               "training": {"max_steps": steps, "grad_accum_steps": 1, "lr": 1e-3}}
+        path.write_text(yaml.safe_dump(cfg))
+        return path
+
+    data = tmp_path / "tokens"
+    data.mkdir()
+    np.random.default_rng(0).integers(0, 256, size=20000, dtype=np.uint32).tofile(data / "tokens_00000.bin")
+    src = recipe(tmp_path / "src.yaml", {"dp_size": 2, "tp_size": 2, "use_sp": True, "zero_stage": 1}, 2, 2)
+    _run(["-m", "maltos_b200.tools.train", "--config", str(src), "--data", str(data), "--checkpoint-dir", str(tmp_path / "rt_a"),
+          "--checkpoint-every", "2", "--log-every", "1"], nproc=4)
+    step_a = tmp_path / "rt_a" / "step_00000002"
+    manifest = json.loads((step_a / "manifest.json").read_text())
+    writers = {e["source_rank"] for r in manifest["ranks"] for e in r["entries"] if e["state_key"].endswith("proj.weight")}
+    assert writers == {0, 1}, writers                       # the two TP ranks of data-parallel replica 0
+    _run(["-m", "maltos_b200.tools.convert_checkpoint", "runtime-to-logical", "--checkpoint", str(step_a), "--output", str(tmp_path / "logical")])
+    logical = load_logical_checkpoint(tmp_path / "logical")
+    # the same training as ZeRO-0 in one process gives the same weights (fp32, summation order aside)
+    single = recipe(tmp_path / "single.yaml", {}, 2, 4)
+    _run(["-m", "maltos_b200.tools.train", "--config", str(single), "--data", str(data), "--checkpoint-dir", str(tmp_path / "rt_s"),
+          "--checkpoint-every", "2", "--log-every", "1"])
+    _run(["-m", "maltos_b200.tools.convert_checkpoint", "runtime-to-logical", "--checkpoint", str(tmp_path / "rt_s" / "step_00000002"),
+          "--output", str(tmp_path / "logical_s")])
+    want = load_logical_checkpoint(tmp_path / "logical_s")
+    assert set(want) == set(logical)
+    for name in want:
+        assert torch.allclose(want[name], logical[name], atol=2e-5), (name, (want[name] - logical[name]).abs().max())
