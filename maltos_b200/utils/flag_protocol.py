@@ -218,5 +218,34 @@ def ring_publish(world: int, calls: int, *, barrier_before_overwrite: bool = Tru
     return programs
 
 
-__all__ = ["Exploration", "ProtocolDeadlock", "ProtocolViolation", "alternating_buffers_with_barrier", "explore", "pull_collective",
+def owner_reduce_and_push(world: int, steps: int, *, barrier_after_reduce: bool = True, barrier_after_push: bool = True) -> dict:
+    """Peer-memory mode of the sharded optimizers (``runtime/plugins/zero1.py``, ``csrc/zero_fused.cu``): backward fills the
+    rank's flat gradient bucket; barrier G1; the owner of shard ``r`` reads slice ``r`` of every rank's bucket
+    (``peer_reduce_shard``); barrier G2; AdamW on the own shard stores the new slice into every rank's parameter buffer
+    (``adamw_push``); barrier G3; the next forward / backward reads all slices of the own parameter buffer and overwrites the
+    gradient bucket. Without G3 a rank reads a parameter slice that a peer has not stored yet; without G2 AND G3 a fast rank's
+    next backward also overwrites a bucket that a peer still reads (both rejected by the exploration). G2 alone is redundant
+    while G3 (or the all-gather that replaces the push) follows: every rank enters it after its reads. The plugin keeps G2:
+    one more one-element all-reduce per step, and the reduction stays safe whatever follows it."""
+    members = tuple(f"rank{r}" for r in range(world))
+    programs = {}
+    for me in range(world):
+        prog = []
+        for n in range(1, steps + 1):
+            prog += [("read", ("param", me, owner), n - 1) for owner in range(world)]          # forward + backward of step n
+            prog += [("write", ("grad", me, shard), n) for shard in range(world)]
+            prog.append(("barrier", f"G1.{n}", members))
+            prog += [("read", ("grad", src, me), n) for src in range(world)]
+            if barrier_after_reduce:
+                prog.append(("barrier", f"G2.{n}", members))
+            prog += [("write", ("param", dst, me), n) for dst in range(world)]
+            if barrier_after_push:
+                prog.append(("barrier", f"G3.{n}", members))
+        prog += [("read", ("param", me, owner), steps) for owner in range(world)]
+        programs[f"rank{me}"] = prog
+    return programs
+
+
+__all__ = ["Exploration", "ProtocolDeadlock", "ProtocolViolation", "alternating_buffers_with_barrier", "explore", "owner_reduce_and_push",
+           "pull_collective",
            "push_with_back_pressure", "ring_publish"]

@@ -48,6 +48,16 @@ def test_ring_publish_barriers(world):
     fp.explore(fp.ring_publish(world, 3, backward=True, buffers=2, barrier_before_overwrite=False))
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_owner_side_reduction_and_parameter_push_need_both_barriers(world):
+    assert fp.explore(fp.owner_reduce_and_push(world, 3)).states > 0
+    assert fp.explore(fp.owner_reduce_and_push(world, 3, barrier_after_reduce=False)).states > 0      # G3 covers for G2
+    with pytest.raises(fp.ProtocolViolation):      # a fast rank's next backward overwrites a bucket that a peer still reads
+        fp.explore(fp.owner_reduce_and_push(world, 2, barrier_after_reduce=False, barrier_after_push=False))
+    with pytest.raises(fp.ProtocolViolation):      # a rank reads a parameter slice its owner has not stored yet
+        fp.explore(fp.owner_reduce_and_push(world, 2, barrier_after_push=False))
+
+
 def test_explorer_reports_deadlock_and_overlapping_writes():
     with pytest.raises(fp.ProtocolDeadlock):
         fp.explore({"a": [("wait", "never", 1)], "b": [("set", "other", 1)]})
