@@ -49,3 +49,29 @@ def test_probe_only_entry_points_are_not_called_from_the_package():
     called = {name for _, _, name, _ in _python_calls()}
     assert not called & {"mb_gemm_set_trace", "mb_gemm_set_debug_mode", "mb_gemm_set_debug_stages", "mb_gemm_set_debug_max_pairs",
                          "mb_gemm_debug_descriptor", "mb_flash_probe_read", "mb_pull_probe_read"}
+
+
+def test_every_polling_loop_in_the_kernels_has_a_deadline_and_nothing_traps():
+    """A wait on an mbarrier, a flag or a peer must give up after a time limit and report through the status words (a
+    hung kernel takes the GPU with it): every open-ended loop that polls has a ``globaltimer`` deadline within its body,
+    and no kernel source uses ``__trap()`` or a device ``assert``."""
+    import re
+
+    polls = re.compile(r"try_wait|ld_acquire|acquire_sys|x_tag\[|volatile")
+    opened = re.compile(r"\bwhile\s*\((?!0\))")
+    checked = 0
+    csrc = ROOT / "maltos_b200" / "csrc"
+    for path in sorted(csrc.glob("*.cu")) + sorted(csrc.glob("*.cuh")) + sorted(csrc.glob("*.h")):
+        lines = path.read_text().splitlines()
+        for i, line in enumerate(lines):
+            code = line.split("//")[0]
+            assert "__trap" not in code, (path.name, i + 1)
+            assert not re.search(r"(?<!static_)\bassert\s*\(", code), (path.name, i + 1)
+            if not opened.search(code):
+                continue
+            body = "\n".join(l.split("//")[0] for l in lines[i:i + 14])
+            if not polls.search(body):
+                continue                 # a host loop or a search over indices
+            checked += 1
+            assert re.search(r"globaltimer_ns\(\)\s*-\s*t0\s*>\s*limit", body), f"{path.name}:{i + 1}: polling loop without a deadline"
+    assert checked >= 4
