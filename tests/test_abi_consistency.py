@@ -78,8 +78,8 @@ def test_every_polling_loop_in_the_kernels_has_a_deadline_and_nothing_traps():
 
 
 def test_no_source_names_a_multicast_bulk_load_or_a_batched_memcpy_call():
-    """Two things this code base must never contain: a TMA / bulk LOAD with cluster multicast (``tcgen05.commit`` with
-    multicast is a barrier arrive, not a load, and is used by the CTA-pair GEMM), and the batched memcpy entry points of
+    """Two things this code base must never contain: a TMA / bulk LOAD with the cluster-multicast qualifier (``tcgen05.commit`` with
+    that qualifier is a barrier arrive, not a load, and is used by the CTA-pair GEMM), and the batched memcpy entry points of
     the CUDA runtime / driver (built from pieces here so that this file does not name them either)."""
     batched = [a + "Memcpy" + b + "Batch" + "Async" for a in ("cuda", "cu") for b in ("", "3D")]
     for path in sorted(ROOT.rglob("*")):
@@ -88,6 +88,7 @@ def test_no_source_names_a_multicast_bulk_load_or_a_batched_memcpy_call():
         text = path.read_text(errors="ignore")
         for name in batched:
             assert name not in text, (path, name)
+        needle = "multicast" + "::cluster"
         for i, line in enumerate(text.splitlines()):
-            if "multicast::cluster" in line:
-                assert "cp.async.bulk" not in line and "tcgen05.commit" in line, (path, i + 1)
+            if needle in line:
+                assert "cp.async" + ".bulk" not in line and "tcgen05.commit" in line, (path, i + 1)
