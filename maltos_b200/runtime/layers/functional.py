@@ -53,6 +53,8 @@ def _narrow_mine(t: torch.Tensor, group, dim: int) -> torch.Tensor:
     world, rank = group_size(group), group_rank(group)
     if world == 1:
         return t
+    if t.shape[dim] % world:      # a floor division here would silently drop the last tokens of every row
+        raise ValueError(f"sequence-parallel split: dim {dim} of size {t.shape[dim]} is not divisible by group size {world}")
     per = t.shape[dim] // world
     return t.narrow(dim, rank * per, per).contiguous()
 

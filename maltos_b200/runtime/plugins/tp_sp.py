@@ -150,9 +150,14 @@ class TpSpPlugin(TensorParallelTransformPlugin):
 
         return hook
 
+    def _check_divisible(self, size: int, dim: int) -> None:
+        if size % self.world_size:        # a floor division would silently drop the last tokens of every row
+            raise ValueError(f"sequence parallelism needs dim {dim} (size {size}) divisible by the tensor-parallel size {self.world_size}")
+
     def _narrow_ids_hook(self, dim: int):
         def hook(module, args):
             ids, *rest = args
+            self._check_divisible(ids.size(dim), dim)
             per = ids.size(dim) // self.world_size
             return (ids.narrow(dim, self.rank * per, per), *rest)
 
@@ -160,6 +165,7 @@ class TpSpPlugin(TensorParallelTransformPlugin):
 
     def _narrow_output_hook(self, dim: int):
         def hook(module, args, output):
+            self._check_divisible(output.size(dim), dim)
             per = output.size(dim) // self.world_size
             return output.narrow(dim, self.rank * per, per)
 

@@ -40,8 +40,22 @@ def validate_args(args: argparse.Namespace, world_size: int) -> None:
         raise ValueError(f"world_size={world_size} must equal dp_size * pp_size * cp_size * tp_size={expected}")
     if args.use_sp and args.tp_size <= 1:
         raise ValueError("--use-sp requires --tp-size > 1")
+    if args.use_sp and not args.hdp_balanced and (args.seq_len // max(args.cp_size, 1)) % args.tp_size:
+        raise ValueError(f"--use-sp splits the (context-parallel share of the) sequence over the tensor-parallel ranks: "
+                         f"--seq-len={args.seq_len} / cp={args.cp_size} must be divisible by --tp-size={args.tp_size}")
     if args.cp_size > 1 and args.seq_len % args.cp_size:
         raise ValueError("--cp-size requires --seq-len divisible by cp_size for CP v0")
+    heads, kv_heads = args.n_heads, args.n_kv_heads or args.n_heads
+    if heads < 1 or kv_heads < 1 or heads % kv_heads:
+        raise ValueError(f"--n-heads={heads} must be a positive multiple of --n-kv-heads={kv_heads}")
+    if args.dim % heads:
+        raise ValueError(f"--dim={args.dim} must be divisible by --n-heads={heads}")
+    if args.tp_size > 1:
+        # attention is split by heads (a rank owns whole query heads and the key / value heads they share), the MLP by columns
+        for flag, value in (("--n-heads", heads), ("--n-kv-heads", kv_heads), ("--hidden-size", args.hidden_size)):
+            if value % args.tp_size:
+                raise ValueError(f"{flag}={value} must be divisible by --tp-size={args.tp_size} (key / value heads are not replicated "
+                                 "across tensor-parallel ranks)")
     if args.hdp_balanced:
         if args.cp_size != 1:
             raise ValueError("--hdp-balanced requires --cp-size 1; HDP replaces fixed CP")

@@ -318,3 +318,27 @@ def test_wandb_that_cannot_start_degrades_to_the_other_sinks(monkeypatch, capsys
     monkeypatch.setenv("MALTOS_B200_WANDB_REQUIRED", "1")
     with pytest.raises(RuntimeError):
         cli._build_logging(args, 0)
+
+
+def test_head_counts_that_tensor_parallelism_cannot_split_are_rejected_up_front():
+    from maltos_b200.train import cli, flags as F
+
+    base = ["--model", "llama", "--dim", "64", "--hidden-size", "128", "--n-layers", "2", "--vocab-size", "256", "--seq-len", "32"]
+    ok = F.parse_args_from(base + ["--n-heads", "8", "--n-kv-heads", "4", "--tp-size", "4"], require_data=False)
+    cli.validate_args(ok, 4)
+    for extra, world, needle in ((["--n-heads", "8", "--n-kv-heads", "2", "--tp-size", "4"], 4, "--n-kv-heads=2 must be divisible by --tp-size=4"),
+                                 (["--n-heads", "6", "--n-kv-heads", "4"], 1, "multiple of --n-kv-heads"),
+                                 (["--n-heads", "5", "--n-kv-heads", "5"], 1, "--dim=64 must be divisible")):
+        with pytest.raises(ValueError, match=needle):
+            cli.validate_args(F.parse_args_from(base + extra, require_data=False), world)
+
+
+def test_sequence_parallel_split_refuses_lengths_it_would_truncate():
+    from maltos_b200.train import cli, flags as F
+
+    base = ["--model", "llama", "--dim", "64", "--n-heads", "4", "--hidden-size", "128", "--n-layers", "2", "--vocab-size", "256", "--tp-size", "4", "--use-sp"]
+    cli.validate_args(F.parse_args_from(base + ["--seq-len", "32"], require_data=False), 4)
+    with pytest.raises(ValueError, match="must be divisible by --tp-size=4"):
+        cli.validate_args(F.parse_args_from(base + ["--seq-len", "30"], require_data=False), 4)
+    with pytest.raises(ValueError, match="must be divisible by --tp-size=4"):      # 48 / cp 2 = 24 per context-parallel rank: fine; 40 / 2 = 20: fine; 36 / 2 = 18: not
+        cli.validate_args(F.parse_args_from(base + ["--seq-len", "36", "--cp-size", "2"], require_data=False), 8)
