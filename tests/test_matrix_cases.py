@@ -29,6 +29,9 @@ MODELS = {
              "--moe-aux-loss-coef", "0"],
     "moe": ["--model", "tiny_moe", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "96", "--n-layers", "2", "--num-experts", "8",
             "--moe-aux-loss-coef", "0"],
+    # more experts than a rank has tokens: on every rank some experts get no token and therefore no gradient
+    "moe64": ["--model", "tiny_moe", "--dim", "64", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "32", "--n-layers", "2", "--num-experts", "64",
+              "--moe-aux-loss-coef", "0"],
 }
 COMMON = ["--vocab-size", str(VOCAB), "--seq-len", str(SEQ), "--lr", "1e-3", "--weight-decay", "0.01", "--grad-clip", "0.1", "--seed", "5",
           "--precision", "fp32", "--disable-metrics"]
@@ -146,6 +149,10 @@ CASES = {
     "moe_top2_dp2_cp4_ep2_ring_zero3": C("moe", "--dp-size 2 --cp-size 4 --ep-size 2 --cp-attn-core ring --cp-token-planner fixed_zigzag --zero-stage 3", common="--moe-top-k 2"),
     "moe_dp2_tp4_ep2": C("moe4", "--dp-size 2 --tp-size 4 --ep-size 2"),
     "moe_dp2_tp4_sp_ep2_zero1": C("moe4", "--dp-size 2 --tp-size 4 --use-sp --ep-size 2 --zero-stage 1"),
+    "moe64_dp4_tp2_bucket_accum2": C("moe64", "--dp-size 4 --tp-size 2 --ddp-mode bucket", accum=2),
+    "moe64_dp8_async": C("moe64", "--dp-size 8 --ddp-mode async"),
+    "moe64_dp8_zero3": C("moe64", "--dp-size 8 --zero-stage 3"),
+    "moe64_dp4_tp2_sp_ep4_zero2_accum2": C("moe64", "--dp-size 4 --tp-size 2 --use-sp --ep-size 4 --zero-stage 2", accum=2),
     "moe_dp4_tp2_sp": C("moe", "--dp-size 4 --tp-size 2 --use-sp"),
     "moe_dp4_tp2": C("moe", "--dp-size 4 --tp-size 2"),
     # load-balance loss switched on: it is a statistic of the LOCAL batch, so these are compared with each other (same data
@@ -221,6 +228,7 @@ def _args(case):
 
 def _micro_batch(batch, dp_rank, dp, accum, m):
     rows = GLOBAL_ROWS // (dp * accum)
+    assert rows >= 1, "the case leaves no row for a micro-step"
     lo = (m * dp + dp_rank) * rows
     return {k: v[lo:lo + rows].clone() for k, v in batch.items()}
 
