@@ -191,6 +191,30 @@ def _fused_gather_ok(symm, M: int, N: int, K: int) -> bool:
     return symm.world <= 4 or 2.0 * M * N * K >= 1.5e11
 
 
+def workspace_plan(world: int, workspace_bytes: int) -> dict[str, int]:
+    """Symmetric transfer buffers the sequence-parallel ops of a group of ``world`` ranks will ask for, with their sizes,
+    given ``workspace_bytes`` = two copies (call parities) of one micro-batch of hidden states, ``2 * tokens * hidden *
+    itemsize``: every tensor that crosses the group in forward or backward has the hidden width. Follows the automatic path
+    selection (``_fused_scatter_ok`` / ``_fused_gather_ok`` without environment overrides): gathered operand of the fused
+    all-gather GEMM, published rows of the pull all-gather (one rank's share), and the reduce-scatter staging - per-source
+    slots for two ranks, the rank's own partial for larger groups."""
+    if world < 2:
+        return {}
+    plan = {"sp_gather": workspace_bytes, "sp_publish": -(-workspace_bytes // world)}
+    plan["sp_scatter" if world <= 2 else "sp_partial"] = workspace_bytes
+    return plan
+
+
+def prewarm_workspace(symm, workspace_bytes: int) -> dict[str, int]:
+    """Allocates the buffers of :func:`workspace_plan` now (collective over the group), so that neither the rendezvous nor a
+    later growth falls into the first training step, where a sharded optimizer issues collectives on other groups at
+    the same time. Returns the sizes actually held."""
+    held = {}
+    for name, nbytes in workspace_plan(symm.world, int(workspace_bytes)).items():
+        held[name] = symm.ensure_buffer(name, nbytes).nbytes
+    return held
+
+
 def all_gather_gemm_unfused(x2: torch.Tensor, w: torch.Tensor, symm, B: int, rows: int, *, b_mn: bool):
     """Same contract as :func:`all_gather_gemm` with the all-gather as a launch of its own (pull kernel over peer memory,
     NCCL without it) in front of a plain GEMM launch; ``gathered`` is an ordinary tensor."""

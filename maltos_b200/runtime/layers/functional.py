@@ -23,6 +23,36 @@ from maltos_b200.utils.distributed import (all_gather_single, all_reduce_tensor,
                                            pairwise_send_recv_async, reduce_scatter_single)
 
 
+def native_comm_overlap_workspace_bytes(*, micro_batch_size: int, seq_len: int, hidden_size: int, tp_size: int, dtype: torch.dtype) -> int:
+    """Size of the largest symmetric transfer buffer the fused tensor / sequence-parallel ops need for one micro-batch:
+    two copies (alternating by call, so that a peer may still read call ``n`` while call ``n + 1`` is written) of the
+    FULL-sequence hidden states. The reference's estimate (``runtime/layers/functional.py:85-114``) is two copies of the
+    LOCAL shard, because its library op keeps only the local output in symmetric memory; here the gathered operand
+    (all-gather -> GEMM) and the un-reduced partial (GEMM -> reduce-scatter) live there, which is ``tp_size`` times that."""
+    for name, value in (("micro_batch_size", micro_batch_size), ("seq_len", seq_len), ("hidden_size", hidden_size), ("tp_size", tp_size)):
+        if value < 1:
+            raise ValueError(f"{name} must be >= 1, got {value}")
+    if seq_len % tp_size:
+        raise ValueError(f"seq_len={seq_len} must be divisible by tp_size={tp_size}")
+    return 2 * micro_batch_size * seq_len * hidden_size * torch.empty((), dtype=dtype).element_size()
+
+
+def prewarm_native_comm_overlap_workspace(group, *, min_workspace_bytes: int) -> bool:
+    """Creates the group's symmetric-memory context and its transfer buffers before the first step (reference
+    ``runtime/layers/functional.py:117-160``). False where the fused path does not exist: no CUDA, a backend other than
+    NCCL, no peer access inside the group."""
+    if group is None or not torch.cuda.is_available() or dist.get_backend(group) != "nccl":
+        return False
+    from maltos_b200.ops import comm, fused_tp
+
+    symm = comm.context_for(group)
+    if symm is None:
+        return False
+    fused_tp.prewarm_workspace(symm, int(min_workspace_bytes))
+    torch.cuda.synchronize()
+    return True
+
+
 def _move_dim0(t: torch.Tensor, dim: int) -> torch.Tensor:
     return t if dim == 0 else t.transpose(0, dim)
 

@@ -18,8 +18,9 @@ head, row-parallel biases) get partial gradients; their sum over the TP group is
 PRE_STEP when the runtime owns the optimizer, or per micro-step through gradient hooks when a ZeRO plugin consumes
 gradients during backward.
 
-``native_comm_overlap`` is accepted for interface compatibility (reference ``tp_sp.py:108-119``): on CUDA the fused
-sm_100a all-gather->GEMM / GEMM->reduce-scatter kernels are always the path when the TP group has peer access.
+``native_comm_overlap`` (reference ``tp_sp.py:108-119``): on CUDA the fused sm_100a all-gather->GEMM / GEMM->reduce-scatter
+kernels are always the path when the TP group has peer access; the flag moves the creation of the group's symmetric-memory
+context - and, with ``native_comm_overlap_workspace_bytes``, of its transfer buffers - from the first step to setup.
 """
 from __future__ import annotations
 
@@ -31,7 +32,7 @@ import torch.nn as nn
 
 from maltos_b200.parallel.protocols import TpSpParallelizableModule
 from maltos_b200.parallel.specs import TpSpComm, TpSpShardAxis
-from maltos_b200.runtime.layers.functional import all_gather
+from maltos_b200.runtime.layers.functional import all_gather, prewarm_native_comm_overlap_workspace
 from maltos_b200.runtime.layers.linear import ColumnParallelLinear, RowParallelLinear
 from maltos_b200.runtime.plugin import PluginId
 from maltos_b200.runtime.types import ParamRole, RuntimePhase, SetupPhase
@@ -86,9 +87,13 @@ class TpSpPlugin(TensorParallelTransformPlugin):
             self._find_projection_groups(model)
         elif phase is SetupPhase.FINALIZE:
             if self.native_comm_overlap:
-                from maltos_b200.ops import comm
+                if self.native_comm_overlap_workspace_bytes:
+                    self.native_comm_overlap_workspace_prewarmed = prewarm_native_comm_overlap_workspace(
+                        self.sp_group, min_workspace_bytes=int(self.native_comm_overlap_workspace_bytes))
+                else:           # context (rendezvous, signal pad) only; the transfer buffers grow on first use
+                    from maltos_b200.ops import comm
 
-                self.native_comm_overlap_workspace_prewarmed = comm.context_for(self.sp_group) is not None
+                    self.native_comm_overlap_workspace_prewarmed = comm.context_for(self.sp_group) is not None
             self._wire_sequence_rules(model)
             self._collect_partial_params(model)
         return model

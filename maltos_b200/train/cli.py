@@ -237,8 +237,17 @@ def _build_runtime(args: argparse.Namespace, model: nn.Module, device: torch.dev
     sched_factory = None if weights_only else _build_scheduler_factory(args)
     plugins: list = []
     clip_in_core = None
-    if args.tp_size > 1:
-        plugins.append(TpSpPlugin(native_comm_overlap=bool(getattr(args, "tp_native_comm_overlap", False))) if args.use_sp else TensorParallelPlugin())
+    if args.tp_size > 1 and args.use_sp:
+        overlap = bool(getattr(args, "tp_native_comm_overlap", False))
+        workspace = None
+        if overlap:       # the symmetric transfer buffers are sized and allocated at setup, not inside the first step
+            from maltos_b200.runtime.layers.functional import native_comm_overlap_workspace_bytes
+
+            workspace = native_comm_overlap_workspace_bytes(micro_batch_size=args.micro_batch_size, seq_len=args.seq_len // max(args.cp_size, 1),
+                                                            hidden_size=args.dim, tp_size=args.tp_size, dtype=dtype or torch.float32)
+        plugins.append(TpSpPlugin(native_comm_overlap=overlap, native_comm_overlap_workspace_bytes=workspace))
+    elif args.tp_size > 1:
+        plugins.append(TensorParallelPlugin())
     if args.hdp_balanced:
         from maltos_b200.runtime.plugins.hdp import ByteScaleHdpPlugin
 

@@ -342,3 +342,58 @@ def test_sequence_parallel_split_refuses_lengths_it_would_truncate():
         cli.validate_args(F.parse_args_from(base + ["--seq-len", "30"], require_data=False), 4)
     with pytest.raises(ValueError, match="must be divisible by --tp-size=4"):      # 48 / cp 2 = 24 per context-parallel rank: fine; 40 / 2 = 20: fine; 36 / 2 = 18: not
         cli.validate_args(F.parse_args_from(base + ["--seq-len", "36", "--cp-size", "2"], require_data=False), 8)
+
+
+def test_tensor_parallel_overlap_workspace_is_sized_and_prewarmed_at_setup(monkeypatch):
+    """The kind of the reference's ``tests/tp_native_overlap_workspace.py``: size estimate, prewarm on / off, command-line
+    wiring, prewarm at plugin finalisation."""
+    from unittest import mock
+
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    from maltos_b200.ops import comm, fused_tp
+    from maltos_b200.runtime.layers import functional as Fn
+    from maltos_b200.runtime.plugins import tp_sp
+    from maltos_b200.runtime.types import SetupPhase
+    from maltos_b200.train import cli, flags as F
+
+    one = Fn.native_comm_overlap_workspace_bytes(micro_batch_size=1, seq_len=4096, hidden_size=5120, tp_size=2, dtype=torch.bfloat16)
+    two = Fn.native_comm_overlap_workspace_bytes(micro_batch_size=2, seq_len=4096, hidden_size=5120, tp_size=2, dtype=torch.bfloat16)
+    assert one == 80 * 2**20 and two == 160 * 2**20          # two parities of the full-sequence hidden states
+    with pytest.raises(ValueError, match="must be divisible"):
+        Fn.native_comm_overlap_workspace_bytes(micro_batch_size=1, seq_len=4095, hidden_size=5120, tp_size=2, dtype=torch.bfloat16)
+    assert fused_tp.workspace_plan(2, 1024) == {"sp_gather": 1024, "sp_publish": 512, "sp_scatter": 1024}
+    assert fused_tp.workspace_plan(8, 1024) == {"sp_gather": 1024, "sp_publish": 128, "sp_partial": 1024}
+    assert fused_tp.workspace_plan(1, 1024) == {}
+
+    group, symm = object(), mock.Mock()
+    symm.world = 4
+    symm.ensure_buffer.side_effect = lambda name, nbytes: mock.Mock(nbytes=nbytes)
+    with mock.patch.object(torch.cuda, "is_available", return_value=True), mock.patch.object(torch.cuda, "synchronize") as sync, \
+            mock.patch.object(dist, "get_backend", return_value="nccl"), mock.patch.object(comm, "context_for", return_value=symm) as ctx_for:
+        assert Fn.prewarm_native_comm_overlap_workspace(group, min_workspace_bytes=4096) is True
+    ctx_for.assert_called_once_with(group)
+    assert {c.args for c in symm.ensure_buffer.call_args_list} == {("sp_gather", 4096), ("sp_publish", 1024), ("sp_partial", 4096)}
+    sync.assert_called_once_with()
+    with mock.patch.object(torch.cuda, "is_available", return_value=True), mock.patch.object(dist, "get_backend", return_value="gloo"), \
+            mock.patch.object(comm, "context_for") as ctx_for:
+        assert Fn.prewarm_native_comm_overlap_workspace(group, min_workspace_bytes=1) is False
+    ctx_for.assert_not_called()
+
+    args = F.parse_args_from(["--model", "llama", "--dim", "384", "--n-heads", "6", "--hidden-size", "1536", "--n-layers", "2", "--vocab-size", "256",
+                              "--seq-len", "512", "--micro-batch-size", "1", "--dp-size", "2", "--tp-size", "2", "--use-sp", "--zero-stage", "3",
+                              "--precision", "bf16", "--tp-native-comm-overlap"], require_data=False)
+    runtime = cli._build_runtime(args, nn.Linear(1, 1), torch.device("cpu"))
+    plugin = next(p for p in runtime.plugins if isinstance(p, tp_sp.TpSpPlugin))
+    assert plugin.native_comm_overlap is True and plugin.native_comm_overlap_workspace_bytes == 2 * 512 * 384 * 2
+
+    plugin = tp_sp.TpSpPlugin(native_comm_overlap=True, native_comm_overlap_workspace_bytes=80 * 2**20)
+    plugin.runtime = mock.Mock()
+    plugin.runtime.get_group.return_value = group
+    with mock.patch.object(tp_sp, "prewarm_native_comm_overlap_workspace", return_value=True) as prewarm, \
+            mock.patch.object(tp_sp.TensorParallelTransformPlugin, "on_setup_phase", lambda self, phase, model: model), \
+            mock.patch.object(tp_sp.TpSpPlugin, "_wire_sequence_rules"), mock.patch.object(tp_sp.TpSpPlugin, "_collect_partial_params"):
+        plugin.on_setup_phase(SetupPhase.FINALIZE, nn.Linear(1, 1))
+    prewarm.assert_called_once_with(group, min_workspace_bytes=80 * 2**20)
+    assert plugin.native_comm_overlap_workspace_prewarmed is True
