@@ -124,3 +124,26 @@ def test_zero3_checkpoint_roundtrip_on_two_ranks(tmp_path):
     assert len(bucket["logical_names"]) == len(bucket["logical_shapes"]) >= 1
     assert len(bucket["physical_shape"]) == 1 and bucket["source_rank"] == 1          # a flat shard, written by its owner
     assert manifest["optimizer_source_ranks"] == [0, 1]
+
+
+def _buffer_case(rank, world, zero_stage):
+    from maltos_b200.train import cli, flags as F
+
+    a = F.parse_args_from(["--model", "olmo2", "--dim", "16", "--n-heads", "4", "--hidden-size", "32", "--n-layers", "2", "--vocab-size", "32", "--seq-len", "8",
+                           "--dp-size", "2", "--zero-stage", str(zero_stage), "--precision", "bf16"], require_data=False)
+    core = cli._build_runtime(a, cli._build_model(a), torch.device("cpu"))
+    core.setup()
+    buffers = {n: (b.dtype, b.device.type) for n, b in core.model.named_buffers()}
+    params = {p.dtype for p in core.model.parameters()}
+    core.close()
+    return buffers, params
+
+
+def test_buffers_after_zero3_setup():
+    """Buffers outside the sharded modules are materialised with the model (kind of the reference's
+    ``tests/zero3_buffer_materialization.py``); the rotary tables stay fp32 here by design, the parameters are bf16."""
+    for zero_stage in (0, 3):
+        buffers, params = run_distributed(_buffer_case, 2, zero_stage)[0]
+        rotary = {n: v for n, v in buffers.items() if n.endswith(("cos", "sin"))}
+        assert len(rotary) >= 2 and all(v == (torch.float32, "cpu") for v in rotary.values()), rotary
+        assert params == {torch.bfloat16}

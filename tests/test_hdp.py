@@ -267,3 +267,18 @@ def test_idle_hdp_ranks_still_join_every_collective(zero_stage):
     for step in range(2):
         total = sum(r[0][step] for r in results) / 4
         assert abs(total - ref[step]) < 2e-4, (step, total, ref[step])
+
+
+def test_command_line_builds_the_cost_model_and_counts_the_global_batch():
+    """The HDP flags reach the config, and a step's token count has no data-parallel factor under HDP: every rank cuts
+    its piece out of ONE canonical batch (reference ``tests/hdp_cli_cost_model.py``)."""
+    from maltos_b200.train import cli, flags as F
+
+    base = ["--model", "tiny", "--seq-len", "64", "--micro-batch-size", "3", "--grad-accum-steps", "2", "--dp-size", "4"]
+    a = F.parse_args_from(base + ["--hdp-balanced", "--hdp-partition-tokens", "16", "--hdp-cost-alpha", "1.25", "--hdp-cost-beta", "3.5",
+                                  "--hdp-cost-gamma", "7.0", "--hdp-balance-delta", "9"], require_data=False)
+    cfg = cli._build_hdp_config(a)
+    assert cfg.partition_tokens == 16 and cfg.balance_delta == 9
+    assert (cfg.cost_model.alpha, cfg.cost_model.beta, cfg.cost_model.gamma) == (1.25, 3.5, 7.0)
+    assert cli._global_batch_tokens(a) == 3 * 64 * 2
+    assert cli._global_batch_tokens(F.parse_args_from(base, require_data=False)) == 3 * 64 * 4 * 2
