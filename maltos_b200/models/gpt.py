@@ -10,7 +10,6 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from maltos_b200.ops.attention import causal_attention
-from maltos_b200.parallel.specs import ContextParallelSpec, PipelineParallelSpec
 from maltos_b200.utils.losses import causal_cross_entropy
 
 from .common import ParsedBatch

@@ -5,7 +5,6 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-import torch
 import torch.nn as nn
 
 from maltos_b200.ops.rope import apply_rope

@@ -9,8 +9,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from maltos_b200.parallel.specs import (ContextParallelSpec, ExpertParallelSpec, PipelineParallelSpec, TpSpParallelSpec,
-                                        TpSpShardAxis, TpSpShardRule)
+from maltos_b200.parallel.specs import ContextParallelSpec, ExpertParallelSpec, PipelineParallelSpec, TpSpParallelSpec
 from maltos_b200.runtime.types import LossOutput, PipelineOutput
 
 from .common import Linear, ParsedBatch, lm_logits, lm_loss

@@ -8,7 +8,6 @@ for every variable-length batch would be slow and fragile (reference ``runtime/l
 from __future__ import annotations
 
 import torch
-import torch.distributed as dist
 
 from maltos_b200.utils.distributed import pairwise_send_recv_async
 

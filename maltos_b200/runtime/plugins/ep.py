@@ -16,7 +16,6 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from maltos_b200.parallel.expert_interfaces import ExpertParallelMoEModule
 from maltos_b200.parallel.protocols import ExpertParallelizableModule
 from maltos_b200.runtime.buffer_allocator import BufferPolicy, acquire_buffer
 from maltos_b200.runtime.layers.moe import ExpertParallelMoE

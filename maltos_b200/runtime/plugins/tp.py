@@ -9,7 +9,6 @@ records logical vs physical shapes and the TP-sharded / TP-replicated axes (refe
 """
 from __future__ import annotations
 
-import torch
 import torch.distributed as dist
 import torch.nn as nn
 

@@ -25,7 +25,6 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from maltos_b200.runtime.buffer_allocator import BufferPolicy, acquire_buffer, release_buffer
 from maltos_b200.runtime.mesh import MeshAxis
 from maltos_b200.runtime.plugin import PluginId
 from maltos_b200.runtime.types import ParamRole, RuntimePhase, SetupPhase

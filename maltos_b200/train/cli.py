@@ -26,7 +26,7 @@ from maltos_b200.parallel import (ContextParallelBatchSharder, ParallelPlan, Pip
 from maltos_b200.parallel.context_interfaces import ContextParallelAttentionCoreType
 from maltos_b200.parallel.context_token_planner import ContextTokenPlannerType
 from maltos_b200.runtime.core import RuntimeCore
-from maltos_b200.runtime.mesh import MeshConfig, validate_expert_parallel
+from maltos_b200.runtime.mesh import MeshConfig
 from maltos_b200.utils.distributed import distributed_barrier
 
 from .flags import build_runtime_spec, parse_args
