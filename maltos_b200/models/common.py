@@ -16,18 +16,18 @@ from maltos_b200.ops.cross_entropy import linear_cross_entropy
 from maltos_b200.ops.gemm import linear
 from maltos_b200.ops.grouped import grouped_linear
 from maltos_b200.utils.activation_checkpoint import activation_checkpoint_context_fn
-from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
+from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, IGNORE_INDEX, INPUT_IDS_KEY, LABELS_KEY, LOSS_SCALE_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
                                          POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 from maltos_b200.utils.losses import causal_cross_entropy
 
 
 class ParsedBatch:
-    __slots__ = ("input_ids", "hidden_states", "labels", "position_offset", "position_ids", "sequence_ids", "loss_weight", "aux_loss_weight")
+    __slots__ = ("input_ids", "hidden_states", "labels", "position_offset", "position_ids", "sequence_ids", "loss_weight", "aux_loss_weight", "loss_scale")
 
     def __init__(self, batch: Any) -> None:
         self.hidden_states = self.labels = self.position_ids = self.sequence_ids = self.loss_weight = None
         self.position_offset = 0
-        self.aux_loss_weight = None
+        self.aux_loss_weight = self.loss_scale = None
         if isinstance(batch, dict):
             self.input_ids = batch.get(INPUT_IDS_KEY)
             self.hidden_states = batch.get(HIDDEN_STATES_KEY)
@@ -37,6 +37,7 @@ class ParsedBatch:
             self.sequence_ids = batch.get(SEQUENCE_IDS_KEY)
             self.loss_weight = batch.get(LOSS_WEIGHT_KEY)
             self.aux_loss_weight = batch.get(AUX_LOSS_WEIGHT_KEY)
+            self.loss_scale = batch.get(LOSS_SCALE_KEY)
         elif isinstance(batch, (tuple, list)):
             self.input_ids, self.labels = batch
         else:
@@ -109,7 +110,7 @@ def lm_logits(hidden: torch.Tensor, lm_head: nn.Module) -> torch.Tensor:
     return lm_head(hidden)
 
 
-def lm_loss(hidden: torch.Tensor, lm_head: nn.Module, labels: torch.Tensor, loss_weight=None) -> torch.Tensor:
+def lm_loss(hidden: torch.Tensor, lm_head: nn.Module, labels: torch.Tensor, loss_weight=None, loss_scale=None) -> torch.Tensor:
     """Mean next-token CE of ``lm_head(hidden)`` vs already-shifted ``labels``.
 
     Plain bias-free heads use the fused linear+CE op (no ``[tokens, vocab]`` logits kept). When the TP+SP plugin
@@ -135,6 +136,8 @@ def lm_loss(hidden: torch.Tensor, lm_head: nn.Module, labels: torch.Tensor, loss
         loss = _GroupSum.apply(local * (local_count.to(local.dtype) / global_count.to(local.dtype)), group)
     if loss_weight is not None:
         loss = loss * float(loss_weight)
+    if loss_scale is not None:          # a device scalar: no host read
+        loss = loss * loss_scale.to(device=loss.device, dtype=loss.dtype)
     return loss
 
 

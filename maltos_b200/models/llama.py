@@ -202,7 +202,7 @@ class LlamaForCausalLM(nn.Module):
             return lm_logits(h, self.lm_head)
         if b.input_ids is not None and b.labels.shape != b.input_ids.shape:
             raise ValueError(f"labels shape must match input_ids shape, got {b.labels.shape} vs {b.input_ids.shape}")
-        return lm_loss(h, self.lm_head, b.labels, b.loss_weight)
+        return lm_loss(h, self.lm_head, b.labels, b.loss_weight, b.loss_scale)
 
     # ---- parallel declarations
     def pipeline_parallel_spec(self) -> PipelineParallelSpec:

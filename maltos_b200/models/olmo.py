@@ -144,7 +144,7 @@ class OlmoForCausalLM(nn.Module):
             return lm_logits(h, self.lm_head)
         if b.input_ids is not None and b.labels.shape != b.input_ids.shape:
             raise ValueError(f"labels shape must match input_ids shape, got {b.labels.shape} vs {b.input_ids.shape}")
-        return lm_loss(h, self.lm_head, b.labels, b.loss_weight)
+        return lm_loss(h, self.lm_head, b.labels, b.loss_weight, b.loss_scale)
 
     def pipeline_parallel_spec(self) -> PipelineParallelSpec:
         return PipelineParallelSpec(head_layers=["embed_tokens"], pipe_layers=["layers"], tail_layers=["norm", "lm_head"])

@@ -176,7 +176,7 @@ class TinyMoETransformer(nn.Module):
             return lm_logits(h, self.lm_head)
         if b.input_ids is not None and b.labels.shape != b.input_ids.shape:
             raise ValueError(f"labels shape must match input_ids shape, got {b.labels.shape} vs {b.input_ids.shape}")
-        ce = lm_loss(h, self.lm_head, b.labels, b.loss_weight)
+        ce = lm_loss(h, self.lm_head, b.labels, b.loss_weight, b.loss_scale)
         if not want_aux:
             return ce
         total = ce + aux_loss

@@ -45,6 +45,7 @@ class PluginId(str, Enum):
     TORCH_PROFILER = "torch_profiler"
     COMPILE = "compile"
     CUDA_GRAPH = "cuda_graph"     # not in the reference: micro-step recorded into a CUDA graph
+    TOKEN_WEIGHTED_LOSS = "token_weighted_loss"     # not in the reference: loss averaged over targets across data-parallel ranks
 
 
 @runtime_checkable

@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from maltos_b200.runtime.buffer_allocator import BufferPolicy, acquire_buffer
 from maltos_b200.runtime.types import LossOutput, PipelineOutput, PpStatus
-from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_TARGET_COUNTS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
+from maltos_b200.utils.constants import (AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY, INPUT_IDS_KEY, LABELS_KEY, LOSS_SCALE_KEY, LOSS_TARGET_COUNTS_KEY, LOSS_WEIGHT_KEY, POSITION_IDS_KEY,
                                          POSITION_OFFSET_KEY, SEQUENCE_IDS_KEY)
 from maltos_b200.utils.distributed import all_reduce_tensor, irecv_tensor_async, isend_tensor_async
 from maltos_b200.utils.profiling import span
@@ -141,6 +141,8 @@ class PipelineStepRunner:
                 model_input[LABELS_KEY] = extract_labels(piece)
                 if isinstance(piece, dict) and LOSS_WEIGHT_KEY in piece:
                     model_input[LOSS_WEIGHT_KEY] = piece[LOSS_WEIGHT_KEY]
+                if isinstance(piece, dict) and LOSS_SCALE_KEY in piece:
+                    model_input[LOSS_SCALE_KEY] = piece[LOSS_SCALE_KEY]
         DefaultStepRunner.run_forward(runtime, model_input)
         out = runtime.state.outputs
 
@@ -293,6 +295,11 @@ def split_batch(batch, num_microbatches: int) -> list:
 
         for piece in pieces:
             piece[LOSS_WEIGHT_KEY] = target_fraction(piece[LOSS_TARGET_COUNTS_KEY])
+    if isinstance(batch, dict) and torch.is_tensor(batch.get(LOSS_SCALE_KEY)) and torch.is_tensor(batch.get("loss_row_targets")):
+        # token-weighted loss: a piece weighs by ITS targets (the runner averages the pieces): batch scale x piece / mean piece
+        whole = batch["loss_row_targets"].sum().clamp_min(1.0)
+        for piece in pieces:
+            piece[LOSS_SCALE_KEY] = batch[LOSS_SCALE_KEY] * piece["loss_row_targets"].sum() * float(num_microbatches) / whole
     return pieces
 
 

@@ -70,6 +70,8 @@ def validate_args(args: argparse.Namespace, world_size: int) -> None:
         if args.hdp_partition_tokens % 2:
             raise ValueError("--hdp-partition-tokens must be even for symmetric zigzag partitions")
         _build_hdp_config(args).validate_tp_sp_partition(tp_size=args.tp_size, use_sp=args.use_sp)
+    if getattr(args, "token_weighted_loss", False) and args.hdp_balanced:
+        raise ValueError("--token-weighted-loss is implied by --hdp-balanced (HDP weights every rank's loss by its targets)")
     if args.ep_size > 1 and args.dp_size % args.ep_size:
         raise ValueError("--ep-size must divide --dp-size")
     if args.ep_size > 1 and args.model != "tiny_moe":
@@ -254,6 +256,10 @@ def _build_runtime(args: argparse.Namespace, model: nn.Module, device: torch.dev
         plugins.append(ByteScaleHdpPlugin(config=_build_hdp_config(args)))
     elif args.cp_size > 1:
         plugins.append(ContextParallelPlugin())
+    if getattr(args, "token_weighted_loss", False):
+        from maltos_b200.runtime.plugins.token_weighted_loss import TokenWeightedLossPlugin
+
+        plugins.append(TokenWeightedLossPlugin())
     if args.ep_size > 1:
         plugins.append(ExpertParallelPlugin())
     if args.pp_size > 1:

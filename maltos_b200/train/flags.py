@@ -100,6 +100,8 @@ FLAGS: tuple[Flag, ...] = (
     # precision / clipping / fused scopes
     Flag("precision", str, "fp32", ("fp32", "bf16", "fp16"), yaml=("training.precision",)),
     Flag("grad_clip", float, None, yaml=("training.grad_clip",)),
+    # loss = mean over the targets of ALL data-parallel ranks of a micro-step instead of the mean of the ranks' means
+    Flag("token_weighted_loss", BOOL, False, yaml=("training.token_weighted_loss",)),
     Flag("compile", BOOL, False, yaml=("compile.enabled",)),
     Flag("compile_scope", str, "mlp", yaml=("compile.scope",)),
     Flag("compile_mode", str, "default", yaml=("compile.mode",)),

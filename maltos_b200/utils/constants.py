@@ -17,10 +17,14 @@ LOSS_TARGET_COUNTS_KEY = "loss_target_counts"
 #: weight of token-count based auxiliary losses (expert load balance) of a rank that holds ``1 / cp`` of every sequence:
 #: context-parallel gradients are SUMMED over the group, so an unweighted local term would count ``cp`` times
 AUX_LOSS_WEIGHT_KEY = "auxiliary_loss_weight"
+#: 0-dim tensor: this rank's targets x data-parallel size / targets of all data-parallel ranks in this micro-step
+#: (``runtime/plugins/token_weighted_loss.py``); multiplies the cross-entropy so that the data-parallel gradient average is
+#: the mean over TARGETS rather than the mean of the ranks' means
+LOSS_SCALE_KEY = "loss_scale"
 HIDDEN_STATES_KEY = "hidden_states"
 
 MODEL_BATCH_KEYS = (
     INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY,
-    POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY, AUX_LOSS_WEIGHT_KEY, HIDDEN_STATES_KEY,
+    POSITION_OFFSET_KEY, LOSS_WEIGHT_KEY, AUX_LOSS_WEIGHT_KEY, LOSS_SCALE_KEY, HIDDEN_STATES_KEY,
 )
 SFT_BATCH_KEYS = (INPUT_IDS_KEY, LABELS_KEY, POSITION_IDS_KEY, SEQUENCE_IDS_KEY)
