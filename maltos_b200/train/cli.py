@@ -70,6 +70,9 @@ def validate_args(args: argparse.Namespace, world_size: int) -> None:
         if args.hdp_partition_tokens % 2:
             raise ValueError("--hdp-partition-tokens must be even for symmetric zigzag partitions")
         _build_hdp_config(args).validate_tp_sp_partition(tp_size=args.tp_size, use_sp=args.use_sp)
+    if args.pp_size > 1 and args.pp_microbatches and args.micro_batch_size % args.pp_microbatches:
+        raise ValueError(f"--micro-batch-size={args.micro_batch_size} must be divisible by --pp-microbatches={args.pp_microbatches} "
+                         "(the pipeline runner cuts every micro-batch into that many pieces)")
     if getattr(args, "token_weighted_loss", False) and args.hdp_balanced:
         raise ValueError("--token-weighted-loss is implied by --hdp-balanced (HDP weights every rank's loss by its targets)")
     if args.ep_size > 1 and args.dp_size % args.ep_size:

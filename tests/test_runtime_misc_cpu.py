@@ -397,3 +397,13 @@ def test_tensor_parallel_overlap_workspace_is_sized_and_prewarmed_at_setup(monke
         plugin.on_setup_phase(SetupPhase.FINALIZE, nn.Linear(1, 1))
     prewarm.assert_called_once_with(group, min_workspace_bytes=80 * 2**20)
     assert plugin.native_comm_overlap_workspace_prewarmed is True
+
+
+def test_pipeline_micro_batches_must_divide_the_micro_batch():
+    from maltos_b200.train import cli, flags as F
+
+    base = ["--model", "llama", "--dim", "64", "--n-heads", "4", "--hidden-size", "128", "--n-layers", "2", "--vocab-size", "256", "--seq-len", "32",
+            "--pp-size", "2"]
+    cli.validate_args(F.parse_args_from(base + ["--micro-batch-size", "4", "--pp-microbatches", "2"], require_data=False), 2)
+    with pytest.raises(ValueError, match="divisible by --pp-microbatches=2"):
+        cli.validate_args(F.parse_args_from(base + ["--micro-batch-size", "3", "--pp-microbatches", "2"], require_data=False), 2)
