@@ -178,6 +178,17 @@ def _artifact(manifest: CheckpointManifest, kind: str, rank: int) -> CheckpointA
     return next((a for a in manifest.artifacts if a.kind == kind and a.rank == rank), None)
 
 
+def _read_artifact(path):
+    """One ``.pt`` file of a checkpoint; an unreadable file (truncated by a crash or a full disk, damaged in transit) is
+    reported with its path instead of the archive reader's message."""
+    try:
+        return torch.load(path, map_location="cpu", weights_only=True)
+    except FileNotFoundError:
+        raise
+    except Exception as exc:  # noqa: BLE001 - zip / pickle errors of any kind
+        raise ValueError(f"checkpoint file {path} cannot be read (truncated or corrupt?): {type(exc).__name__}: {exc}") from exc
+
+
 def load_sharded_checkpoint(state_manager: StateManager, path, *, weights_only: bool = False) -> None:
     runtime = state_manager.runtime
     ckpt = Path(path)
@@ -192,10 +203,10 @@ def load_sharded_checkpoint(state_manager: StateManager, path, *, weights_only: 
         if t_art is None:
             raise ValueError(f"manifest missing trainer artifact for rank={rank}")
         with torch.serialization.safe_globals([PpStatus]):
-            trainer_blob = torch.load(ckpt / t_art.path, map_location="cpu", weights_only=True)
+            trainer_blob = _read_artifact(ckpt / t_art.path)
         o_art = _artifact(manifest, "optimizer", manifest.optimizer_source_ranks[rank])
         if o_art is not None:
-            optim_blob = torch.load(ckpt / o_art.path, map_location="cpu", weights_only=True)
+            optim_blob = _read_artifact(ckpt / o_art.path)
 
     state_manager.import_model_state(model_state)
     optimizer, _ = runtime.get_optimizer_and_scheduler()
@@ -229,7 +240,7 @@ def _gather_model_entries(ckpt: Path, manifest: CheckpointManifest, rank_meta: R
         if art is None:
             raise ValueError(f"manifest missing model artifact for source rank={src} (used by rank={rank}, entry={entry.state_key})")
         if src not in opened:
-            opened[src] = torch.load(ckpt / art.path, map_location="cpu", weights_only=True)
+            opened[src] = _read_artifact(ckpt / art.path)
         if entry.state_key not in opened[src]:
             raise ValueError(f"model state missing entry={entry.state_key} in source rank={src} artifact")
         out[entry.state_key] = opened[src][entry.state_key]

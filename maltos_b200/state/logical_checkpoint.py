@@ -29,7 +29,7 @@ import torch.distributed as dist
 
 from maltos_b200.parallel.specs import TpSpShardAxis
 from maltos_b200.runtime.mesh import MeshAxis
-from maltos_b200.state.checkpoint import CheckpointManifest, load_checkpoint_manifest
+from maltos_b200.state.checkpoint import CheckpointManifest, _read_artifact, load_checkpoint_manifest
 from maltos_b200.state.state import ModelStateMeta
 
 if TYPE_CHECKING:
@@ -328,7 +328,7 @@ class _RankFiles:
             artifact = _find_model_artifact(self.manifest, rank)
             if artifact is None:
                 raise ValueError(f"manifest missing model artifact for rank={rank}")
-            self._cache[rank] = torch.load(self.dir / artifact.path, map_location="cpu", weights_only=True)
+            self._cache[rank] = _read_artifact(self.dir / artifact.path)
         state = self._cache[rank]
         if state_key not in state:
             raise ValueError(f"model state missing entry={state_key} in source rank={rank} artifact")

@@ -155,6 +155,11 @@ def test_manifest_validation_errors(tmp_path):
     load_sharded_checkpoint(fresh.state_manager, ckpt)
     for (n, a), (_, b) in zip(rt.model.named_parameters(), fresh.model.named_parameters()):
         assert torch.equal(a, b), n
+    # a file cut short (a crash or a full disk while it was written elsewhere, a partial copy) is named in the error
+    model_file = next(ckpt.glob("model_rank_*.pt"))
+    model_file.write_bytes(model_file.read_bytes()[:200])
+    with pytest.raises(ValueError, match=f"{model_file.name} cannot be read"):
+        load_sharded_checkpoint(_tiny_runtime().state_manager, ckpt)
     assert fresh.state.step_context.step == 1
     with pytest.raises(RuntimeError, match="insufficient free space"):
         save_sharded_checkpoint(rt.state_manager, tmp_path / "step_00000002", min_free_gb=1e9)
