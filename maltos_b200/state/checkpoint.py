@@ -23,7 +23,7 @@ import torch
 import torch.distributed as dist
 
 from maltos_b200.runtime.types import PpStatus, RuntimePhase
-from maltos_b200.utils.distributed import distributed_barrier
+from maltos_b200.utils.distributed import distributed_barrier, raise_if_any_rank_failed
 
 from .state import ModelStateMeta, OptimizerState, RngState, StateManager, TrainerState
 
@@ -193,20 +193,26 @@ def load_sharded_checkpoint(state_manager: StateManager, path, *, weights_only: 
     runtime = state_manager.runtime
     ckpt = Path(path)
     rank, _ = _rank_world()
-    manifest = load_checkpoint_manifest(ckpt)
-    _validate_manifest_for_runtime(manifest, runtime, weights_only=weights_only)
-
-    model_state = _gather_model_entries(ckpt, manifest, manifest.ranks[rank], rank)
-    trainer_blob = optim_blob = None
-    if not weights_only:
-        t_art = _artifact(manifest, "trainer", rank)
-        if t_art is None:
-            raise ValueError(f"manifest missing trainer artifact for rank={rank}")
-        with torch.serialization.safe_globals([PpStatus]):
-            trainer_blob = _read_artifact(ckpt / t_art.path)
-        o_art = _artifact(manifest, "optimizer", manifest.optimizer_source_ranks[rank])
-        if o_art is not None:
-            optim_blob = _read_artifact(ckpt / o_art.path)
+    # Reading is file work without collectives, and every rank reads different files: one of them may fail alone (a file
+    # cut short, a missing mount). All ranks learn of it here, before the first collective of the import.
+    model_state = trainer_blob = optim_blob = None
+    failure = None
+    try:
+        manifest = load_checkpoint_manifest(ckpt)
+        _validate_manifest_for_runtime(manifest, runtime, weights_only=weights_only)
+        model_state = _gather_model_entries(ckpt, manifest, manifest.ranks[rank], rank)
+        if not weights_only:
+            t_art = _artifact(manifest, "trainer", rank)
+            if t_art is None:
+                raise ValueError(f"manifest missing trainer artifact for rank={rank}")
+            with torch.serialization.safe_globals([PpStatus]):
+                trainer_blob = _read_artifact(ckpt / t_art.path)
+            o_art = _artifact(manifest, "optimizer", manifest.optimizer_source_ranks[rank])
+            if o_art is not None:
+                optim_blob = _read_artifact(ckpt / o_art.path)
+    except Exception as exc:  # noqa: BLE001 - re-raised below, on every rank
+        failure = exc
+    raise_if_any_rank_failed(failure, f"reading checkpoint {ckpt}")
 
     state_manager.import_model_state(model_state)
     optimizer, _ = runtime.get_optimizer_and_scheduler()

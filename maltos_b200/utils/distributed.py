@@ -193,6 +193,26 @@ def distributed_barrier() -> None:
         dist.barrier()
 
 
+def raise_if_any_rank_failed(error: BaseException | None, what: str) -> None:
+    """Collective over the world: every rank reports whether its part of ``what`` worked; if one failed, ALL raise - the
+    failing rank its own exception, the others a ``RuntimeError`` that names the ranks - instead of walking into the next
+    collective without it and waiting there for the process-group timeout."""
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        if error is not None:
+            raise error
+        return
+    on_gpu = dist.get_backend() == "nccl" and torch.cuda.is_available()
+    flags = torch.zeros(dist.get_world_size(), dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()) if on_gpu else "cpu")
+    if error is not None:
+        flags[dist.get_rank()] = 1
+    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    failed = [r for r, f in enumerate(flags.tolist()) if f]
+    if error is not None:
+        raise error
+    if failed:
+        raise RuntimeError(f"{what} failed on rank(s) {failed}; this rank stops with them")
+
+
 def group_size(group) -> int:
     if group is None or not dist.is_initialized():
         return 1

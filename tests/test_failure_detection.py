@@ -104,6 +104,47 @@ def test_loader_failure_propagates_and_checkpoint_guards(tmp_path):
     rt2.close()
 
 
+def _truncated_file_case(rank, world, root):
+    """Two data-parallel ranks with ZeRO-3 (every rank reads its own files); rank 1's model file is cut short."""
+    import time
+
+    from maltos_b200.state import load_sharded_checkpoint, save_sharded_checkpoint
+    from maltos_b200.train import cli, flags as F
+
+    a = F.parse_args_from(["--model", "tiny", "--dim", "32", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "64", "--n-layers", "1", "--vocab-size", "64",
+                           "--seq-len", "16", "--dp-size", "2", "--zero-stage", "3", "--precision", "fp32", "--disable-metrics"], require_data=False)
+    torch.manual_seed(0)
+    core = cli._build_runtime(a, cli._build_model(a), torch.device("cpu"))
+    core.setup()
+    ckpt = f"{root}/step_00000000"
+    save_sharded_checkpoint(core.state_manager, ckpt)
+    if rank == 1:
+        path = f"{ckpt}/model_rank_1.pt"
+        data = open(path, "rb").read()
+        open(path, "wb").write(data[: len(data) // 2])
+    import torch.distributed as dist
+
+    dist.barrier()
+    t0 = time.monotonic()
+    try:
+        load_sharded_checkpoint(core.state_manager, ckpt)
+        outcome = "loaded"
+    except Exception as exc:  # noqa: BLE001
+        outcome = f"{type(exc).__name__}: {exc}"
+    seconds = time.monotonic() - t0
+    core.close()
+    return outcome, seconds
+
+
+def test_every_rank_stops_when_one_rank_cannot_read_its_checkpoint_file(tmp_path):
+    from tests.dist_utils import run_distributed
+
+    (own, t_own), (other, t_other) = reversed(run_distributed(_truncated_file_case, 2, str(tmp_path)))
+    assert own.startswith("ValueError") and "model_rank_1.pt cannot be read" in own, own
+    assert other.startswith("RuntimeError") and "failed on rank(s) [1]" in other, other      # the healthy rank does not wait for a timeout
+    assert max(t_own, t_other) < 20.0
+
+
 # ------------------------------------------------------------------------------------------------ device side
 @pytest.mark.gpu
 def test_wait_on_a_flag_nobody_sets_times_out_cleanly():
