@@ -85,29 +85,41 @@ def save_sharded_checkpoint_from_model_state(state_manager: StateManager, path, 
 
 
 def _save(sm: StateManager, final_dir: Path, min_free_gb, model_override, entries_override, with_training: bool) -> None:
-    if min_free_gb is not None:
-        _check_min_free_space(final_dir.parent, min_free_gb)
+    # A refusal or an I/O error on one rank (the directory exists, the disk is full) stops ALL ranks at the next agreement
+    # point: a rank that raised alone would leave the others waiting in the barrier behind it.
     rank, _ = _rank_world()
     tmp_dir = final_dir.with_name(final_dir.name + ".tmp")
-    if rank == 0:
-        if final_dir.exists():
-            if any(final_dir.iterdir()):
-                raise FileExistsError(f"checkpoint already exists: {final_dir}")
-            final_dir.rmdir()
-        if tmp_dir.exists():
-            shutil.rmtree(tmp_dir)
-        tmp_dir.parent.mkdir(parents=True, exist_ok=True)
-    distributed_barrier()
-    _write_rank_files(sm, tmp_dir, model_override, entries_override, with_training)
-    distributed_barrier()
+    failure = None
+    try:
+        if min_free_gb is not None:
+            _check_min_free_space(final_dir.parent, min_free_gb)
+        if rank == 0:
+            if final_dir.exists():
+                if any(final_dir.iterdir()):
+                    raise FileExistsError(f"checkpoint already exists: {final_dir}")
+                final_dir.rmdir()
+            if tmp_dir.exists():
+                shutil.rmtree(tmp_dir)
+            tmp_dir.parent.mkdir(parents=True, exist_ok=True)
+    except Exception as exc:  # noqa: BLE001 - re-raised on every rank
+        failure = exc
+    raise_if_any_rank_failed(failure, f"preparing checkpoint directory {final_dir}")
+    written = None
+    try:
+        written = _write_local_files(sm, tmp_dir, model_override, entries_override, with_training)
+    except Exception as exc:  # noqa: BLE001
+        failure = exc
+    raise_if_any_rank_failed(failure, f"writing checkpoint files under {tmp_dir}")
+    _write_manifest(sm, tmp_dir, *written)
     if rank == 0:
         tmp_dir.rename(final_dir)
     distributed_barrier()
 
 
-def _write_rank_files(sm: StateManager, out_dir: Path, model_override, entries_override, with_training: bool) -> None:
+def _write_local_files(sm: StateManager, out_dir: Path, model_override, entries_override, with_training: bool):
+    """This rank's ``.pt`` files; returns ``(entries, artifacts)`` as JSON-ready lists for the manifest."""
     runtime = sm.runtime
-    rank, world = _rank_world()
+    rank, _ = _rank_world()
     out_dir.mkdir(parents=True, exist_ok=True)
 
     if model_override is not None and entries_override is not None:
@@ -132,7 +144,13 @@ def _write_rank_files(sm: StateManager, out_dir: Path, model_override, entries_o
         torch.save(asdict(sm.export_trainer_state()), out_dir / trainer_file)
         artifacts.append(asdict(CheckpointArtifact("trainer", rank, trainer_file)))
 
-    entry_dicts = [asdict(e) for e in entries]
+    return [asdict(e) for e in entries], artifacts
+
+
+def _write_manifest(sm: StateManager, out_dir: Path, entry_dicts, artifacts) -> None:
+    """Collective: rank 0 gathers every rank's entries and artifacts and writes ``manifest.json``."""
+    runtime = sm.runtime
+    rank, world = _rank_world()
     if dist.is_initialized():
         all_entries = [None] * world if rank == 0 else None
         all_artifacts = [None] * world if rank == 0 else None

@@ -132,14 +132,20 @@ def _truncated_file_case(rank, world, root):
     except Exception as exc:  # noqa: BLE001
         outcome = f"{type(exc).__name__}: {exc}"
     seconds = time.monotonic() - t0
+    try:                                   # a second save into the same place: rank 0 refuses, rank 1 must not wait in a barrier
+        save_sharded_checkpoint(core.state_manager, ckpt)
+        second = "saved"
+    except Exception as exc:  # noqa: BLE001
+        second = f"{type(exc).__name__}: {exc}"
     core.close()
-    return outcome, seconds
+    return outcome, seconds, second
 
 
 def test_every_rank_stops_when_one_rank_cannot_read_its_checkpoint_file(tmp_path):
     from tests.dist_utils import run_distributed
 
-    (own, t_own), (other, t_other) = reversed(run_distributed(_truncated_file_case, 2, str(tmp_path)))
+    (own, t_own, save_1), (other, t_other, save_0) = reversed(run_distributed(_truncated_file_case, 2, str(tmp_path)))
+    assert save_0.startswith("FileExistsError") and save_1.startswith("RuntimeError") and "failed on rank(s) [0]" in save_1, (save_0, save_1)
     assert own.startswith("ValueError") and "model_rank_1.pt cannot be read" in own, own
     assert other.startswith("RuntimeError") and "failed on rank(s) [1]" in other, other      # the healthy rank does not wait for a timeout
     assert max(t_own, t_other) < 20.0
