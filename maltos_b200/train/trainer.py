@@ -18,6 +18,7 @@ import torch.distributed as dist
 from maltos_b200.data.prefetch import PrefetchDataLoader
 from maltos_b200.runtime.mesh import MeshAxis
 from maltos_b200.state.checkpoint import save_runtime_spec, save_sharded_checkpoint
+from maltos_b200.utils.distributed import raise_if_any_rank_failed
 from maltos_b200.utils.metrics import MetricAggregator, PendingMetricFlush
 from maltos_b200.utils.profiling import span
 
@@ -109,10 +110,13 @@ class Trainer:
         self.runtime.state_manager.bind_dataloader(self.dataloader)
         self.runtime.setup(checkpoint_path=self.config.resume_from, load_weights_only=self.config.load_weights_only)
         if self.config.checkpoint_every is not None:
-            if _is_log_rank():
-                save_runtime_spec(self.config.checkpoint_dir, self.runtime_spec)
-            if dist.is_initialized():
-                dist.barrier()
+            failure = None
+            try:
+                if _is_log_rank():
+                    save_runtime_spec(self.config.checkpoint_dir, self.runtime_spec)
+            except Exception as exc:  # noqa: BLE001 - an unwritable checkpoint directory must stop every rank, now
+                failure = exc
+            raise_if_any_rank_failed(failure, f"writing the runtime spec under {self.config.checkpoint_dir}")
         self._last_logged_step = self.runtime.state.step_context.step
 
     def _cp_rank(self):
