@@ -212,3 +212,17 @@ def test_every_recipe_and_every_profiler_case_validates():
             ptp._synthetic_config(ptp._parse_tool_args(["--case", case.name]), case)
     finally:
         os.chdir(here)
+
+
+def test_doctor_reports_the_installation_and_finds_every_entry_point(capsys):
+    """Without a CUDA device the tool still loads the kernel library (it has no link-time dependency on the driver) and
+    checks that every ``mb_*`` entry point the package calls is exported; exit code 0 = nothing a CUDA run needs is missing."""
+    from maltos_b200.tools import doctor
+
+    report = doctor.collect()
+    lib = report["library"]
+    if lib["present"]:
+        assert lib["loads"] and lib["entry_points_called"] >= 30 and lib["entry_points_missing"] == [], lib
+    assert report["mode"].startswith("cpu") == (not report["devices"])
+    assert doctor.main(["--json"]) == (1 if [p for p in report["problems"] if not p.startswith("no peer access")] else 0)
+    assert '"library"' in capsys.readouterr().out
