@@ -186,7 +186,11 @@ def test_same_losses_as_the_reference_on_four_ranks(name, extra, model, shards, 
 
 
 @pytest.mark.skipif(not (REF / "runtime" / "core.py").exists(), reason="reference not installed under baseline/_ref")
-@pytest.mark.parametrize("model", [["--model", "olmo2"], ["--model", "tiny"], ["--model", "tiny_moe", "--num-experts", "4", "--moe-aux-loss-coef", "0.01"]])
+@pytest.mark.parametrize("model", [["--model", "olmo2"], ["--model", "tiny"], ["--model", "tiny_moe", "--num-experts", "4", "--moe-aux-loss-coef", "0.01"],
+                                   # optimizer and schedule flags: warm-up, cosine decay to a floor, weight decay, betas
+                                   ["--lr", "3e-3", "--lr-schedule", "cosine", "--warmup-steps", "1", "--min-lr", "3e-4", "--weight-decay", "0.1",
+                                    "--adam-beta2", "0.95", "--grad-clip", "0.5"],
+                                   ["--lr", "3e-3", "--lr-schedule", "linear", "--warmup-steps", "2", "--min-lr", "1e-4", "--fused-adamw"]])
 def test_every_model_family_trains_like_the_reference_in_one_process(model, shards, tmp_path):
     """Same flags, same seed, one process each: the logged losses of three optimizer steps are equal digit for digit (OLMo:
     rotate-half rotary pairing, q/k norm over the whole projection, post-norm blocks; MoE: router, balance term). In one
