@@ -98,6 +98,35 @@ def validate_args(args: argparse.Namespace, world_size: int) -> None:
             raise ValueError("--wandb-checkpoint-every requires enabled W&B logging")
 
 
+def latest_checkpoint(checkpoint_dir) -> Path | None:
+    """Newest COMPLETE checkpoint under ``checkpoint_dir``: the highest ``step_XXXXXXXX`` that has a manifest (a directory
+    still being written is called ``step_XXXXXXXX.tmp`` and never matches)."""
+    if checkpoint_dir is None or not Path(checkpoint_dir).is_dir():
+        return None
+    steps = sorted(p for p in Path(checkpoint_dir).glob("step_[0-9]*") if p.is_dir() and p.name[5:].isdigit() and (p / "manifest.json").is_file())
+    return steps[-1] if steps else None
+
+
+def resolve_resume_path(resume_from, checkpoint_dir, *, rank: int):
+    """``--resume-from latest``: the newest complete checkpoint of ``--checkpoint-dir`` (an error if there is none);
+    ``--resume-from auto``: the same, or a fresh start when there is none - the form a restart loop wants (the reference
+    takes explicit paths only). Rank 0 looks and tells the others, so that every rank resumes from the same step even
+    while a retention policy deletes old checkpoints. Any other value is returned as given."""
+    if resume_from not in ("latest", "auto"):
+        return resume_from
+    found = [None]
+    if rank == 0:
+        hit = latest_checkpoint(checkpoint_dir)
+        found = [None if hit is None else str(hit)]
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.broadcast_object_list(found, src=0)
+    if found[0] is None and resume_from == "latest":
+        raise ValueError(f"--resume-from latest: no complete checkpoint (step_XXXXXXXX with manifest.json) under --checkpoint-dir={checkpoint_dir}")
+    if rank == 0:
+        print(f"resume_from={resume_from} -> {found[0] or 'fresh start'}", flush=True)
+    return found[0]
+
+
 # ------------------------------------------------------------------------------------------------ model
 def _variant(base, tp, sp, args):
     return sp if args.use_sp else (tp if args.tp_size > 1 else base)
@@ -526,6 +555,7 @@ def main(argv: list[str] | None = None) -> None:
     dp_rank = mesh.rank_coordinates(rank)[0]
     model = _build_model(args)
     n_params = _count_trainable_params(model)
+    args.resume_from = resolve_resume_path(args.resume_from, args.checkpoint_dir, rank=rank)
     runtime = _build_runtime(args, model, device)
     data_paths, loader, data_format = _build_dataloader(args, dp_rank=dp_rank, cp_token_planner=runtime.plan.cp_token_planner)
     loggers, uploader = (None, None) if args.dry_run else _build_logging(args, rank)

@@ -203,3 +203,25 @@ def test_every_model_family_trains_like_the_reference_in_one_process(model, shar
     ref = _losses(_run([sys.executable, "tools/train.py", "--data", str(shards), *flags, "--max-steps", "3", "--checkpoint-dir", str(tmp_path / "ref")],
                        REF, {"PYTHONPATH": str(REF)}))
     assert len(ours) == 3 and ours == ref, (ours, ref)
+
+
+def test_resume_from_auto_and_latest_pick_the_newest_complete_checkpoint(shards, tmp_path):
+    """A restart loop passes the same command line every time: ``--resume-from auto`` starts fresh the first time and
+    continues from the newest complete ``step_*`` afterwards (rank 0 looks, all ranks follow); an unfinished ``.tmp``
+    directory and a directory without manifest are ignored; ``latest`` insists on a checkpoint."""
+    from maltos_b200.train.cli import latest_checkpoint, resolve_resume_path
+
+    ckpt = tmp_path / "run"
+    extra = ["--dp-size", "2", "--zero-stage", "1", "--resume-from", "auto"]
+    first = _losses(_launch(ROOT, ["-m", "maltos_b200.tools.train"], shards, ckpt, 4, extra, 2))
+    assert len(first) == 4 and latest_checkpoint(ckpt).name == "step_00000004"
+    (ckpt / "step_00000009.tmp").mkdir()                     # a save that was interrupted
+    (ckpt / "step_00000008").mkdir()                         # a directory without manifest
+    assert latest_checkpoint(ckpt).name == "step_00000004"
+    again = _losses(_launch(ROOT, ["-m", "maltos_b200.tools.train"], shards, ckpt, 6, extra, 2))
+    uninterrupted = _losses(_launch(ROOT, ["-m", "maltos_b200.tools.train"], shards, tmp_path / "straight", 6, extra[:-2], 2))
+    assert len(again) == 2 and again == uninterrupted[4:], (again, uninterrupted)
+    assert resolve_resume_path("auto", tmp_path / "nothing_here", rank=0) is None
+    assert resolve_resume_path(str(ckpt / "step_00000002"), ckpt, rank=0) == str(ckpt / "step_00000002")
+    with pytest.raises(ValueError, match="no complete checkpoint"):
+        resolve_resume_path("latest", tmp_path / "nothing_here", rank=0)
