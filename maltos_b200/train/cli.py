@@ -566,6 +566,10 @@ def main(argv: list[str] | None = None) -> None:
                              checkpoint_keep_last=args.checkpoint_keep_last, checkpoint_keep_every_n_steps=args.checkpoint_keep_every_n_steps,
                              checkpoint_min_free_gb=args.checkpoint_min_free_gb, data_prefetch_batches=args.data_prefetch_batches))
     trainer.setup()
+    if getattr(args, "graceful_stop", False):
+        import signal
+
+        trainer.enable_graceful_stop(signals=(signal.SIGTERM, signal.SIGUSR1))
     common = dict(args=args, runtime=runtime, initial_trainable_params=n_params, data_paths=data_paths, data_format=data_format,
                   device=device, world_size=world)
     _print_run_summary(rank=rank, **common)
@@ -577,6 +581,8 @@ def main(argv: list[str] | None = None) -> None:
         runtime.close()
     else:
         trainer.fit()
+        if trainer.stopped_early_at is not None and rank == 0:
+            print(f"stopped on request after step {trainer.stopped_early_at}", flush=True)
     if dist.is_initialized():
         distributed_barrier()
         dist.destroy_process_group()

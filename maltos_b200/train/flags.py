@@ -136,6 +136,8 @@ FLAGS: tuple[Flag, ...] = (
     Flag("checkpoint_keep_every_n_steps", int, None, yaml=("checkpoint.keep_every_n_steps", "checkpoint.checkpoint_keep_every_n_steps")),
     Flag("checkpoint_min_free_gb", float, None, yaml=("checkpoint.min_free_gb", "checkpoint.checkpoint_min_free_gb")),
     Flag("resume_from", str, None, yaml=("checkpoint.resume_from",)),
+    # SIGTERM / SIGUSR1 end the run cleanly: all ranks finish the same step, save it and exit (resume with --resume-from auto)
+    Flag("graceful_stop", BOOL, False, yaml=("checkpoint.graceful_stop",)),
     Flag("load_weights_only", BOOL, False, yaml=("checkpoint.load_weights_only",)),
     # launch
     Flag("backend", str, None),

@@ -105,6 +105,10 @@ class Trainer:
         self.runtime_spec = runtime_spec
         self._last_logged_step = 0
         self._pending_log: PendingMetricFlush | None = None
+        self._graceful_stop = False
+        self._stop_requested = False
+        self._stop_pending = None
+        self.stopped_early_at: int | None = None
 
     def setup(self) -> None:
         self.runtime.state_manager.bind_dataloader(self.dataloader)
@@ -118,6 +122,44 @@ class Trainer:
                 failure = exc
             raise_if_any_rank_failed(failure, f"writing the runtime spec under {self.config.checkpoint_dir}")
         self._last_logged_step = self.runtime.state.step_context.step
+
+    # ------------------------------------------------------------------ graceful stop (not in the reference)
+    def enable_graceful_stop(self, signals=()) -> None:
+        """After this call ``request_stop()`` - from any rank, e.g. from the handler installed here for ``signals`` (a
+        scheduler's SIGTERM before preemption) - ends ``fit()`` cleanly: all ranks finish the same optimizer step, write a
+        checkpoint of it (when a checkpoint directory is configured) and return; ``--resume-from auto`` continues there.
+        The ranks agree through one asynchronous one-element all-reduce per optimizer step that is read a step later, when
+        it has long finished: no extra synchronisation in the step, and a stop takes effect within two steps."""
+        import signal as _signal
+
+        self._graceful_stop = True
+        for sig in signals:
+            _signal.signal(sig, lambda *_: self.request_stop())
+
+    def request_stop(self) -> None:
+        self._stop_requested = True
+
+    def _stop_agreed(self) -> bool:
+        """Once per optimizer step on every rank: reads the agreement issued a step ago, issues the next one."""
+        if not self._graceful_stop:
+            return False
+        import torch
+
+        from maltos_b200.utils.metrics import _metric_device
+
+        previous, self._stop_pending = self._stop_pending, None
+        agreed = False
+        if previous is not None:
+            work, flag = previous
+            if work is not None:
+                work.wait()
+            agreed = bool(flag.item())
+        flag = torch.tensor([1.0 if self._stop_requested else 0.0], device=_metric_device())
+        work = None
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            work = dist.all_reduce(flag, op=dist.ReduceOp.MAX, async_op=True)
+        self._stop_pending = (work, flag)
+        return agreed
 
     def _cp_rank(self):
         if not self.runtime.plan.batch_data_cp_aware:
@@ -139,6 +181,10 @@ class Trainer:
                     self.metric_aggregator.update(rt.collect_metrics())   # one host read of the loss per optimizer step
                 self._maybe_log()
                 self._maybe_checkpoint()
+                if self._stop_agreed():
+                    self.stopped_early_at = rt.state.step_context.step
+                    self._maybe_checkpoint(force=True)
+                    break
             self._flush_pending_log()
         finally:
             rt.close()
@@ -173,10 +219,15 @@ class Trainer:
                 self._emit(pending.wait())
 
     # ------------------------------------------------------------------ checkpoints
-    def _maybe_checkpoint(self) -> None:
+    def _maybe_checkpoint(self, force: bool = False) -> None:
         every = self.config.checkpoint_every
         step = self.runtime.state.step_context.step
-        if every is None or step == 0 or step % every:
+        if every is None or step == 0:
+            return
+        if force:
+            if step % every == 0:
+                return                          # the regular save of this step has just been written
+        elif step % every:
             return
         target = _checkpoint_step_dir(self.config.checkpoint_dir, step)
         with span("maltos::checkpoint.save"):

@@ -151,6 +151,68 @@ def test_every_rank_stops_when_one_rank_cannot_read_its_checkpoint_file(tmp_path
     assert max(t_own, t_other) < 20.0
 
 
+def _graceful_stop_case(rank, world, root):
+    """Rank 1 alone is told to stop while step 3 is being prepared (a scheduler's SIGTERM reaches ranks at different
+    times); both ranks must leave after the SAME step with a checkpoint of it."""
+    from maltos_b200.data import SimpleTensorDataLoader
+    from maltos_b200.train import Trainer, TrainerConfig, cli, flags as F
+
+    a = F.parse_args_from(["--model", "tiny", "--dim", "32", "--n-heads", "4", "--n-kv-heads", "2", "--hidden-size", "64", "--n-layers", "1", "--vocab-size", "64",
+                           "--seq-len", "16", "--dp-size", "2", "--zero-stage", "1", "--precision", "fp32", "--disable-metrics", "--lr", "1e-2"], require_data=False)
+
+    def run(ckpt_dir, resume, stop_at, max_steps):
+        torch.manual_seed(0)
+        core = cli._build_runtime(a, cli._build_model(a), torch.device("cpu"))
+        g = torch.Generator().manual_seed(5 + rank)
+        loader = SimpleTensorDataLoader(torch.randint(0, 64, (64, 17), generator=g), batch_size=2)
+        trainer = Trainer(runtime=core, dataloader=loader, runtime_spec={"v": 1},
+                          config=TrainerConfig(max_steps=max_steps, log_every=100, checkpoint_every=50, checkpoint_dir=ckpt_dir, resume_from=resume))
+        trainer.setup()
+        trainer.enable_graceful_stop()
+        inner = loader.next_batch
+        calls = {"n": 0}
+
+        def next_batch(cp_rank=None):
+            calls["n"] += 1
+            if stop_at is not None and rank == 1 and calls["n"] == stop_at:
+                trainer.request_stop()
+            t = inner(cp_rank)
+            t = t["input_ids"] if isinstance(t, dict) else t
+            return {"input_ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()}
+
+        loader.next_batch = next_batch
+        losses = []
+        step_optimizer = core.step_optimizer
+
+        def record():
+            step_optimizer()
+            losses.append(float(core.collect_metrics()["loss"]))
+
+        core.step_optimizer = record
+        trainer.fit()
+        return trainer.stopped_early_at, losses
+
+    stopped, first = run(f"{root}/a", None, 3, 8)
+    from maltos_b200.train.cli import latest_checkpoint
+
+    newest = latest_checkpoint(f"{root}/a")
+    _, rest = run(f"{root}/a", str(newest), None, 8)
+    _, straight = run(f"{root}/b", None, None, 8)
+    return stopped, newest.name, first, rest, straight
+
+
+def test_a_stop_request_on_one_rank_ends_all_ranks_after_the_same_step_with_a_checkpoint(tmp_path):
+    from tests.dist_utils import run_distributed
+
+    results = run_distributed(_graceful_stop_case, 2, str(tmp_path))
+    stops = {r[0] for r in results}
+    assert len(stops) == 1 and 3 <= next(iter(stops)) <= 5, stops                  # requested before step 3, effective within two steps
+    step = next(iter(stops))
+    for stopped, newest, first, rest, straight in results:
+        assert newest == f"step_{step:08d}" and len(first) == step
+        assert first + rest == pytest.approx(straight, abs=1e-6) and len(straight) == 8      # stop + resume == uninterrupted
+
+
 # ------------------------------------------------------------------------------------------------ device side
 @pytest.mark.gpu
 def test_wait_on_a_flag_nobody_sets_times_out_cleanly():
