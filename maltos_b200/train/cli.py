@@ -570,6 +570,8 @@ def main(argv: list[str] | None = None) -> None:
         import signal
 
         trainer.enable_graceful_stop(signals=(signal.SIGTERM, signal.SIGUSR1))
+    if getattr(args, "heartbeat_timeout", None):
+        trainer.enable_heartbeat(timeout=float(args.heartbeat_timeout), interval=min(1.0, float(args.heartbeat_timeout) / 4))
     common = dict(args=args, runtime=runtime, initial_trainable_params=n_params, data_paths=data_paths, data_format=data_format,
                   device=device, world_size=world)
     _print_run_summary(rank=rank, **common)

@@ -138,6 +138,8 @@ FLAGS: tuple[Flag, ...] = (
     Flag("resume_from", str, None, yaml=("checkpoint.resume_from",)),
     # SIGTERM / SIGUSR1 end the run cleanly: all ranks finish the same step, save it and exit (resume with --resume-from auto)
     Flag("graceful_stop", BOOL, False, yaml=("checkpoint.graceful_stop",)),
+    # seconds without a heartbeat after which a rank is reported lost (host-side check before every micro-step); unset = off
+    Flag("heartbeat_timeout", float, None, yaml=("training.heartbeat_timeout",)),
     Flag("load_weights_only", BOOL, False, yaml=("checkpoint.load_weights_only",)),
     # launch
     Flag("backend", str, None),

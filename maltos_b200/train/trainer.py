@@ -109,6 +109,7 @@ class Trainer:
         self._stop_requested = False
         self._stop_pending = None
         self.stopped_early_at: int | None = None
+        self.heartbeat = None
 
     def setup(self) -> None:
         self.runtime.state_manager.bind_dataloader(self.dataloader)
@@ -135,6 +136,14 @@ class Trainer:
         self._graceful_stop = True
         for sig in signals:
             _signal.signal(sig, lambda *_: self.request_stop())
+
+    def enable_heartbeat(self, *, timeout: float, interval: float = 1.0) -> None:
+        """Watch the other ranks from a background thread (``utils/heartbeat.py``); ``fit()`` then checks before every
+        micro-step and raises ``PeerLostError`` instead of launching into a collective that a dead rank will never join."""
+        from maltos_b200.utils.heartbeat import HeartbeatMonitor
+
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            self.heartbeat = HeartbeatMonitor.for_default_group(interval=interval, timeout=timeout).start()
 
     def request_stop(self) -> None:
         self._stop_requested = True
@@ -172,6 +181,8 @@ class Trainer:
             while rt.state.step_context.step < self.config.max_steps:
                 with span("maltos::data.next_batch"):
                     batch = self.dataloader.next_batch(self._cp_rank())
+                if self.heartbeat is not None:
+                    self.heartbeat.check()
                 _, should_step = rt.run_step(batch)
                 if not should_step:
                     continue
@@ -187,6 +198,8 @@ class Trainer:
                     break
             self._flush_pending_log()
         finally:
+            if self.heartbeat is not None:
+                self.heartbeat.stop()
             rt.close()
             closer = getattr(self.dataloader, "close", None)
             if callable(closer):

@@ -213,6 +213,57 @@ def test_a_stop_request_on_one_rank_ends_all_ranks_after_the_same_step_with_a_ch
         assert first + rest == pytest.approx(straight, abs=1e-6) and len(straight) == 8      # stop + resume == uninterrupted
 
 
+def _heartbeat_worker(rank, world, port, queue):
+    import time
+
+    from maltos_b200.utils.heartbeat import HeartbeatMonitor, PeerLostError
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    monitor = HeartbeatMonitor.for_default_group(interval=0.2, timeout=1.5).start()
+    t = torch.ones(1)
+    dist.all_reduce(t)                               # a healthy step with everyone
+    if rank == 3:                                    # finishes normally: must not be reported
+        monitor.stop()
+        queue.put((rank, "left on purpose"))
+    elif rank == 2:                                  # disappears between steps, nothing of its own in flight
+        queue.put((rank, "vanished"))
+        queue.close()
+        queue.join_thread()
+        os._exit(0)
+    else:
+        t0 = time.monotonic()
+        outcome = "nothing noticed"
+        while time.monotonic() - t0 < 20:
+            try:
+                monitor.check()                      # what the trainer does before every micro-step
+            except PeerLostError as exc:
+                outcome = f"lost {exc.ranks} after {time.monotonic() - t0:.1f}s"
+                break
+            time.sleep(0.1)
+        monitor.stop()
+        queue.put((rank, outcome))
+    queue.close()
+    queue.join_thread()
+    os._exit(0)                                      # no collective shutdown: a peer is gone
+
+
+def test_heartbeat_names_the_rank_that_vanished_before_the_next_collective():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_heartbeat_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=90) for _ in range(4))
+    for p in procs:
+        p.join(timeout=30)
+    assert got[2] == "vanished" and got[3] == "left on purpose"
+    for survivor in (0, 1):
+        assert got[survivor].startswith("lost [2] after"), got           # rank 3 ended normally and is not reported
+        assert float(got[survivor].split("after ")[1][:-1]) < 10.0, got
+
+
 # ------------------------------------------------------------------------------------------------ device side
 @pytest.mark.gpu
 def test_wait_on_a_flag_nobody_sets_times_out_cleanly():
