@@ -24,6 +24,10 @@ class Fp16Plugin(RuntimePlugin):
         return rt is not None and rt.dtype == torch.float16 and (torch.device(rt.device).type == "cuda" or self.allow_cpu)
 
     def on_setup_phase(self, phase: SetupPhase, model):
+        rt = self.runtime
+        if phase is SetupPhase.FINALIZE and rt.dtype == torch.float16 and not self.active:
+            # fp16 without loss scaling underflows silently: refuse, as the reference does (``fp16.py:28-33``)
+            raise ValueError("Fp16Plugin requires CUDA model parameters for float16 training (allow_cpu=True enables the CPU scaler for tests)")
         if phase is SetupPhase.FINALIZE and self.active:
             from maltos_b200.utils.amp import DistributedGradScaler
 
@@ -37,6 +41,7 @@ class Fp16Plugin(RuntimePlugin):
             st = self.runtime.state
             if st.loss is not None:
                 st.metadata["raw_loss_for_metrics"] = st.loss.detach().float()
+                st.metadata["loss_scaled_for_backward"] = True
                 st.loss = self.scaler.scale(st.loss)
 
     def export_plugin_state(self):

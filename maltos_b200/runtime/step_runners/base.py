@@ -50,8 +50,10 @@ class DefaultStepRunner:
             if grad_output is None:
                 if st.loss is None:
                     raise TypeError("RuntimeCore expected runtime.state.loss to be a Tensor before backward()")
-                # the metric must show the un-divided loss
-                st.metadata["raw_loss_for_metrics"] = st.loss.detach().float()
+                # the metric must show the un-divided loss - and the un-SCALED one: the fp16 plugin has kept it before it
+                # multiplied the loss at PRE_BACKWARD (the reference overwrites it here and logs loss x scale under fp16)
+                if not st.metadata.pop("loss_scaled_for_backward", False):
+                    st.metadata["raw_loss_for_metrics"] = st.loss.detach().float()
                 div = st.step_context.loss_divisor
                 if div != 1:
                     st.loss = st.loss / div

@@ -312,7 +312,7 @@ def _build_runtime(args: argparse.Namespace, model: nn.Module, device: torch.dev
 
         plugins.append(CudaGraphPlugin())
     if dtype == torch.float16:
-        plugins.append(Fp16Plugin())
+        plugins.append(Fp16Plugin(allow_cpu=torch.device(device).type == "cpu"))     # CPU runs (tests) scale the loss too
     if not weights_only and args.grad_clip is not None:
         if args.zero_stage == 0:
             plugins.append(GradClipPlugin(max_norm=args.grad_clip))

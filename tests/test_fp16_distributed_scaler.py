@@ -1,6 +1,7 @@
 """fp16 loss scaling when gradients are spread over ranks (ZeRO shards, tensor-parallel shards): an overflow seen by ONE
 rank must skip the step and back the scale off on EVERY rank; clipping must act on unscaled norms. Two gloo ranks on CPU
 (the plugin is switched on for CPU explicitly; on CUDA it is active whenever the dtype is fp16)."""
+import pytest
 import torch
 
 from tests.dist_utils import run_distributed
@@ -79,3 +80,38 @@ def test_overflow_is_a_global_decision_under_zero3():
 
 def test_overflow_on_one_tensor_parallel_shard_skips_the_step_everywhere():
     _check(run_distributed(_train, 2, "tp"))
+
+
+def test_fp16_logs_the_unscaled_loss_and_refuses_to_run_without_a_scaler():
+    """The loss metric is the model's loss, not loss x scale (the step runner used to overwrite the value the plugin had
+    kept before scaling - as the reference does), and float16 on CPU without ``allow_cpu`` is refused at setup instead of
+    training without loss scaling (reference ``tests/smoke_runtime_core.py:716-733``)."""
+    import torch.nn as nn
+
+    from maltos_b200.runtime import RuntimeCore
+    from maltos_b200.runtime.plugins.fp16 import Fp16Plugin
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(4, 4)
+
+        def forward(self, x):
+            return self.lin(x.to(self.lin.weight.dtype)).float().pow(2).mean()
+
+    torch.manual_seed(0)
+    core = RuntimeCore(model=Model(), dtype=torch.float16, grad_accum_steps=2, optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.01),
+                       plugins=[Fp16Plugin(allow_cpu=True)])
+    core.setup()
+    x = torch.randn(8, 4)
+    expected = float(core.model(x))
+    core.run_step(x)
+    core.run_step(x)
+    core.step_optimizer()
+    metrics = core.collect_metrics()
+    assert abs(float(metrics["loss"]) - expected) < 1e-3 * max(1.0, expected), (metrics["loss"], expected)
+    assert float(core.state.scaler.get_scale()) >= 2.0 ** 15
+    core.close()
+    refused = RuntimeCore(model=Model(), dtype=torch.float16, optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.01), plugins=[Fp16Plugin()])
+    with pytest.raises(ValueError, match="requires CUDA model parameters"):
+        refused.setup()
