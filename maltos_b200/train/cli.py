@@ -27,7 +27,7 @@ from maltos_b200.parallel.context_interfaces import ContextParallelAttentionCore
 from maltos_b200.parallel.context_token_planner import ContextTokenPlannerType
 from maltos_b200.runtime.core import RuntimeCore
 from maltos_b200.runtime.mesh import MeshConfig
-from maltos_b200.utils.distributed import distributed_barrier
+from maltos_b200.utils.distributed import distributed_barrier, raise_if_any_rank_failed
 
 from .flags import build_runtime_spec, parse_args
 from .trainer import Trainer, TrainerConfig
@@ -557,7 +557,14 @@ def main(argv: list[str] | None = None) -> None:
     n_params = _count_trainable_params(model)
     args.resume_from = resolve_resume_path(args.resume_from, args.checkpoint_dir, rank=rank)
     runtime = _build_runtime(args, model, device)
-    data_paths, loader, data_format = _build_dataloader(args, dp_rank=dp_rank, cp_token_planner=runtime.plan.cp_token_planner)
+    # data paths are per host: a mount missing on one node must stop every rank here, not leave the others in the first barrier
+    failure, built = None, (None, None, None)
+    try:
+        built = _build_dataloader(args, dp_rank=dp_rank, cp_token_planner=runtime.plan.cp_token_planner)
+    except Exception as exc:  # noqa: BLE001 - re-raised on every rank
+        failure = exc
+    raise_if_any_rank_failed(failure, "opening the training data")
+    data_paths, loader, data_format = built
     loggers, uploader = (None, None) if args.dry_run else _build_logging(args, rank)
     trainer = Trainer(
         runtime=runtime, dataloader=loader, logger=loggers, checkpoint_uploader=uploader, runtime_spec=build_runtime_spec(args),
