@@ -140,6 +140,7 @@ class RuntimeCore:
         self._param_roles.clear()
         for plugin in self.plugins:
             plugin.bind(self)
+        self._refuse_tied_parameters_under_model_splitting()
         self._run_setup_phase(SetupPhase.TRANSFORM)
         self._run_setup_phase(SetupPhase.MATERIALIZE)
         self.state_manager.register_module(self.model)
@@ -158,6 +159,21 @@ class RuntimeCore:
             from maltos_b200.state.checkpoint import load_sharded_checkpoint
 
             load_sharded_checkpoint(self.state_manager, checkpoint_path, weights_only=load_weights_only)
+
+    def _refuse_tied_parameters_under_model_splitting(self) -> None:
+        """A parameter that two modules share (tied input / output embeddings) cannot be cut by tensor or pipeline parallelism
+        the way the plugins cut modules - one module at a time: the halves would stop being the same tensor, silently (the
+        reference accepts it and trains two diverging copies)."""
+        splitting = [pid for pid in (PluginId.TP, PluginId.TP_SP, PluginId.PP) if self.has_plugin(pid)]
+        if not splitting:
+            return
+        owners: dict[int, list[str]] = {}
+        for name, param in self.model.named_parameters(remove_duplicate=False):
+            owners.setdefault(id(param), []).append(name)
+        tied = [names for names in owners.values() if len(names) > 1]
+        if tied:
+            raise ValueError(f"parameters shared between modules {tied[:4]} are not supported with {[p.value for p in splitting]}: "
+                             "untie them (tie_word_embeddings=False) or train without tensor / pipeline parallelism")
 
     def _run_setup_phase(self, phase: SetupPhase) -> None:
         if phase is SetupPhase.MATERIALIZE and self._model_state_owner is self:

@@ -407,3 +407,21 @@ def test_pipeline_micro_batches_must_divide_the_micro_batch():
     cli.validate_args(F.parse_args_from(base + ["--micro-batch-size", "4", "--pp-microbatches", "2"], require_data=False), 2)
     with pytest.raises(ValueError, match="divisible by --pp-microbatches=2"):
         cli.validate_args(F.parse_args_from(base + ["--micro-batch-size", "3", "--pp-microbatches", "2"], require_data=False), 2)
+
+
+def test_tied_embeddings_are_refused_when_a_plugin_splits_the_model():
+    from maltos_b200.models import LlamaConfig, LlamaForCausalLM
+    from maltos_b200.runtime import MeshConfig, RuntimeCore
+    from maltos_b200.runtime.plugins.tp import TensorParallelPlugin
+
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                      max_position_embeddings=16, tie_word_embeddings=True)
+    plain = RuntimeCore(model=LlamaForCausalLM(cfg), optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.1))
+    plain.setup()                                          # one process, nothing split: tying is fine
+    ids = torch.randint(0, 64, (2, 16))
+    plain.run_step({"input_ids": ids, "labels": ids.roll(-1, 1)})
+    assert plain.model.lm_head.weight is plain.model.embed_tokens.weight
+    split = RuntimeCore(model=LlamaForCausalLM(cfg), mesh=MeshConfig(tp=2), optimizer_factory=lambda p: torch.optim.SGD(p, lr=0.1),
+                        plugins=[TensorParallelPlugin()])
+    with pytest.raises(ValueError, match="shared between modules"):
+        split.setup()
