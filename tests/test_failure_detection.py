@@ -220,7 +220,7 @@ def _heartbeat_worker(rank, world, port, queue):
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
-    monitor = HeartbeatMonitor.for_default_group(interval=0.2, timeout=1.5).start()
+    monitor = HeartbeatMonitor.for_default_group(interval=0.3, timeout=3.0).start()
     t = torch.ones(1)
     dist.all_reduce(t)                               # a healthy step with everyone
     if rank == 3:                                    # finishes normally: must not be reported
@@ -261,7 +261,7 @@ def test_heartbeat_names_the_rank_that_vanished_before_the_next_collective():
     assert got[2] == "vanished" and got[3] == "left on purpose"
     for survivor in (0, 1):
         assert got[survivor].startswith("lost [2] after"), got           # rank 3 ended normally and is not reported
-        assert float(got[survivor].split("after ")[1][:-1]) < 10.0, got
+        assert float(got[survivor].split("after ")[1][:-1]) < 15.0, got
 
 
 # ------------------------------------------------------------------------------------------------ device side
