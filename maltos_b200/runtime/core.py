@@ -56,11 +56,19 @@ def order_plugins(plugins: list[RuntimePlugin]) -> list[RuntimePlugin]:
         for later in p.runs_before:
             if later in by_id:
                 graph[later].add(p.id)
-    # feed the sorter in declaration order so that unconstrained plugins keep the user's order
-    sorter = TopologicalSorter()
-    for p in plugins:
-        sorter.add(p.id, *graph[p.id])
-    return [by_id[pid] for pid in sorter.static_order()]
+    # Deterministic on every rank: among the plugins whose predecessors are all placed, the one declared first goes next.
+    # (Feeding sets of ids to a generic sorter breaks ties by the iteration order of those sets, which follows the
+    # per-process string hash seed: two ranks could order unconstrained plugins - and their collectives - differently.)
+    TopologicalSorter(graph).prepare()          # raises CycleError with the offending cycle
+    ordered: list[RuntimePlugin] = []
+    placed: set[PluginId] = set()
+    remaining = list(plugins)
+    while remaining:
+        nxt = next(p for p in remaining if graph[p.id] <= placed)
+        ordered.append(nxt)
+        placed.add(nxt.id)
+        remaining.remove(nxt)
+    return ordered
 
 
 def _single_owner(plugins: list[RuntimePlugin], flag: str, what: str):

@@ -36,9 +36,15 @@ class CompilePlugin(RuntimePlugin):
                     self._modules.append(m)
         return model
 
+    @property
+    def compiled_module_paths(self) -> list[str]:
+        """The reference's name for the covered module paths (there: the modules whose ``forward`` was compiled)."""
+        return list(self.covered_paths)
+
     def param_materialization_groups(self):
         """Each covered module's parameters are gathered together by ZeRO-3 (they are used by one fused region)."""
         return tuple((m, tuple(m.parameters())) for m in self._modules if any(True for _ in m.parameters()))
 
     def collect_metrics(self):
-        return {"fused_scopes": len(self._modules)}
+        return {"fused_scopes": len(self._modules), "compile/scope": self.scope, "compile/backend": self.backend, "compile/mode": self.mode,
+                "compile/modules": len(self.covered_paths)}

@@ -54,8 +54,7 @@ class Fp16Plugin(RuntimePlugin):
     def collect_metrics(self):
         rt = self.runtime
         out = {"dtype": str(rt.dtype).replace("torch.", "") if rt.dtype is not None else "float32"}
-        if self.scaler is not None:
-            md = rt.state.metadata
-            out["loss_scale"] = md.get("loss_scale")
-            out["overflow"] = bool(md.get("overflow", False))
+        md = rt.state.metadata          # without a scaler (fp32 / bf16): scale None, never an overflow - the reference's keys
+        out["loss_scale"] = md.get("loss_scale") if self.scaler is not None else None
+        out["overflow"] = bool(md.get("overflow", False)) if self.scaler is not None else False
         return out

@@ -55,6 +55,7 @@ class GradClipPlugin(RuntimePlugin):
         coef, norm = clip_coefficient(sq, self.max_norm)
         scale_tensors_(grads, coef)
         self._norm = norm
+        rt.state.metadata["grad_norm"] = norm       # a device scalar: read by whoever wants the number (the reference stores a float)
 
     def collect_metrics(self):
         if self._norm is None:

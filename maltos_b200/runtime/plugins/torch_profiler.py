@@ -64,6 +64,14 @@ class TorchProfilerPlugin(RuntimePlugin):
         if self.rank0_only and at_boundary and dist.is_initialized():
             dist.barrier()
 
+    def collect_metrics(self):
+        """The reference's keys (``runtime/plugins/torch_profiler.py:88-97``)."""
+        enabled = self._profiler is not None
+        out_dir = self.trace_dir / f"rank_{self._rank():05d}"
+        return {"torch_profiler/enabled": enabled, "torch_profiler/rank0_only": self.rank0_only,
+                "torch_profiler/trace_dir": str(out_dir) if enabled else None, "torch_profiler/wait": self.wait,
+                "torch_profiler/warmup": self.warmup, "torch_profiler/active": self.active, "torch_profiler/repeat": self.repeat}
+
     def close(self) -> None:
         if self._profiler is not None:
             self._profiler.stop()

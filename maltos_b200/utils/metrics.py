@@ -57,7 +57,7 @@ _EXACT_LAST = {"lr", "step", "microbatch_idx", "grad_accum_steps", "scheduler_la
 def _rule_for_key(key: str, rules: dict[str, MetricRule]) -> MetricRule:
     if key in rules:
         return rules[key]
-    if key == "loss" or key.startswith("loss/") or key.endswith("/loss"):
+    if key == "loss" or key.startswith("loss/") or key.endswith("/loss") or key.endswith("_loss"):      # moe/load_balance_loss too
         return MetricRule(_R.MEAN, _R.MEAN)
     if key in _EXACT_LAST or key.endswith("/lr"):
         return _LAST0
